@@ -1,0 +1,691 @@
+// "direct-conv-tc": 3x3 convolution (+bias, +ReLU, +2x2 max pool, over a concat
+// of two operands, the first optionally read through a 2x nearest upsample) as
+// an implicit GEMM on the sm_100a tensor cores: tcgen05.mma with fp32
+// accumulators in tensor memory.  It replaces direct_conv_cm.comp and
+// concat_conv_cm.comp of the reference
+// (compiler/src/denox/compiler/implement/shaders/conv/), keeps their GEMM view
+// (M = pixels, N = all output channels, K = taps x channels walked tap major,
+// direct_conv_cm.comp:328-334) and their two phase concat (operand a's channels
+// then operand b's into one accumulator, concat_conv_cm.comp:1042-1127).
+//
+// Shape of the computation
+//   A persistent CTA (one per SM) walks work units.  A unit is a strip of 128
+//   pixels in x times RB output rows.  Input rows stream through a ring of
+//   shared memory slots (one slot = one input row of the strip: 130 pixels x
+//   all channels), so every input row is fetched once per unit and reused by
+//   the three vertical taps; the three horizontal taps are the same slot read
+//   at a 16 byte offset.  One MMA covers M = 128 pixels of one output row.
+//   R output rows form a pass: the pass walks the 9 taps once and issues, per
+//   tap and per 16 channel step, R MMAs that share the weight tile.
+//
+// Shared memory operand layout (no swizzle, K major "core matrices" of 8 rows
+// x 16 bytes): slot[chunk c8][pixel p][8 halves].  For an MMA the 8 row groups
+// of M are 128 bytes apart (SBO) and the two 8 channel halves of a K=16 step
+// are one chunk pitch apart (LBO).  Weights: w[tap][chunk c8][n][8 halves],
+// SBO = 128, LBO = N*16.
+//
+// Warp roles (320 threads): warp 0 issues MMAs and owns the TMEM allocation,
+// warp 1 moves weights with bulk async copies, warps 2-5 are the epilogue
+// (TMEM -> registers -> ReLU / pool -> global), warps 6-9 fill the input slots
+// with 16 byte cp.async (zero fill = conv padding; the upsample is the address
+// map src = dst / 2, basic_upsample.comp:49-56).
+//
+// Every wait on an mbarrier is bounded: when a wait runs out the kernel raises
+// a CTA wide abort flag, stores a code to the dispatch's device_status word
+// and every role leaves its loop; TMEM is freed on that path too.
+#include "internal.h"
+#include <stdlib.h>
+
+namespace dnxcu {
+namespace {
+
+constexpr int STRIP = 128;        // pixels per MMA (M)
+constexpr int SLOT_PX = 130;      // pixels held per slot row (strip + 1 left + 1 right)
+constexpr int WH = 137;           // slot pixel pitch: chunk pitch = 137*16 B = 16 (mod 128) -> conflict free fills
+constexpr int CHUNK_PITCH = WH * 16;
+constexpr int HEADER_BYTES = 1024;
+constexpr int MAX_SLOTS = 16;
+constexpr int MAX_WST = 4;
+constexpr int N_PRODUCER = 128;
+constexpr int THREADS = 320;
+constexpr unsigned long long WAIT_LIMIT_CYCLES = 3000000000ull;  // about 1.5 s
+
+// barrier indices inside the header
+constexpr int BAR_FULL = 0;                   // [MAX_SLOTS] slot filled (4 producer warps arrive)
+constexpr int BAR_EMPTY = BAR_FULL + MAX_SLOTS;   // [MAX_SLOTS] slot free (tcgen05.commit)
+constexpr int BAR_TFULL = BAR_EMPTY + MAX_SLOTS;  // [2] accumulator set complete (tcgen05.commit)
+constexpr int BAR_TEMPTY = BAR_TFULL + 2;         // [2] accumulator set drained (4 epilogue warps)
+constexpr int BAR_WFULL = BAR_TEMPTY + 2;         // [MAX_WST] weight stage landed
+constexpr int BAR_WEMPTY = BAR_WFULL + MAX_WST;   // [MAX_WST] weight stage consumed
+constexpr int BAR_WRES = BAR_WEMPTY + MAX_WST;    // resident weights landed
+constexpr int BAR_COUNT = BAR_WRES + 1;
+static_assert(BAR_COUNT * 8 + 16 <= HEADER_BYTES, "header too small");
+constexpr int OFF_TMEM_PTR = BAR_COUNT * 8;
+constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
+
+struct Seg {
+  const __half *ptr;  // H x W x C (or (H/2) x (W/2) x C when up)
+  const __half *top;  // row above the band or nullptr
+  const __half *bot;  // row below the band or nullptr
+  int C;              // channels
+  int nch;            // 8 channel chunks after padding C to a multiple of 16
+  int up;
+};
+
+struct TcArgs {
+  Seg a, b;
+  const __half *w;  // [9][nch_a + nch_b][N][8]
+  const __half *bias;
+  __half *out;
+  __half *out_pool;
+  int *status;
+  int H, W, K, N, Ns;
+  int relu, pool, full_out;
+  int RB, S, nstrips, nunits;
+  int wstream, WST;
+  uint32_t tmem_cols;
+  int desc_swap;  // debugging aid: exchange the two descriptor strides
+};
+
+// ---- PTX wrappers ---------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another ran out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
+                                          int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = clock64();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 0) {
+      if (*abort_flag) return false;
+      if ((unsigned long long)clock64() - t0 > WAIT_LIMIT_CYCLES) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
+      "[%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared memory matrix descriptor, no swizzle, K major:
+// bits [0,14) start >> 4, [16,30) leading byte offset >> 4 (between the two
+// 8 channel core matrices of a K = 16 step), [32,46) stride byte offset >> 4
+// (between 8 row groups), bits [46,48) = 1 (sm_100 descriptor version).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
+         (1ull << 46);
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
+struct Unit {
+  int x0, y0, rows_out, npass, rows_in;
+};
+template <int R>
+__device__ __forceinline__ Unit unit_of(const TcArgs &g, int u) {
+  Unit t;
+  const int strip = u % g.nstrips, rb = u / g.nstrips;
+  t.x0 = strip * STRIP;
+  t.y0 = rb * g.RB;
+  int rows = g.H - t.y0;
+  if (rows > g.RB) rows = g.RB;
+  t.npass = (rows + R - 1) / R;
+  t.rows_out = t.npass * R;
+  t.rows_in = t.rows_out + 2;
+  return t;
+}
+
+// Fills one slot with input row iy of the strip starting at x0 (pixels x0-1 .. x0+128).
+__device__ __forceinline__ void load_row(const TcArgs &g, uint32_t slot_addr, int iy, int x0, int tid) {
+  int chbase = 0;
+#pragma unroll 1
+  for (int sg = 0; sg < 2; ++sg) {
+    const Seg &s = sg ? g.b : g.a;
+    if (s.nch == 0) continue;
+    const int Ws = s.up ? g.W >> 1 : g.W;
+    const __half *row = nullptr;
+    if (iy < 0) row = (iy == -1) ? s.top : nullptr;
+    else if (iy >= g.H) row = (iy == g.H) ? s.bot : nullptr;
+    else row = s.ptr + (long long)(s.up ? iy >> 1 : iy) * Ws * s.C;
+    const int items = SLOT_PX * s.nch;
+    const bool vec = (s.C & 7) == 0;
+    const int nchv = s.C >> 3;
+#pragma unroll 1
+    for (int i = tid; i < items; i += N_PRODUCER) {
+      const int px = i / s.nch, ch = i - px * s.nch;
+      const int ix = x0 - 1 + px;
+      const bool inb = row != nullptr && ix >= 0 && ix < g.W;
+      const uint32_t dst = slot_addr + (uint32_t)((chbase + ch) * CHUNK_PITCH + px * 16);
+      const long long poff = (long long)(s.up ? ix >> 1 : ix) * s.C + ch * 8;
+      if (vec) {
+        const bool ok = inb && ch < nchv;
+        cp_async16(dst, ok ? (const void *)(row + poff) : (const void *)s.ptr, ok ? 16u : 0u);
+      } else {
+        uint32_t v[4] = {0u, 0u, 0u, 0u};
+        if (inb) {
+          const unsigned short *p = reinterpret_cast<const unsigned short *>(row + poff);
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            if (ch * 8 + e < s.C) v[e >> 1] |= (uint32_t)__ldg(p + e) << ((e & 1) * 16);
+        }
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
+                     : "memory");
+      }
+    }
+    chbase += s.nch;
+  }
+}
+
+template <int R>
+__global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const TcArgs g) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const uint32_t sbase = smem_u32(smem);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + OFF_ABORT);
+  volatile uint32_t *tmem_ptr = reinterpret_cast<volatile uint32_t *>(smem + OFF_TMEM_PTR);
+  auto bar = [&](int i) { return sbase + (uint32_t)i * 8u; };
+
+  const int nch = g.a.nch + g.b.nch;
+  const uint32_t wtap_bytes = (uint32_t)nch * g.N * 16u;
+  const uint32_t w_addr = sbase + HEADER_BYTES;
+  const uint32_t wregion = g.wstream ? wtap_bytes * g.WST : wtap_bytes * 9u;
+  const uint32_t slot_bytes = (uint32_t)nch * CHUNK_PITCH;
+  const uint32_t slots_addr = w_addr + ((wregion + 127u) & ~127u);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < MAX_SLOTS; ++i) {
+      mbar_init(bar(BAR_FULL + i), 4);
+      mbar_init(bar(BAR_EMPTY + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(BAR_TFULL + i), 1);
+      mbar_init(bar(BAR_TEMPTY + i), 4);
+    }
+    for (int i = 0; i < MAX_WST; ++i) {
+      mbar_init(bar(BAR_WFULL + i), 1);
+      mbar_init(bar(BAR_WEMPTY + i), 1);
+    }
+    mbar_init(bar(BAR_WRES), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + OFF_TMEM_PTR),
+                 "r"(g.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp == 0) {
+    // ---------------- MMA issue ----------------
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(g.N >> 3) << 17) | ((uint32_t)(STRIP >> 4) << 24);
+      const uint32_t a_lbo = g.desc_swap ? 128u : (uint32_t)CHUNK_PITCH;
+      const uint32_t a_sbo = g.desc_swap ? (uint32_t)CHUNK_PITCH : 128u;
+      const uint32_t b_lbo = g.desc_swap ? 128u : (uint32_t)g.N * 16u;
+      const uint32_t b_sbo = g.desc_swap ? (uint32_t)g.N * 16u : 128u;
+      const int nk16 = nch >> 1;
+      bool ok = true;
+      if (!g.wstream) ok = mbar_wait(bar(BAR_WRES), 0, abort_flag, g.status, 1);
+      int gbase = 0, gpass = 0, gw = 0;
+      for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
+        const Unit t = unit_of<R>(g, u);
+        int waited = 0;
+        for (int p = 0; ok && p < t.npass; ++p) {
+          const int need = p * R + R + 1;
+          while (ok && waited <= need) {
+            const int gg = gbase + waited;
+            ok = mbar_wait(bar(BAR_FULL + gg % g.S), (uint32_t)(gg / g.S) & 1u, abort_flag, g.status, 2);
+            ++waited;
+          }
+          if (!ok) break;
+          const int set = gpass & 1;
+          ok = mbar_wait(bar(BAR_TEMPTY + set), ((uint32_t)(gpass >> 1) & 1u) ^ 1u, abort_flag, g.status, 3);
+          if (!ok) break;
+          tc_fence_after();
+          for (int tap = 0; ok && tap < 9; ++tap) {
+            const int dy = tap / 3, dx = tap - dy * 3;
+            uint32_t wb;
+            int ws = 0;
+            if (g.wstream) {
+              ws = gw % g.WST;
+              ok = mbar_wait(bar(BAR_WFULL + ws), (uint32_t)(gw / g.WST) & 1u, abort_flag, g.status, 4);
+              if (!ok) break;
+              tc_fence_after();
+              wb = w_addr + (uint32_t)ws * wtap_bytes;
+            } else {
+              wb = w_addr + (uint32_t)tap * wtap_bytes;
+            }
+            for (int kc = 0; kc < nk16; ++kc) {
+              const uint64_t bdesc = make_desc(wb + (uint32_t)kc * 2u * g.N * 16u, b_lbo, b_sbo);
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+                const int slot = (gbase + p * R + r + dy) % g.S;
+                const uint32_t aaddr =
+                    slots_addr + (uint32_t)slot * slot_bytes + (uint32_t)kc * 2u * CHUNK_PITCH + (uint32_t)dx * 16u;
+                tc_mma(tmem_base + (uint32_t)((set * R + r) * g.Ns), make_desc(aaddr, a_lbo, a_sbo), bdesc, idesc,
+                       (tap | kc) != 0 ? 1u : 0u);
+              }
+            }
+            if (g.wstream) {
+              tc_commit(bar(BAR_WEMPTY + ws));
+              ++gw;
+            }
+          }
+          if (!ok) break;
+          tc_commit(bar(BAR_TFULL + set));
+          const int nrel = (p == t.npass - 1) ? R + 2 : R;
+          for (int q = 0; q < nrel; ++q) tc_commit(bar(BAR_EMPTY + (gbase + p * R + q) % g.S));
+          ++gpass;
+        }
+        gbase += t.rows_in;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- weights ----------------
+    if (lane == 0) {
+      const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(g.w);
+      if (!g.wstream) {
+        mbar_expect_tx(bar(BAR_WRES), wtap_bytes * 9u);
+        for (int tap = 0; tap < 9; ++tap)
+          bulk_g2s(w_addr + (uint32_t)tap * wtap_bytes, wsrc + (size_t)tap * wtap_bytes, wtap_bytes, bar(BAR_WRES));
+      } else {
+        bool ok = true;
+        int gw = 0;
+        for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
+          const Unit t = unit_of<R>(g, u);
+          for (int p = 0; ok && p < t.npass; ++p)
+            for (int tap = 0; ok && tap < 9; ++tap) {
+              const int ws = gw % g.WST;
+              ok = mbar_wait(bar(BAR_WEMPTY + ws), ((uint32_t)(gw / g.WST) & 1u) ^ 1u, abort_flag, g.status, 5);
+              if (!ok) break;
+              mbar_expect_tx(bar(BAR_WFULL + ws), wtap_bytes);
+              bulk_g2s(w_addr + (uint32_t)ws * wtap_bytes, wsrc + (size_t)tap * wtap_bytes, wtap_bytes,
+                       bar(BAR_WFULL + ws));
+              ++gw;
+            }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ---------------- epilogue ----------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int m = q * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const bool vec_out = (g.K & 7) == 0;
+    bool ok = true;
+    int gpass = 0;
+    for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
+      const Unit t = unit_of<R>(g, u);
+      const int x = t.x0 + m;
+      const bool xin = x < g.W;
+      for (int p = 0; ok && p < t.npass; ++p) {
+        const int set = gpass & 1;
+        ok = mbar_wait(bar(BAR_TFULL + set), (uint32_t)(gpass >> 1) & 1u, abort_flag, g.status, 6);
+        if (!ok) break;
+        tc_fence_after();
+        const int yb = t.y0 + p * R;
+        constexpr int RSTEP = (R >= 2) ? 2 : 1;
+#pragma unroll 1
+        for (int r = 0; r < R; r += RSTEP) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < g.N; c0 += 16) {
+            uint32_t v0[16], v1[16];
+            tc_ld16(lane_addr + (uint32_t)((set * R + r) * g.Ns + c0), v0);
+            if (RSTEP == 2) tc_ld16(lane_addr + (uint32_t)((set * R + r + 1) * g.Ns + c0), v1);
+            tc_wait_ld();
+            float f0[16], f1[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float bj = 0.0f;
+              if (g.bias && c0 + j < g.K) bj = __half2float(g.bias[c0 + j]);
+              f0[j] = __uint_as_float(v0[j]) + bj;
+              if (g.relu) f0[j] = fmaxf(f0[j], 0.0f);
+              if (RSTEP == 2) {
+                f1[j] = __uint_as_float(v1[j]) + bj;
+                if (g.relu) f1[j] = fmaxf(f1[j], 0.0f);
+              }
+            }
+            if (g.full_out && xin) {
+#pragma unroll
+              for (int rr = 0; rr < RSTEP; ++rr) {
+                const int y = yb + r + rr;
+                if (y >= g.H) continue;
+                const float *f = rr ? f1 : f0;
+                __half *o = g.out + ((long long)y * g.W + x) * g.K + c0;
+                if (vec_out && c0 + 16 <= g.K) {
+                  uint4 lo = make_uint4(pack_h2(f[0], f[1]), pack_h2(f[2], f[3]), pack_h2(f[4], f[5]),
+                                        pack_h2(f[6], f[7]));
+                  uint4 hi = make_uint4(pack_h2(f[8], f[9]), pack_h2(f[10], f[11]), pack_h2(f[12], f[13]),
+                                        pack_h2(f[14], f[15]));
+                  reinterpret_cast<uint4 *>(o)[0] = lo;
+                  reinterpret_cast<uint4 *>(o)[1] = hi;
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 16; ++j)
+                    if (c0 + j < g.K) o[j] = __float2half_rn(f[j]);
+                }
+              }
+            }
+            if (RSTEP == 2 && g.pool) {
+              // 2x2 max: vertical in registers, horizontal with the neighbouring lane
+              // (basic_pool.comp:44-82; max commutes with the rounding to binary16)
+              float pm[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float vmax = fmaxf(f0[j], f1[j]);
+                pm[j] = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1));
+              }
+              const int y = yb + r;
+              if (xin && !(lane & 1) && y + 1 < g.H + (g.H & 1) && y < g.H) {
+                __half *o = g.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (x >> 1)) * g.K + c0;
+                if (vec_out && c0 + 16 <= g.K) {
+                  uint4 lo = make_uint4(pack_h2(pm[0], pm[1]), pack_h2(pm[2], pm[3]), pack_h2(pm[4], pm[5]),
+                                        pack_h2(pm[6], pm[7]));
+                  uint4 hi = make_uint4(pack_h2(pm[8], pm[9]), pack_h2(pm[10], pm[11]), pack_h2(pm[12], pm[13]),
+                                        pack_h2(pm[14], pm[15]));
+                  reinterpret_cast<uint4 *>(o)[0] = lo;
+                  reinterpret_cast<uint4 *>(o)[1] = hi;
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 16; ++j)
+                    if (c0 + j < g.K) o[j] = __float2half_rn(pm[j]);
+                }
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_TEMPTY + set));
+        ++gpass;
+      }
+    }
+  } else {
+    // ---------------- input slots ----------------
+    const int tid = threadIdx.x - 6 * 32;
+    bool ok = true;
+    int gl = 0;
+    for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
+      const Unit t = unit_of<R>(g, u);
+      for (int j = 0; ok && j < t.rows_in; ++j) {
+        const int slot = gl % g.S;
+        ok = mbar_wait(bar(BAR_EMPTY + slot), ((uint32_t)(gl / g.S) & 1u) ^ 1u, abort_flag, g.status, 7);
+        if (!ok) break;
+        load_row(g, slots_addr + (uint32_t)slot * slot_bytes, t.y0 - 1 + j, t.x0, tid);
+        cp_async_commit();
+        if (gl >= 1) {
+          cp_async_wait<1>();
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(BAR_FULL + (gl - 1) % g.S));
+        }
+        ++gl;
+      }
+    }
+    cp_async_wait<0>();
+    if (ok && gl >= 1) {
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_FULL + (gl - 1) % g.S));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(g.tmem_cols) : "memory");
+  }
+}
+
+// ---- host side --------------------------------------------------------------
+
+inline int pad16(int c) { return (c + 15) / 16 * 16; }
+inline int nch_of(int c) { return c > 0 ? pad16(c) / 8 : 0; }
+
+struct Plan {
+  TcArgs args;
+  size_t smem;
+  int grid;
+  int R;
+};
+
+constexpr size_t SMEM_LIMIT = 232448;  // 227 KB opt-in per block on sm_100
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
+// v.p0 = R (rows per pass), v.p1 = wanted slots, v.p2 = weight mode (0 resident, 1 streamed), v.p3 = weight stages
+int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl) {
+  if (!d.in_a || !d.weights || d.c_a <= 0 || d.c_out <= 0 || d.c_b < 0) return DNXCU_E_BAD_ARG;
+  if (d.pc[0] == 0 || d.pc[1] == 0) return DNXCU_E_BAD_ARG;
+  if (d.c_b > 0 && !d.in_b) return DNXCU_E_BAD_ARG;
+  if ((d.flags & DNXCU_F_BIAS) && !d.bias) return DNXCU_E_BAD_ARG;
+  const int W = (int)d.pc[0], H = (int)d.pc[1];
+  const bool up = d.flags & DNXCU_F_UP2X_A, pool = d.flags & DNXCU_F_POOL_OUT;
+  const bool full = !(d.flags & DNXCU_F_NO_FULL_OUT);
+  if ((d.flags & DNXCU_F_NO_FULL_OUT) && !pool) return DNXCU_E_BAD_ARG;
+  if (full && !d.out) return DNXCU_E_BAD_ARG;
+  if (pool && !d.out_pool) return DNXCU_E_BAD_ARG;
+  if ((up || pool) && ((W | H) & 1)) return DNXCU_E_BAD_ARG;
+  const int R = v.p0;
+  if (pool && R < 2) return DNXCU_E_UNSUPPORTED;
+  if (d.c_out > 256) return DNXCU_E_UNSUPPORTED;
+  // 16 byte rules: vector loads of operands with C % 8 == 0, vector stores when K % 8 == 0, bulk weight copies
+  if ((uintptr_t)d.weights & 15) return DNXCU_E_MISALIGNED;
+  if ((d.c_a % 8 == 0) && (((uintptr_t)d.in_a | (uintptr_t)d.halo[0] | (uintptr_t)d.halo[1]) & 15))
+    return DNXCU_E_MISALIGNED;
+  if (d.c_b > 0 && (d.c_b % 8 == 0) && (((uintptr_t)d.in_b | (uintptr_t)d.halo[2] | (uintptr_t)d.halo[3]) & 15))
+    return DNXCU_E_MISALIGNED;
+  if ((d.c_out % 8 == 0) && (((uintptr_t)d.out | (uintptr_t)d.out_pool) & 15)) return DNXCU_E_MISALIGNED;
+  if (((uintptr_t)d.in_a | (uintptr_t)d.in_b | (uintptr_t)d.out | (uintptr_t)d.out_pool | (uintptr_t)d.bias) & 1)
+    return DNXCU_E_MISALIGNED;
+
+  TcArgs &g = pl.args;
+  g.a = {(const __half *)d.in_a, (const __half *)d.halo[0], (const __half *)d.halo[1], d.c_a, nch_of(d.c_a), up ? 1 : 0};
+  g.b = {(const __half *)d.in_b, (const __half *)d.halo[2], (const __half *)d.halo[3], d.c_b, nch_of(d.c_b), 0};
+  g.w = (const __half *)d.weights;
+  g.bias = (d.flags & DNXCU_F_BIAS) ? (const __half *)d.bias : nullptr;
+  g.out = (__half *)d.out;
+  g.out_pool = (__half *)d.out_pool;
+  g.status = d.device_status;
+  g.H = H;
+  g.W = W;
+  g.K = d.c_out;
+  g.N = pad16(d.c_out);
+  g.Ns = (g.N + 31) / 32 * 32;
+  g.relu = (d.flags & DNXCU_F_RELU) ? 1 : 0;
+  g.pool = pool ? 1 : 0;
+  g.full_out = full ? 1 : 0;
+  g.wstream = v.p2;
+  g.WST = v.p3 > 0 ? v.p3 : 2;
+  if (g.WST > MAX_WST) g.WST = MAX_WST;
+  const char *sw = getenv("DNXCU_TC_DESC_SWAP");
+  g.desc_swap = (sw && sw[0] == '1') ? 1 : 0;
+
+  uint32_t cols = 2u * R * g.Ns;
+  if (cols > 512) return DNXCU_E_UNSUPPORTED;
+  uint32_t p2 = 32;
+  while (p2 < cols) p2 <<= 1;
+  g.tmem_cols = p2;
+
+  const int nch = g.a.nch + g.b.nch;
+  const size_t wtap = (size_t)nch * g.N * 16;
+  const size_t wregion = ((g.wstream ? wtap * g.WST : wtap * 9) + 127) & ~(size_t)127;
+  if (wtap * 9 >= (1u << 20)) return DNXCU_E_UNSUPPORTED;  // mbarrier transaction count limit
+  const size_t slot_bytes = (size_t)nch * CHUNK_PITCH;
+  if (HEADER_BYTES + wregion + (size_t)(R + 2) * slot_bytes > SMEM_LIMIT) return DNXCU_E_UNSUPPORTED;
+  int S = (int)((SMEM_LIMIT - HEADER_BYTES - wregion) / slot_bytes);
+  if (S > v.p1) S = v.p1;
+  if (S > MAX_SLOTS) S = MAX_SLOTS;
+  g.S = S;
+  pl.smem = HEADER_BYTES + wregion + (size_t)S * slot_bytes;
+
+  // rows per unit: whole waves of CTAs with little halo re-read
+  g.nstrips = (W + STRIP - 1) / STRIP;
+  const int sms = sm_count();
+  const int step = (R > 2 ? R : 2);
+  double best = 1e30;
+  int bestRB = step;
+  for (int rb = step; rb <= 64; rb += step) {
+    const long long units = (long long)g.nstrips * ((H + rb - 1) / rb);
+    const long long waves = (units + sms - 1) / sms;
+    const double cost = (double)waves * (rb + 2.5);
+    if (cost < best - 1e-9) {
+      best = cost;
+      bestRB = rb;
+    }
+  }
+  g.RB = bestRB;
+  g.nunits = g.nstrips * ((H + g.RB - 1) / g.RB);
+  pl.grid = g.nunits < sms ? g.nunits : sms;
+  pl.R = R;
+  return DNXCU_OK;
+}
+
+template <int R>
+int launch_r(const Plan &pl, cudaStream_t s) {
+  static bool attr_done[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && !attr_done[dev]) {
+    DNXCU_CUDA(cudaFuncSetAttribute(conv3x3_tc<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
+    attr_done[dev] = true;
+  } else if (dev >= 16) {
+    DNXCU_CUDA(cudaFuncSetAttribute(conv3x3_tc<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
+  }
+  conv3x3_tc<R><<<pl.grid, THREADS, pl.smem, s>>>(pl.args);
+  DNXCU_CUDA(cudaGetLastError());
+  return DNXCU_OK;
+}
+
+}  // namespace
+
+size_t conv_tc_weight_bytes(const Variant &, int k, int ca, int cb) {
+  return (size_t)9 * (nch_of(ca) + nch_of(cb)) * pad16(k) * 16;
+}
+
+// KCRS -> [tap][chunk c8][n][8]: operand a's chunks first, each operand's channel
+// count padded to a multiple of 16 and the output channels to a multiple of 16,
+// zero filled.  Plays the role of the RSCKC16 / KRSCK16 re-layouts of the
+// reference (common/src/denox/memory/tensor/FilterLayout.hpp:74-78,104-108).
+void conv_tc_prepare(const Variant &, const uint16_t *kcrs, int K, int ca, int cb, uint16_t *out) {
+  const int C = ca + cb, N = pad16(K), nch = nch_of(ca) + nch_of(cb);
+  const size_t n = (size_t)9 * nch * N * 8;
+  for (size_t i = 0; i < n; ++i) out[i] = 0;
+  for (int seg = 0; seg < 2; ++seg) {
+    const int Cs = seg ? cb : ca, cbase = seg ? ca : 0, chbase = seg ? nch_of(ca) : 0;
+    for (int t = 0; t < 9; ++t)
+      for (int c = 0; c < Cs; ++c)
+        for (int k = 0; k < K; ++k)
+          out[(((size_t)t * nch + chbase + c / 8) * N + k) * 8 + c % 8] = kcrs[((size_t)k * C + cbase + c) * 9 + t];
+  }
+}
+
+int conv_tc_validate(const Variant &v, const dnxcu_dispatch &d) {
+  Plan pl;
+  return make_plan(v, d, pl);
+}
+
+void conv_tc_grid(const Variant &v, const dnxcu_dispatch &d, uint32_t g[3]) {
+  Plan pl;
+  g[0] = g[1] = g[2] = 1;
+  if (make_plan(v, d, pl) == DNXCU_OK) g[0] = (uint32_t)pl.grid;
+}
+
+int conv_tc_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
+  Plan pl;
+  int st = make_plan(v, d, pl);
+  if (st) return st;
+  switch (pl.R) {
+    case 1: return launch_r<1>(pl, s);
+    case 2: return launch_r<2>(pl, s);
+    case 4: return launch_r<4>(pl, s);
+    default: return DNXCU_E_UNSUPPORTED;
+  }
+}
+
+}  // namespace dnxcu

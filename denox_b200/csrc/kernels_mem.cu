@@ -1,0 +1,195 @@
+// Bandwidth bound kernels: 2x2 max pool, 2x nearest upsample, channel concat,
+// ReLU.  Each has a 128-bit form (channel counts multiple of 8, 16-byte aligned
+// pointers) and a 2-byte form for everything else, like the reference's HWC8 /
+// HWC split (basic_pool.comp:28-226).  All are grid-stride loops over 16-byte
+// (or 2-byte) output items with consecutive threads on consecutive addresses.
+#include "internal.h"
+
+namespace dnxcu {
+namespace {
+
+__device__ __forceinline__ uint4 ldg16(const void *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
+
+__device__ __forceinline__ uint32_t hmax2u(uint32_t a, uint32_t b) {
+  __half2 r = __hmax2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
+  return *reinterpret_cast<uint32_t *>(&r);
+}
+__device__ __forceinline__ uint4 hmax8(uint4 a, uint4 b) {
+  return make_uint4(hmax2u(a.x, b.x), hmax2u(a.y, b.y), hmax2u(a.z, b.z), hmax2u(a.w, b.w));
+}
+
+// out[y][x][c] = max over the 2x2 window (basic_pool.comp:44-82), floor size.
+__global__ void pool2x2_v8(const uint4 *__restrict__ in, uint4 *__restrict__ out, int H, int W, int C8) {
+  const int H2 = H >> 1, W2 = W >> 1;
+  const long long n = (long long)H2 * W2 * C8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C8);
+    const long long p = i / C8;
+    const int x = (int)(p % W2), y = (int)(p / W2);
+    const uint4 *r0 = in + ((long long)(2 * y) * W + 2 * x) * C8 + c;
+    const uint4 *r1 = r0 + (long long)W * C8;
+    uint4 a = ldg16(r0), b = ldg16(r0 + C8), d = ldg16(r1), e = ldg16(r1 + C8);
+    out[i] = hmax8(hmax8(a, b), hmax8(d, e));
+  }
+}
+__global__ void pool2x2_s(const __half *__restrict__ in, __half *__restrict__ out, int H, int W, int C) {
+  const int H2 = H >> 1, W2 = W >> 1;
+  const long long n = (long long)H2 * W2 * C;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C);
+    const long long p = i / C;
+    const int x = (int)(p % W2), y = (int)(p / W2);
+    const __half *r0 = in + ((long long)(2 * y) * W + 2 * x) * C + c;
+    const __half *r1 = r0 + (long long)W * C;
+    out[i] = __hmax(__hmax(r0[0], r0[C]), __hmax(r1[0], r1[C]));
+  }
+}
+
+// out[y][x] = in[y/2][x/2] (basic_upsample.comp:49-56); H, W are the INPUT extent.
+__global__ void upsample2x_v8(const uint4 *__restrict__ in, uint4 *__restrict__ out, int H, int W, int C8) {
+  const int W2 = W * 2;
+  const long long n = (long long)H * 2 * W2 * C8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C8);
+    const long long p = i / C8;
+    const int x = (int)(p % W2), y = (int)(p / W2);
+    out[i] = ldg16(in + ((long long)(y >> 1) * W + (x >> 1)) * C8 + c);
+  }
+}
+__global__ void upsample2x_s(const __half *__restrict__ in, __half *__restrict__ out, int H, int W, int C) {
+  const int W2 = W * 2;
+  const long long n = (long long)H * 2 * W2 * C;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C);
+    const long long p = i / C;
+    const int x = (int)(p % W2), y = (int)(p / W2);
+    out[i] = in[((long long)(y >> 1) * W + (x >> 1)) * C + c];
+  }
+}
+
+// out[p][0:Ca] = a[p], out[p][Ca:Ca+Cb] = b[p] (copy_transform.comp:53-64).
+__global__ void concat_v8(const uint4 *__restrict__ a, const uint4 *__restrict__ b, uint4 *__restrict__ out,
+                          long long P, int Ca8, int Cb8) {
+  const int C8 = Ca8 + Cb8;
+  const long long n = P * C8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C8);
+    const long long p = i / C8;
+    out[i] = c < Ca8 ? ldg16(a + p * Ca8 + c) : ldg16(b + p * Cb8 + (c - Ca8));
+  }
+}
+__global__ void concat_s(const __half *__restrict__ a, const __half *__restrict__ b, __half *__restrict__ out,
+                         long long P, int Ca, int Cb) {
+  const int C = Ca + Cb;
+  const long long n = P * C;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C);
+    const long long p = i / C;
+    out[i] = c < Ca ? a[p * Ca + c] : b[p * Cb + (c - Ca)];
+  }
+}
+
+// max(v, 0) (basic_activation.comp:26-34)
+__global__ void relu_v8(const uint4 *__restrict__ in, uint4 *__restrict__ out, long long n8) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * blockDim.x) {
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    out[i] = hmax8(ldg16(in + i), z);
+  }
+}
+__global__ void relu_s(const __half *__restrict__ in, __half *__restrict__ out, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    out[i] = __hmax(in[i], __float2half(0.0f));
+}
+
+constexpr int kThreads = 256;
+
+// Number of 16-byte (or 2-byte) items the dispatch writes.
+long long item_count(const Variant &v, const dnxcu_dispatch &d) {
+  const long long W = d.pc[0], H = d.pc[1];
+  const int vec = v.p0;
+  switch (v.kind) {
+    case VK_POOL: return (H / 2) * (W / 2) * (d.c_a / vec);
+    case VK_UPSAMPLE: return 4 * H * W * (d.c_a / vec);
+    case VK_CONCAT: return H * W * ((d.c_a + d.c_b) / vec);
+    case VK_RELU: return H * W * d.c_a / vec;
+    default: return 0;
+  }
+}
+
+int sm_count_cached() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+}  // namespace
+
+void mem_grid(const Variant &v, const dnxcu_dispatch &d, uint32_t g[3]) {
+  const long long n = item_count(v, d);
+  // whole waves of resident blocks: a multiple of the SM count, 8 blocks of 256 per SM at most
+  const long long want = (n + kThreads - 1) / kThreads;
+  const long long cap = (long long)sm_count_cached() * 8;
+  long long blocks = want < cap ? want : cap;
+  if (blocks < 1) blocks = 1;
+  g[0] = (uint32_t)blocks;
+  g[1] = g[2] = 1;
+}
+
+int mem_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
+  const int W = (int)d.pc[0], H = (int)d.pc[1];
+  const int vec = v.p0;
+  if (!d.in_a || !d.out || W <= 0 || H <= 0 || d.c_a <= 0) return DNXCU_E_BAD_ARG;
+  if (v.kind == VK_CONCAT && (!d.in_b || d.c_b <= 0)) return DNXCU_E_BAD_ARG;
+  if (vec == 8) {
+    if (d.c_a % 8 || (v.kind == VK_CONCAT && d.c_b % 8)) {
+      if (v.kind != VK_RELU || ((long long)H * W * d.c_a) % 8) return DNXCU_E_UNSUPPORTED;
+    }
+    if (((uintptr_t)d.in_a | (uintptr_t)d.out | (uintptr_t)d.in_b) & 15) return DNXCU_E_MISALIGNED;
+  } else {
+    if (((uintptr_t)d.in_a | (uintptr_t)d.out | (uintptr_t)d.in_b) & 1) return DNXCU_E_MISALIGNED;
+  }
+  if (v.kind == VK_POOL && (H < 2 || W < 2)) return DNXCU_E_BAD_ARG;
+  uint32_t g[3];
+  mem_grid(v, d, g);
+  const long long P = (long long)H * W;
+  switch (v.kind) {
+    case VK_POOL:
+      if (vec == 8) pool2x2_v8<<<g[0], kThreads, 0, s>>>((const uint4 *)d.in_a, (uint4 *)d.out, H, W, d.c_a / 8);
+      else pool2x2_s<<<g[0], kThreads, 0, s>>>((const __half *)d.in_a, (__half *)d.out, H, W, d.c_a);
+      break;
+    case VK_UPSAMPLE:
+      if (vec == 8) upsample2x_v8<<<g[0], kThreads, 0, s>>>((const uint4 *)d.in_a, (uint4 *)d.out, H, W, d.c_a / 8);
+      else upsample2x_s<<<g[0], kThreads, 0, s>>>((const __half *)d.in_a, (__half *)d.out, H, W, d.c_a);
+      break;
+    case VK_CONCAT:
+      if (vec == 8)
+        concat_v8<<<g[0], kThreads, 0, s>>>((const uint4 *)d.in_a, (const uint4 *)d.in_b, (uint4 *)d.out, P,
+                                            d.c_a / 8, d.c_b / 8);
+      else
+        concat_s<<<g[0], kThreads, 0, s>>>((const __half *)d.in_a, (const __half *)d.in_b, (__half *)d.out, P,
+                                           d.c_a, d.c_b);
+      break;
+    case VK_RELU:
+      if (vec == 8) relu_v8<<<g[0], kThreads, 0, s>>>((const uint4 *)d.in_a, (uint4 *)d.out, P * d.c_a / 8);
+      else relu_s<<<g[0], kThreads, 0, s>>>((const __half *)d.in_a, (__half *)d.out, P * d.c_a);
+      break;
+    default: return DNXCU_E_BAD_ARG;
+  }
+  DNXCU_CUDA(cudaGetLastError());
+  return DNXCU_OK;
+}
+
+}  // namespace dnxcu

@@ -1,0 +1,341 @@
+/*
+ * dnxcu — C ABI of the sm_100a dispatch backend for denox fp16 HWC U-Nets.
+ *
+ * denox has no C ABI of its own: its hot path sits behind C++ interfaces
+ * (variant generator, dispatch record, runtime instance, benchmark database).
+ * Each entry point below names the reference interface it stands in for
+ * (paths relative to the reference project root).  A maintainer binds these
+ * from the reference's C++ with a plain `extern "C"` include; nothing here
+ * uses C++ types, exceptions or torch types.
+ *
+ * Conventions
+ *  - every function returns DNXCU_OK (0) or a negative dnxcu_status;
+ *    nothing throws, aborts or exits;
+ *  - tensors are HWC binary16: index(h,w,c) = (h*W + w)*C + c
+ *    (common/src/denox/memory/tensor/ActivationLayout.hpp:38-40);
+ *  - "launch" calls are stream ordered and never synchronise; the caller owns
+ *    every device buffer it passes in;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ */
+#ifndef DNXCU_H
+#define DNXCU_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define DNXCU_API
+#else
+#define DNXCU_API __attribute__((visibility("default")))
+#endif
+
+typedef enum dnxcu_status {
+  DNXCU_OK = 0,
+  DNXCU_E_BAD_ARG = -1,      /* null pointer, non-positive size, inconsistent channels */
+  DNXCU_E_UNSUPPORTED = -2,  /* the variant cannot run this shape / flag combination   */
+  DNXCU_E_MISALIGNED = -3,   /* a pointer breaks the variant's alignment rule          */
+  DNXCU_E_CUDA = -4,         /* a CUDA runtime call failed; see dnxcu_last_cuda_error  */
+  DNXCU_E_DEVICE = -5,       /* a kernel reported a bounded wait that ran out          */
+  DNXCU_E_NO_MEMORY = -6,
+  DNXCU_E_STATE = -7,        /* object used in the wrong state                         */
+  DNXCU_E_IO = -8,           /* database file could not be read or written             */
+  DNXCU_E_LIMIT = -9         /* a fixed capacity of the library was exceeded           */
+} dnxcu_status;
+
+/* Human readable name of a status code (static string). */
+DNXCU_API const char *dnxcu_status_string(int status);
+/* cudaError_t of the most recent failing CUDA call on this thread (0 if none). */
+DNXCU_API int dnxcu_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------
+ * Device capabilities.
+ * Stands in for denox::DeviceInfo filled by query_driver_device_info
+ * (device_info/src/denox/device_info/DeviceInfo.hpp:12-20), which the variant
+ * generators read to prune their configuration space
+ * (compiler/src/denox/compiler/implement/shaders/conv/DirectConvShaderCM.cpp:19-28).
+ * ---------------------------------------------------------------------- */
+typedef struct dnxcu_caps {
+  int32_t device;
+  int32_t cc_major, cc_minor;
+  int32_t sm_count;
+  int32_t max_threads_per_block;
+  int32_t tmem_columns; /* tensor memory columns per SM (512 on sm_100)  */
+  int32_t tcgen05;      /* 1 when the tcgen05/TMEM conv variants can run */
+  int32_t reserved;
+  uint64_t smem_per_block_optin; /* bytes */
+  uint64_t l2_bytes;
+  uint64_t global_bytes;
+  char name[64];
+} dnxcu_caps;
+
+DNXCU_API int dnxcu_get_device_caps(int device, dnxcu_caps *caps);
+
+/* ------------------------------------------------------------------------
+ * Kernel variants.
+ * A variant is what an IShader configuration is in the reference
+ * (compiler/src/denox/compiler/implement/shaders/IShader.hpp:33-71): one
+ * kernel family with one fixed set of tuning parameters.  `config` uses the
+ * reference's KEY=VAL#KEY=VAL spelling (DirectConvShaderCM.cpp:690-694).
+ * ---------------------------------------------------------------------- */
+typedef enum dnxcu_op {
+  DNXCU_OP_CONV3X3 = 1,    /* direct_conv_cm.comp / concat_conv_cm.comp / direct_conv.comp */
+  DNXCU_OP_MAXPOOL2X2 = 2, /* basic_pool.comp      */
+  DNXCU_OP_UPSAMPLE2X = 3, /* basic_upsample.comp  */
+  DNXCU_OP_CONCAT = 4,     /* copy_transform.comp  */
+  DNXCU_OP_RELU = 5        /* basic_activation.comp */
+} dnxcu_op;
+
+/* dispatch flags (conv only unless noted) */
+#define DNXCU_F_RELU 0x01u        /* max(0, x) on the finished sum                          */
+#define DNXCU_F_BIAS 0x02u        /* dispatch.bias holds c_out binary16 values              */
+#define DNXCU_F_UP2X_A 0x04u      /* operand a is (H/2)x(W/2), read through src = dst/2      */
+#define DNXCU_F_POOL_OUT 0x08u    /* also write the 2x2 max pooled result to out_pool       */
+#define DNXCU_F_NO_FULL_OUT 0x10u /* with POOL_OUT: do not write the full resolution output */
+
+typedef struct dnxcu_variant_desc {
+  int32_t id;          /* index in the table, stable within one build of the library */
+  int32_t op;          /* dnxcu_op */
+  const char *family;  /* e.g. "direct-conv-tc" (names follow the reference's shaders) */
+  const char *config;  /* KEY=VAL#KEY=VAL */
+  uint32_t allowed_flags; /* dispatch flags this variant implements */
+  int32_t needs_tcgen05;  /* 1: requires dnxcu_caps.tcgen05 */
+  int32_t c_align;        /* operand channel counts must be multiples of this, or 1 */
+  int32_t k_align;        /* output channel count must be a multiple of this, or 1  */
+  int32_t max_c_out;
+  int32_t reserved;
+} dnxcu_variant_desc;
+
+/* Registration list; stands in for get_all_shaders
+ * (compiler/src/denox/compiler/implement/shaders/shaders.cpp:16-50). */
+DNXCU_API int dnxcu_variant_count(void);
+DNXCU_API const dnxcu_variant_desc *dnxcu_variant(int id);
+/* First variant whose family and config match exactly, or DNXCU_E_BAD_ARG. */
+DNXCU_API int dnxcu_find_variant(const char *family, const char *config);
+/* SHA-256 of (family, config, kernel source revision) as 64 hex digits plus
+ * NUL: the identity a benchmark database keys on.  Stands in for
+ * GlslCompilerInstance::fast_sha256 (spirv/src/denox/glsl/GlslCompilerInstance.hpp:73-79). */
+DNXCU_API int dnxcu_variant_sha256(int id, char out_hex[65]);
+
+/* ------------------------------------------------------------------------
+ * One dispatch.
+ * Stands in for ComputeDispatch
+ * (compiler/src/denox/compiler/implement/ComputeDispatch.hpp:29-40) and its
+ * run-time form InstanceDispatch (runtime/src/denox/runtime/instance.hpp:13-21).
+ * pc[] keeps the reference's push constant block {IN_W, IN_H}
+ * (DirectConvShaderCM.cpp:628-630): the extent of the tensor the kernel
+ * iterates over — the output resolution for a conv, the input resolution for
+ * pool / upsample / concat / relu.  Channel counts, which the reference bakes
+ * into the shader as #defines, are plain fields.
+ * Pointers follow the reference's binding order: inputs, outputs, parameters.
+ * ---------------------------------------------------------------------- */
+typedef struct dnxcu_dispatch {
+  int32_t variant;
+  uint32_t flags;
+  uint32_t pc[2]; /* IN_W, IN_H */
+  int32_t c_a;    /* channels of operand a */
+  int32_t c_b;    /* channels of operand b (concat second operand), 0 if none */
+  int32_t c_out;  /* output channels (conv); ignored otherwise */
+  int32_t reserved;
+  const void *in_a;
+  const void *in_b;
+  void *out;
+  void *out_pool;      /* (H/2)x(W/2)xc_out, conv with DNXCU_F_POOL_OUT */
+  const void *weights; /* blob made by dnxcu_prepare_weights for this variant */
+  const void *bias;    /* c_out binary16, or NULL */
+  /* Row band execution: one row (W x C binary16, or (W/2) x C for an operand
+   * read through UP2X_A) that sits directly above / below this band in the
+   * full image, already resident in this device's memory.  NULL = image
+   * border (zeros).  Order: a_top, a_bottom, b_top, b_bottom. */
+  const void *halo[4];
+  int32_t *device_status; /* optional device int: a kernel stores a non-zero code
+                             here when one of its bounded waits ran out */
+} dnxcu_dispatch;
+
+/* Checks the dispatch against the variant's rules without launching. */
+DNXCU_API int dnxcu_validate(const dnxcu_dispatch *d);
+/* Enqueues the kernel on `stream`.  Stands in for the vkCmdDispatch recorded in
+ * Instance::infer (runtime/src/denox/runtime/instance.cpp:367-396). */
+DNXCU_API int dnxcu_launch(const dnxcu_dispatch *d, void *stream);
+/* Grid the launch would use (wgX, wgY, wgZ of the reference's dispatch record). */
+DNXCU_API int dnxcu_grid(const dnxcu_dispatch *d, uint32_t grid[3]);
+/* Algorithmic cost of the dispatch, the reference's per dispatch metadata
+ * (DirectConvShaderCM.cpp:632-644): bytes read, bytes written, flops. */
+DNXCU_API int dnxcu_cost(const dnxcu_dispatch *d, uint64_t *bytes_read, uint64_t *bytes_written,
+                         uint64_t *flops);
+
+/* ------------------------------------------------------------------------
+ * Parameter re-layout (host side).
+ * Stands in for the lazy FilterTensor conversion a conv variant registers with
+ * OpImpl::createParameter (DirectConvShaderCM.cpp:595-619,
+ * ConcatConvCMShader.cpp:832-873; index formulas
+ * common/src/denox/memory/tensor/FilterLayout.hpp:36-118).
+ * Input: KCRS (= ONNX OIHW) binary16, C = c_a + c_b, R = S = 3.
+ * Call with out == NULL to get the blob size in *bytes.
+ * ---------------------------------------------------------------------- */
+DNXCU_API int dnxcu_prepare_weights(int variant, const void *kcrs_f16, int c_out, int c_a, int c_b,
+                                    void *out, size_t *bytes);
+
+/* float -> binary16 exactly as the reference converts fp32 model weights:
+ * mantissa truncated, sub-normal results flushed to zero
+ * (common/src/denox/memory/dtype/f16.cpp:6-20). */
+DNXCU_API uint16_t dnxcu_f16_from_float(float f);
+DNXCU_API float dnxcu_f16_to_float(uint16_t h);
+
+/* ------------------------------------------------------------------------
+ * Model / instance runtime.
+ * Stands in for runtime::Model::make, Instance::make, Instance::infer and
+ * Instance::bench (runtime/src/denox/runtime/model.hpp:107-168,
+ * instance.hpp:44-81).  The model is described as the un-fused node list an
+ * ONNX import produces (Conv, Relu, MaxPool, Resize-nearest-2x, Concat);
+ * dnxcu_model_create runs the fusion patterns and picks a variant per
+ * dispatch (from a benchmark database when one is given).
+ * ---------------------------------------------------------------------- */
+typedef enum dnxcu_node_kind {
+  DNXCU_NODE_CONV = 1,
+  DNXCU_NODE_RELU = 2,
+  DNXCU_NODE_MAXPOOL = 3,
+  DNXCU_NODE_UPSAMPLE = 4,
+  DNXCU_NODE_CONCAT = 5
+} dnxcu_node_kind;
+
+typedef struct dnxcu_node {
+  int32_t kind;     /* dnxcu_node_kind */
+  int32_t in0;      /* tensor id */
+  int32_t in1;      /* tensor id (concat) or -1 */
+  int32_t out;      /* tensor id */
+  int32_t c_out;    /* conv: output channels */
+  int32_t reserved;
+  const void *weights_kcrs; /* conv: host binary16 [c_out][c_in][3][3] */
+  const void *bias;         /* conv: host binary16 [c_out] or NULL */
+} dnxcu_node;
+
+typedef struct dnxcu_model_desc {
+  int32_t n_nodes;
+  int32_t n_tensors;
+  const dnxcu_node *nodes; /* topological order */
+  int32_t input_tensor;
+  int32_t input_channels;
+  int32_t output_tensor;
+  uint32_t options; /* DNXCU_OPT_* */
+} dnxcu_model_desc;
+
+#define DNXCU_OPT_NO_FUSE_ACTIVATION 0x1u /* reference --ffusion off (Options.hpp:16) */
+#define DNXCU_OPT_NO_FUSE_POOL 0x2u
+#define DNXCU_OPT_NO_FUSE_UPSAMPLE 0x4u
+#define DNXCU_OPT_NO_FUSE_CONCAT 0x8u
+#define DNXCU_OPT_NO_TCGEN05 0x10u /* reference --fcoopmat off */
+
+typedef struct dnxcu_model dnxcu_model;
+typedef struct dnxcu_instance dnxcu_instance;
+typedef struct dnxcu_db dnxcu_db;
+
+/* db may be NULL: variants are then picked by a fixed preference order. */
+DNXCU_API int dnxcu_model_create(const dnxcu_model_desc *desc, const dnxcu_db *db, int device,
+                                 dnxcu_model **out);
+DNXCU_API void dnxcu_model_destroy(dnxcu_model *m);
+DNXCU_API int dnxcu_model_dispatch_count(const dnxcu_model *m);
+
+/* Row band of a taller image: band rows [row0, row0+rows) of image height
+ * image_h; (0, h, h) = whole image.  All three must be multiples of 16 when
+ * the band is a strict part of the image. */
+typedef struct dnxcu_band {
+  int32_t image_h, row0, rows;
+} dnxcu_band;
+
+DNXCU_API int dnxcu_instance_create(const dnxcu_model *m, int height, int width,
+                                    const dnxcu_band *band, dnxcu_instance **out);
+DNXCU_API void dnxcu_instance_destroy(dnxcu_instance *inst);
+
+/* Host in, host out, synchronous — the contract of Instance::infer
+ * (instance.hpp:59; instance.cpp:322-430): input is H x W x C_in binary16,
+ * output H x W x C_out binary16, tightly packed. */
+DNXCU_API int dnxcu_instance_infer(dnxcu_instance *inst, const void *host_in, void *host_out);
+/* Device resident form: input/output are device pointers, work is enqueued on
+ * `stream`, nothing is synchronised. */
+DNXCU_API int dnxcu_instance_enqueue(dnxcu_instance *inst, const void *dev_in, void *dev_out,
+                                     void *stream);
+/* Device pointer and shape of any tensor of the instance after a run (for per
+ * layer parity checks): returns the device pointer in *ptr. */
+DNXCU_API int dnxcu_instance_tensor(const dnxcu_instance *inst, int tensor_id, void **ptr,
+                                    int *h, int *w, int *c);
+
+typedef struct dnxcu_dispatch_info {
+  char name[48];   /* reference style dispatch name, e.g. "direct-conv-tc+relu+pool" */
+  int32_t variant;
+  int32_t src_node; /* first node of the model this dispatch covers */
+  uint32_t grid[3];
+  uint32_t flags;
+  uint64_t bytes_read, bytes_written, flops;
+  float ms; /* filled by dnxcu_instance_bench */
+  int32_t h, w, c_a, c_b, c_out;
+  int32_t out_tensor;
+} dnxcu_dispatch_info;
+
+DNXCU_API int dnxcu_instance_dispatch_info(const dnxcu_instance *inst, int i,
+                                           dnxcu_dispatch_info *info);
+/* `warmup` untimed passes, then `iters` passes with a CUDA event pair around
+ * every dispatch; info[i].ms = mean per dispatch.  Stands in for
+ * Instance::bench (instance.cpp:432-654: 100 warm-up passes, one timed pass). */
+DNXCU_API int dnxcu_instance_bench(dnxcu_instance *inst, int warmup, int iters,
+                                   dnxcu_dispatch_info *info, int n_info, float *total_ms);
+
+/* Halo rows of a row band instance.  For every conv dispatch the instance
+ * keeps, per operand, one row above and one row below the band.  These calls
+ * expose them so that a caller (NCCL, peer copies, or a test on one device)
+ * can move rows between neighbouring bands between dispatches.
+ *   dnxcu_instance_halo_count: number of exchange points (one per conv operand)
+ *   dnxcu_instance_halo: for exchange point e: the dispatch index it precedes,
+ *     device pointers of this band's own first/last row of that operand
+ *     (send_top / send_bottom), the slabs the neighbour rows must land in
+ *     (recv_top / recv_bottom) and the row size in bytes. */
+typedef struct dnxcu_halo_point {
+  int32_t before_dispatch;
+  int32_t tensor;
+  const void *send_top, *send_bottom;
+  void *recv_top, *recv_bottom;
+  uint64_t row_bytes;
+} dnxcu_halo_point;
+DNXCU_API int dnxcu_instance_halo_count(const dnxcu_instance *inst);
+DNXCU_API int dnxcu_instance_halo(const dnxcu_instance *inst, int e, dnxcu_halo_point *p);
+/* Runs dispatches [first, last) on `stream` (row band callers interleave this
+ * with their halo exchange). */
+DNXCU_API int dnxcu_instance_enqueue_range(dnxcu_instance *inst, int first, int last, void *stream);
+/* Copies the band's input into the instance's input tensor / the output out. */
+DNXCU_API int dnxcu_instance_io(const dnxcu_instance *inst, void **dev_in, void **dev_out);
+
+/* ------------------------------------------------------------------------
+ * Benchmark database.
+ * Stands in for denox::Db (database/src/denox/db/Db.hpp:15-76) and the
+ * sampling loop of runtime::Db::bench (runtime/src/denox/runtime/db.cpp:665-868).
+ * Key = (variant sha-256, push constants, channel counts, flags, grid); value
+ * = sample count, mean and standard deviation of the latency in ms.
+ * ---------------------------------------------------------------------- */
+DNXCU_API int dnxcu_db_open(const char *path, dnxcu_db **out); /* missing file = empty db */
+DNXCU_API void dnxcu_db_close(dnxcu_db *db);
+DNXCU_API int dnxcu_db_size(const dnxcu_db *db);
+/* Adds every (dispatch, variant) candidate of the model at H x W that is not
+ * in the database yet; returns the number added (denox::populate,
+ * compiler/src/denox/compiler/populate.cpp:23-256). */
+DNXCU_API int dnxcu_db_populate(dnxcu_db *db, const dnxcu_model_desc *desc, int height, int width,
+                                int device);
+/* Samples un-converged entries until n >= min_samples and
+ * sem / mean <= max_relative_error, coldest first then largest relative error
+ * (db.cpp:71-175, 630-649); writes back atomically when done. */
+DNXCU_API int dnxcu_db_bench(dnxcu_db *db, int device, int min_samples, double max_relative_error,
+                             int max_rounds);
+DNXCU_API int dnxcu_db_atomic_writeback(dnxcu_db *db); /* tmp file + rename (Db.cpp:270-506) */
+/* Latency in ms of the entry matching the dispatch, or DNXCU_E_BAD_ARG when
+ * absent / never sampled (Db::query_dispatch_latency). */
+DNXCU_API int dnxcu_db_query(const dnxcu_db *db, const dnxcu_dispatch *d, double *mean_ms,
+                             double *std_ms, int *samples);
+DNXCU_API int dnxcu_db_add_result(dnxcu_db *db, const dnxcu_dispatch *d, const double *samples_ms,
+                                  int n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DNXCU_H */

@@ -1,0 +1,118 @@
+"""Generates the golden fixtures of tests/golden/ with PyTorch on CPU.
+
+The reference's own tests define correctness as agreement with PyTorch's
+forward pass (test/__init__.py:84-97 of the reference: conv / relu / max_pool2d
+/ interpolate(nearest) / cat), so PyTorch is the generator here.  Convolutions
+are evaluated in float32 on binary16 inputs and rounded to binary16 after every
+layer.  Inputs and weights come from denox_b200.rng (seeded), so only outputs
+are stored.
+
+    python tests/golden/make_golden.py
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+from denox_b200 import nets, rng  # noqa: E402
+
+CONV, RELU, MAXPOOL, UPSAMPLE, CONCAT = 1, 2, 3, 4, 5
+
+
+def t_in(x):  # HWC binary16 -> 1CHW float32
+    return torch.from_numpy(np.asarray(x, dtype=np.float32)).permute(2, 0, 1)[None]
+
+
+def t_out(y):  # 1CHW float32 -> HWC binary16
+    return y[0].permute(1, 2, 0).contiguous().numpy().astype(np.float16)
+
+
+def run_torch(net, x):
+    t = {net.input_tensor: t_in(x)}
+    half = lambda v: v.half().float()  # one rounding to binary16 per layer
+    for nd in net.nodes:
+        if nd.kind == CONV:
+            w = torch.from_numpy(nd.weights.astype(np.float32))
+            b = None if nd.bias is None else torch.from_numpy(nd.bias.astype(np.float32))
+            t[nd.out] = half(F.conv2d(t[nd.in0], w, b, padding=1))
+        elif nd.kind == RELU:
+            t[nd.out] = F.relu(t[nd.in0])
+        elif nd.kind == MAXPOOL:
+            t[nd.out] = F.max_pool2d(t[nd.in0], 2, 2)
+        elif nd.kind == UPSAMPLE:
+            t[nd.out] = F.interpolate(t[nd.in0], scale_factor=2, mode="nearest")
+        elif nd.kind == CONCAT:
+            t[nd.out] = torch.cat((t[nd.in0], t[nd.in1]), 1)
+    return {k: t_out(v) for k, v in t.items()}
+
+
+# (name, H, W, Ca, Cb, K, relu, bias, up_a): single layer cases; channel counts follow
+# the reference's test list (test/system/test_conv.py) and the benchmark networks
+CONV_CASES = [
+    ("c3_k16", 20, 36, 3, 0, 16, True, False, False),
+    ("c9_k32", 16, 40, 9, 0, 32, True, False, False),
+    ("c32_k32", 24, 150, 32, 0, 32, True, True, False),
+    ("c16_k3", 18, 34, 16, 0, 3, False, False, False),
+    ("c67_k24", 10, 22, 67, 0, 24, True, True, False),
+    ("c48_k64", 12, 20, 48, 0, 64, True, False, False),
+    ("cat32_16_k16", 16, 32, 32, 16, 16, True, False, True),
+    ("cat96_80_k112", 8, 16, 96, 80, 112, True, False, True),
+    ("cat64_9_k64", 12, 140, 64, 9, 64, True, False, True),
+    ("cat16_8_k8", 10, 12, 16, 8, 8, False, True, False),
+]
+
+
+def conv_case_tensors(case):
+    name, h, w, ca, cb, k, relu, bias, up = case
+    seed = 5000 + sum(name.encode())
+    ha, wa = (h // 2, w // 2) if up else (h, w)
+    a = rng.to_f16(rng.uniform(seed, ha * wa * ca, -1.0, 1.0)).reshape(ha, wa, ca)
+    b = rng.to_f16(rng.uniform(seed + 1, h * w * cb, -1.0, 1.0)).reshape(h, w, cb) if cb else None
+    wt = rng.he_normal_weights(seed + 2, k, ca + cb)
+    bs = rng.to_f16(rng.uniform(seed + 3, k, -0.5, 0.5)) if bias else None
+    return a, b, wt, bs
+
+
+def conv_case_torch(case):
+    name, h, w, ca, cb, k, relu, bias, up = case
+    a, b, wt, bs = conv_case_tensors(case)
+    x = t_in(a)
+    if up:
+        x = F.interpolate(x, scale_factor=2, mode="nearest")
+    if b is not None:
+        x = torch.cat((x, t_in(b)), 1)
+    y = F.conv2d(x, torch.from_numpy(wt.astype(np.float32)),
+                 None if bs is None else torch.from_numpy(bs.astype(np.float32)), padding=1)
+    if relu:
+        y = F.relu(y)
+    return t_out(y)
+
+
+def main():
+    torch.set_num_threads(4)
+    out = {}
+    for case in CONV_CASES:
+        out["conv/" + case[0]] = conv_case_torch(case)
+    tiny = nets.tiny_unet()
+    res = run_torch(tiny, nets.tiny_input(1000, 128, 128))
+    out["tiny/out"] = res[tiny.output_tensor]
+    tinyb = nets.tiny_unet(bias=True)
+    res = run_torch(tinyb, nets.tiny_input(1001, 48, 80))
+    out["tiny_bias/out"] = res[tinyb.output_tensor]
+    oidn = nets.oidn_unet()
+    res = run_torch(oidn, nets.oidn_input(1000, 32, 48))
+    out["oidn_32x48/out"] = res[oidn.output_tensor]
+    for name in ("enc_conv1", "enc_conv4", "dec_conv4a", "dec_conv1a"):
+        nd = next(n for n in oidn.nodes if n.name == name + ".relu")
+        out[f"oidn_32x48/{name}"] = res[nd.out]
+    path = os.path.join(HERE, "golden.npz")
+    np.savez_compressed(path, **out)
+    print(path, os.path.getsize(path), "bytes", len(out), "arrays")
+
+
+if __name__ == "__main__":
+    main()

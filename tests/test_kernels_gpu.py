@@ -1,0 +1,142 @@
+"""Per kernel parity on the GPU, through the C ABI, against the CPU oracle and the
+PyTorch generated golden fixtures.  Tolerance: |d| <= 2e-2 + 1e-2 |ref| per element
+against the binary16-accumulating oracle (the stand-in for the reference's own
+arithmetic); against the fp32-accumulating oracle the kernels (fp32 accumulation,
+one rounding) must agree to one binary16 ulp."""
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+
+from conftest import assert_close
+from denox_b200 import lib, nets, rng
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+spec = importlib.util.spec_from_file_location("make_golden", os.path.join(HERE, "golden", "make_golden.py"))
+mg = importlib.util.module_from_spec(spec)
+spec.loader.exec_module(mg)
+GOLD = np.load(os.path.join(HERE, "golden", "golden.npz"))
+
+CONV_VARIANTS = [v["id"] for v in lib.variants() if v["op"] == lib.OP_CONV3X3]
+
+
+def one_ulp(got, ref):
+    g, r = got.astype(np.float32), ref.astype(np.float32)
+    return np.abs(g - r) <= np.maximum(np.abs(r) * 2.0 ** -10, 2.0 ** -14) * 1.01
+
+
+def supports(variant, flags, ca, cb, k, h, w):
+    import ctypes as C
+    d = lib.Dispatch()
+    d.variant, d.flags, d.c_a, d.c_b, d.c_out = variant, flags, ca, cb, k
+    d.pc[0], d.pc[1] = w, h
+    d.in_a = d.out = d.weights = d.bias = 0x1000
+    d.in_b = 0x1000 if cb else None
+    d.out_pool = 0x1000
+    return lib.L.dnxcu_validate(C.byref(d)) == 0
+
+
+@pytest.mark.parametrize("variant", CONV_VARIANTS)
+@pytest.mark.parametrize("case", mg.CONV_CASES, ids=[c[0] for c in mg.CONV_CASES])
+def test_conv_against_oracle_and_golden(variant, case):
+    from gpu_util import run_conv
+    name, h, w, ca, cb, k, relu, bias, up = case
+    flags = (lib.F_RELU if relu else 0) | (lib.F_BIAS if bias else 0) | (lib.F_UP2X_A if up else 0)
+    if not supports(variant, flags, ca, cb, k, h, w):
+        pytest.skip("variant does not take this dispatch")
+    a, b, wt, bs = mg.conv_case_tensors(case)
+    y, _ = run_conv(variant, a, wt, bs, relu=relu, b=b, up_a=up)
+    ref32 = oracle.conv3x3(a, wt, bs, relu=relu, mode=oracle.ACC_F32, b=b, up_a=up)
+    ref16 = oracle.conv3x3(a, wt, bs, relu=relu, mode=oracle.ACC_F16, b=b, up_a=up)
+    assert one_ulp(y, ref32).all(), (name, np.abs(y.astype(np.float32) - ref32.astype(np.float32)).max())
+    assert_close(y, ref16, f"{name} vs acc=f16 oracle", max_violation_fraction=1e-3)
+    assert_close(y, GOLD["conv/" + name], f"{name} vs PyTorch golden")
+
+
+@pytest.mark.parametrize("variant", CONV_VARIANTS)
+@pytest.mark.parametrize("shape", [(16, 128, 32, 32), (18, 130, 16, 48), (34, 300, 48, 64), (16, 16, 64, 80),
+                                   (2, 2, 16, 16), (6, 1922 // 2 * 2, 32, 32)])
+def test_conv_pool_epilogue(variant, shape):
+    """conv + relu + 2x2 max pool in one dispatch: single (pooled only) and dual output."""
+    from gpu_util import run_conv
+    h, w, c, k = shape
+    flags = lib.F_RELU | lib.F_POOL_OUT
+    if not supports(variant, flags, c, 0, k, h, w):
+        pytest.skip("variant does not take this dispatch")
+    a = rng.to_f16(rng.uniform(77 + h + w, h * w * c, -1, 1)).reshape(h, w, c)
+    wt = rng.he_normal_weights(78, k, c)
+    ref = oracle.conv3x3(a, wt, relu=True)
+    refp = oracle.maxpool2x2(ref)
+    y, yp = run_conv(variant, a, wt, relu=True, pool=True, full=True)
+    assert one_ulp(y, ref).all() and one_ulp(yp, refp).all()
+    # pooling commutes with rounding: the pooled tensor must be exactly the pool of the kernel's own full output
+    assert (yp == oracle.maxpool2x2(y)).all()
+    _, yp2 = run_conv(variant, a, wt, relu=True, pool=True, full=False)
+    assert (yp2 == yp).all()
+
+
+@pytest.mark.parametrize("variant", CONV_VARIANTS)
+def test_conv_row_band_with_halo_rows(variant):
+    """A band of a taller image plus halo rows gives bit-identical rows (row band multi-GPU path)."""
+    from gpu_util import run_conv
+    h, w, ca, cb, k = 32, 200, 32, 16, 32
+    flags = lib.F_RELU | lib.F_UP2X_A
+    if not supports(variant, flags, ca, cb, k, h, w):
+        pytest.skip("variant does not take this dispatch")
+    a = rng.to_f16(rng.uniform(91, (h // 2) * (w // 2) * ca, -1, 1)).reshape(h // 2, w // 2, ca)
+    b = rng.to_f16(rng.uniform(92, h * w * cb, -1, 1)).reshape(h, w, cb)
+    wt = rng.he_normal_weights(93, k, ca + cb)
+    full, _ = run_conv(variant, a, wt, relu=True, b=b, up_a=True)
+    ref = oracle.conv3x3(a, wt, relu=True, b=b, up_a=True)
+    assert one_ulp(full, ref).all()
+    # rows [16, 32): top halo = row 15 of the virtual upsampled a = source row 7, of b = row 15; bottom = image border
+    band, _ = run_conv(variant, a[8:16], wt, relu=True, b=b[16:32], up_a=True, halo=(a[7], None, b[15], None))
+    assert (band == full[16:32]).all()
+    band0, _ = run_conv(variant, a[0:8], wt, relu=True, b=b[0:16], up_a=True, halo=(None, a[8], None, b[16]))
+    assert (band0 == full[0:16]).all()
+
+
+@pytest.mark.parametrize("c", [8, 32, 48, 80, 3, 9, 67])
+def test_pool_upsample_concat_relu(c):
+    from gpu_util import run_mem
+    h, w = 34, 46
+    x = rng.to_f16(rng.normal(5 + c, h * w * c)).reshape(h, w, c)
+    y = rng.to_f16(rng.normal(6 + c, h * w * c)).reshape(h, w, c)
+    for v in lib.variants():
+        vec = v["config"] == "VEC=8"
+        if v["op"] == lib.OP_CONV3X3 or (vec and c % 8):
+            continue
+        if v["op"] == lib.OP_MAXPOOL2X2:
+            assert (run_mem(v["id"], x) == oracle.maxpool2x2(x)).all()
+        elif v["op"] == lib.OP_UPSAMPLE2X:
+            assert (run_mem(v["id"], x) == oracle.upsample2x(x)).all()
+        elif v["op"] == lib.OP_CONCAT:
+            assert (run_mem(v["id"], x, y) == oracle.concat(x, y)).all()
+        elif v["op"] == lib.OP_RELU:
+            assert (run_mem(v["id"], x) == oracle.relu(x)).all()
+
+
+def test_pool_odd_extent_floor():
+    from gpu_util import run_mem
+    x = rng.to_f16(rng.normal(3, 7 * 9 * 8)).reshape(7, 9, 8)
+    for vid in (6, 7):
+        assert (run_mem(vid, x) == oracle.maxpool2x2(x)).all()
+
+
+def test_launch_rejects_bad_dispatches_without_touching_the_device():
+    import ctypes as C
+    d = lib.Dispatch()
+    d.variant = 2
+    assert lib.L.dnxcu_launch(C.byref(d), None) == lib.E_BAD_ARG
+    d.variant = 999
+    assert lib.L.dnxcu_launch(C.byref(d), None) == lib.E_BAD_ARG
+    assert lib.L.dnxcu_launch(None, None) == lib.E_BAD_ARG
+
+
+def test_device_caps():
+    caps = lib.device_caps(0)
+    assert caps.sm_count > 0 and caps.cc_major == 10 and caps.tcgen05 == 1 and caps.tmem_columns == 512

@@ -1,0 +1,83 @@
+"""Whole network parity on the GPU through the model / instance runtime (host in,
+host out, like Instance::infer), free running and per tensor, against the CPU
+oracle and the golden fixtures."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import assert_close, error_report
+from denox_b200 import lib, nets
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+GOLD = np.load(os.path.join(HERE, "golden", "golden.npz"))
+
+
+def fetch(inst, tid):
+    from gpu_util import wrap
+    p, h, w, c = inst.tensor(tid)
+    return wrap(p, (h, w, c)).cpu().numpy()
+
+
+@pytest.mark.parametrize("options", [0, lib.OPT_NO_TCGEN05,
+                                     lib.OPT_NO_FUSE_POOL | lib.OPT_NO_FUSE_UPSAMPLE | lib.OPT_NO_FUSE_CONCAT
+                                     | lib.OPT_NO_FUSE_ACTIVATION])
+@pytest.mark.parametrize("which,shape,seed,key", [
+    ("tiny", (128, 128), 1000, "tiny/out"),
+    ("tiny_bias", (48, 80), 1001, "tiny_bias/out"),
+    ("oidn", (32, 48), 1000, "oidn_32x48/out"),
+])
+def test_network_matches_oracle_and_golden(which, shape, seed, key, options):
+    if which == "oidn":
+        net, x = nets.oidn_unet(), nets.oidn_input(seed, *shape)
+    else:
+        net, x = nets.tiny_unet(bias=(which == "tiny_bias")), nets.tiny_input(seed, *shape)
+    model = lib.Model(net, options=options)
+    inst = lib.Instance(model, *shape)
+    y = inst.infer(x)
+    y2 = inst.infer(x)  # second call replays the captured graph
+    assert (y == y2).all()
+    ref32 = oracle.run_network(net, x, oracle.ACC_F32)
+    ref16 = oracle.run_network(net, x, oracle.ACC_F16)
+    assert_close(y, ref32[net.output_tensor], f"{which} end to end vs acc=f32 oracle")
+    assert_close(y, ref16[net.output_tensor], f"{which} end to end vs acc=f16 oracle", max_violation_fraction=1e-3)
+    assert_close(y, GOLD[key], f"{which} end to end vs PyTorch golden")
+    # every materialised tensor, free running
+    for info in inst.dispatch_info():
+        tid = info.out_tensor
+        got = fetch(inst, tid)
+        rep = assert_close(got, ref32[tid], f"{which} tensor {tid} ({info.name.decode()})")
+        assert rep["max"] < 0.05
+    if options == 0:
+        n_conv = sum(1 for nd in net.nodes if nd.kind == nets.CONV)
+        assert model.dispatch_count() == n_conv  # pool / upsample / concat / relu all fused away
+    inst.close()
+    model.close()
+
+
+def test_oidn_larger_frame_properties():
+    """At a size the oracle still finishes in seconds: 96 x 256."""
+    net = nets.oidn_unet()
+    x = nets.oidn_input(1003, 96, 256)
+    model = lib.Model(net)
+    inst = lib.Instance(model, 96, 256)
+    y = inst.infer(x)
+    ref = oracle.run_network(net, x, oracle.ACC_F32)[net.output_tensor]
+    rep = assert_close(y, ref, "oidn 96x256")
+    print("oidn 96x256 end-to-end", rep)
+    infos, total = inst.bench(warmup=1, iters=2)
+    assert total > 0 and all(i.ms > 0 for i in infos)
+    inst.close()
+    model.close()
+
+
+def test_instance_rejects_unaligned_extent():
+    net = nets.oidn_unet()
+    model = lib.Model(net)
+    with pytest.raises(lib.DnxcuError) as e:
+        lib.Instance(model, 100, 100)  # not a multiple of 16: the reference pads such images first
+    assert e.value.status == lib.E_UNSUPPORTED
+    model.close()
