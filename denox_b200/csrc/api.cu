@@ -75,11 +75,11 @@ static const uint32_t CONV_ALL = CONV_BASE | DNXCU_F_POOL_OUT | DNXCU_F_NO_FULL_
 static const Variant kVariants[] = {
     // id, op, family, config, flags, tcgen05, c_align, k_align, max_c_out | kind, p0..p3
     {{0, DNXCU_OP_CONV3X3, "direct-conv", "ACC=f32#TILE=16x8#KT=32", CONV_BASE, 0, 1, 1, 65536, 0}, VK_CONV_DIRECT, 0, 0, 0, 0},
-    {{1, DNXCU_OP_CONV3X3, "direct-conv-tc", "R=1#SLOTS=8#W=resident", CONV_BASE, 1, 1, 1, 256, 0}, VK_CONV_TC, 1, 8, 0, 0},
-    {{2, DNXCU_OP_CONV3X3, "direct-conv-tc", "R=2#SLOTS=8#W=resident", CONV_ALL, 1, 1, 1, 256, 0}, VK_CONV_TC, 2, 8, 0, 0},
-    {{3, DNXCU_OP_CONV3X3, "direct-conv-tc", "R=4#SLOTS=10#W=resident", CONV_ALL, 1, 1, 1, 128, 0}, VK_CONV_TC, 4, 10, 0, 0},
-    {{4, DNXCU_OP_CONV3X3, "direct-conv-tc", "R=2#SLOTS=8#W=stream3", CONV_ALL, 1, 1, 1, 256, 0}, VK_CONV_TC, 2, 8, 1, 3},
-    {{5, DNXCU_OP_CONV3X3, "direct-conv-tc", "R=4#SLOTS=10#W=stream3", CONV_ALL, 1, 1, 1, 128, 0}, VK_CONV_TC, 4, 10, 1, 3},
+    {{1, DNXCU_OP_CONV3X3, "direct-conv-tc", "R=1#KG=1#W=resident", CONV_BASE, 1, 1, 1, 256, 0}, VK_CONV_TC, 1, 1, 0, 0},
+    {{2, DNXCU_OP_CONV3X3, "direct-conv-tc", "R=2#KG=1#W=resident", CONV_ALL, 1, 1, 1, 256, 0}, VK_CONV_TC, 2, 1, 0, 0},
+    {{3, DNXCU_OP_CONV3X3, "direct-conv-tc", "R=4#KG=1#W=resident", CONV_ALL, 1, 1, 1, 128, 0}, VK_CONV_TC, 4, 1, 0, 0},
+    {{4, DNXCU_OP_CONV3X3, "direct-conv-tc", "R=2#KG=1#W=stream3", CONV_ALL, 1, 1, 1, 256, 0}, VK_CONV_TC, 2, 1, 1, 3},
+    {{5, DNXCU_OP_CONV3X3, "direct-conv-tc", "R=2#KG=2#W=stream3", CONV_ALL, 1, 1, 1, 256, 0}, VK_CONV_TC, 2, 2, 1, 3},
     {{6, DNXCU_OP_MAXPOOL2X2, "basic-pool", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_POOL, 8, 0, 0, 0},
     {{7, DNXCU_OP_MAXPOOL2X2, "basic-pool", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_POOL, 1, 0, 0, 0},
     {{8, DNXCU_OP_UPSAMPLE2X, "basic-upsample", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_UPSAMPLE, 8, 0, 0, 0},

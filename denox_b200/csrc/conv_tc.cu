@@ -34,17 +34,21 @@
 // a CTA wide abort flag, stores a code to the dispatch's device_status word
 // and every role leaves its loop; TMEM is freed on that path too.
 #include "internal.h"
+#include <cuda.h>
 #include <stdlib.h>
+#include <string.h>
 
 namespace dnxcu {
 namespace {
 
 constexpr int STRIP = 128;        // pixels per MMA (M)
-constexpr int SLOT_PX = 130;      // pixels held per slot row (strip + 1 left + 1 right)
-constexpr int WH = 137;           // slot pixel pitch: chunk pitch = 137*16 B = 16 (mod 128) -> conflict free fills
+constexpr int SLOT_PX = 130;      // pixels used per slot row (strip + 1 left + 1 right)
+constexpr int WH = 132;           // slot pixel pitch = TMA box width: two chunks = 4224 B, a multiple of 128
 constexpr int CHUNK_PITCH = WH * 16;
 constexpr int HEADER_BYTES = 1024;
 constexpr int MAX_SLOTS = 16;
+constexpr int MAX_GROUPS = 4;
+constexpr int MAX_DEPTH = 8;      // input rows a producer thread keeps in flight
 constexpr int MAX_WST = 4;
 constexpr int N_PRODUCER = 128;
 constexpr int THREADS = 320;
@@ -70,9 +74,14 @@ struct Seg {
   int C;              // channels
   int nch;            // 8 channel chunks after padding C to a multiple of 16
   int up;
+  int tma;            // rows of this operand are fetched by TMA (tensor map below)
 };
 
 struct TcArgs {
+  // 4-D views of the operands for TMA: (8 channels, pixel x, 8 channel chunk, row y), so that a box of
+  // (8, 132, 2, 1) lands in shared memory as [chunk][pixel][8 halves] — the MMA's K major core matrix order
+  alignas(64) CUtensorMap tm_a;
+  alignas(64) CUtensorMap tm_b;
   Seg a, b;
   const __half *w;  // [9][nch_a + nch_b][N][8]
   const __half *bias;
@@ -83,8 +92,16 @@ struct TcArgs {
   int relu, pool, full_out;
   int RB, S, nstrips, nunits;
   int wstream, WST;
+  int G;                 // K groups: 1 = rolling row window; > 1 = every pass loads its rows once per group
+  int gc0[MAX_GROUPS];   // first 8 channel chunk of each group
+  int gch[MAX_GROUPS];   // chunks in each group (even)
+  int gmax;              // largest group
+  int D;                 // producer depth (rows in flight per thread)
+  int cpa;               // producer warps copy part of the rows (cp.async) besides TMA
   uint32_t tmem_cols;
   int desc_swap;  // debugging aid: exchange the two descriptor strides
+  long long *trace;  // debugging aid: per role time stamps of CTA 0 (nullptr = off)
+  int skip;       // debugging aid (timing only, results wrong): 1 no input loads, 2 no MMAs, 4 no output stores
 };
 
 // ---- PTX wrappers ---------------------------------------------------------
@@ -170,6 +187,26 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+// 4-D tiled TMA load, global -> shared, completion counted in bytes on an mbarrier.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], "
+      "[%6];" ::"r"(dst),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared memory matrix descriptor, no swizzle, K major:
@@ -186,8 +223,14 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   return *reinterpret_cast<uint32_t *>(&h);
 }
 
+// Debug time line: role `role` of CTA 0 stores clock64() at event `ev` of its n-th iteration.
+constexpr int TRACE_ITERS = 64, TRACE_EVENTS = 6;
+__device__ __forceinline__ void trace(const TcArgs &g, int role, int n, int ev) {
+  if (g.trace && blockIdx.x == 0 && n < TRACE_ITERS) g.trace[(role * TRACE_ITERS + n) * TRACE_EVENTS + ev] = clock64();
+}
+
 struct Unit {
-  int x0, y0, rows_out, npass, rows_in;
+  int x0, y0, npass;
 };
 template <int R>
 __device__ __forceinline__ Unit unit_of(const TcArgs &g, int u) {
@@ -198,54 +241,189 @@ __device__ __forceinline__ Unit unit_of(const TcArgs &g, int u) {
   int rows = g.H - t.y0;
   if (rows > g.RB) rows = g.RB;
   t.npass = (rows + R - 1) / R;
-  t.rows_out = t.npass * R;
-  t.rows_in = t.rows_out + 2;
   return t;
 }
 
-// Fills one slot with input row iy of the strip starting at x0 (pixels x0-1 .. x0+128).
-__device__ __forceinline__ void load_row(const TcArgs &g, uint32_t slot_addr, int iy, int x0, int tid) {
+__device__ __forceinline__ void cp_async_wait_dyn(int n) {
+  switch (n) {
+    case 0: cp_async_wait<0>(); break;
+    case 1: cp_async_wait<1>(); break;
+    case 2: cp_async_wait<2>(); break;
+    case 3: cp_async_wait<3>(); break;
+    case 4: cp_async_wait<4>(); break;
+    case 5: cp_async_wait<5>(); break;
+    case 6: cp_async_wait<6>(); break;
+    default: cp_async_wait<7>(); break;
+  }
+}
+
+// True when TMA fetches this operand's part of input row iy (otherwise the
+// producer warps copy it): the operand has a tensor map and the row is not one
+// of the separately stored halo rows of a row band.
+__device__ __forceinline__ bool row_by_tma(const TcArgs &g, const Seg &s, int iy) {
+  if (!s.tma) return false;
+  if (iy == -1 && s.top) return false;
+  if (iy == g.H && s.bot) return false;
+  return true;
+}
+
+// TMA part of one ring entry: chunks [c_lo, c_hi) of input row iy, pixels x0-1 ..
+// x0+130, two 8 channel chunks per copy.  Rows and pixels outside the tensor
+// are zero filled by the copy engine (= the convolution's zero padding).
+// Returns the bytes that will land.
+template <bool ISSUE>
+__device__ __forceinline__ uint32_t tma_row(const TcArgs &g, uint32_t slot_addr, int iy, int x0, int c_lo, int c_hi,
+                                            uint32_t bar) {
+  uint32_t bytes = 0;
   int chbase = 0;
 #pragma unroll 1
   for (int sg = 0; sg < 2; ++sg) {
     const Seg &s = sg ? g.b : g.a;
     if (s.nch == 0) continue;
-    const int Ws = s.up ? g.W >> 1 : g.W;
-    const __half *row = nullptr;
-    if (iy < 0) row = (iy == -1) ? s.top : nullptr;
-    else if (iy >= g.H) row = (iy == g.H) ? s.bot : nullptr;
-    else row = s.ptr + (long long)(s.up ? iy >> 1 : iy) * Ws * s.C;
-    const int items = SLOT_PX * s.nch;
-    const bool vec = (s.C & 7) == 0;
-    const int nchv = s.C >> 3;
+    const int lo = max(c_lo - chbase, 0), hi = min(c_hi - chbase, s.nch);
+    if (hi > lo && row_by_tma(g, s, iy)) {
+      const void *tm = sg ? (const void *)&g.tm_b : (const void *)&g.tm_a;
 #pragma unroll 1
-    for (int i = tid; i < items; i += N_PRODUCER) {
-      const int px = i / s.nch, ch = i - px * s.nch;
-      const int ix = x0 - 1 + px;
-      const bool inb = row != nullptr && ix >= 0 && ix < g.W;
-      const uint32_t dst = slot_addr + (uint32_t)((chbase + ch) * CHUNK_PITCH + px * 16);
-      const long long poff = (long long)(s.up ? ix >> 1 : ix) * s.C + ch * 8;
-      if (vec) {
-        const bool ok = inb && ch < nchv;
-        cp_async16(dst, ok ? (const void *)(row + poff) : (const void *)s.ptr, ok ? 16u : 0u);
-      } else {
-        uint32_t v[4] = {0u, 0u, 0u, 0u};
-        if (inb) {
-          const unsigned short *p = reinterpret_cast<const unsigned short *>(row + poff);
+      for (int c = lo; c < hi; c += 2) {
+        if (ISSUE) tma_load_4d(slot_addr + (uint32_t)((chbase + c - c_lo) * CHUNK_PITCH), tm, 0, x0 - 1, c, iy, bar);
+        bytes += 2u * CHUNK_PITCH;
+      }
+    }
+    chbase += s.nch;
+  }
+  return bytes;
+}
+
+// Producer warp part of one ring entry: the operands (or halo rows) TMA does not
+// cover, with 16 byte cp.async (2 byte loads for channel counts that are not a
+// multiple of 8).  Chunk c of the operand list lands at slot chunk c - c_lo.
+__device__ __forceinline__ void load_row(const TcArgs &g, uint32_t slot_addr, int iy, int x0, int tid, int c_lo,
+                                         int c_hi) {
+  int chbase = 0;
+#pragma unroll 1
+  for (int sg = 0; sg < 2; ++sg) {
+    const Seg &s = sg ? g.b : g.a;
+    if (s.nch == 0) continue;
+    const int lo = max(c_lo - chbase, 0), hi = min(c_hi - chbase, s.nch);
+    if (hi > lo && !row_by_tma(g, s, iy)) {
+      const int n = hi - lo;
+      const int Ws = s.up ? g.W >> 1 : g.W;
+      const __half *row = nullptr;
+      if (iy < 0) row = (iy == -1) ? s.top : nullptr;
+      else if (iy >= g.H) row = (iy == g.H) ? s.bot : nullptr;
+      else row = s.ptr + (long long)(s.up ? iy >> 1 : iy) * Ws * s.C;
+      const int items = SLOT_PX * n;
+      const bool vec = (s.C & 7) == 0;
+      const int nchv = s.C >> 3;
+      const uint32_t dst0 = slot_addr + (uint32_t)((chbase + lo - c_lo) * CHUNK_PITCH);
+#pragma unroll 1
+      for (int i = tid; i < items; i += N_PRODUCER) {
+        const int px = i / n, ch = i - px * n;
+        const int ix = x0 - 1 + px;
+        const bool inb = row != nullptr && ix >= 0 && ix < g.W;
+        const uint32_t dst = dst0 + (uint32_t)(ch * CHUNK_PITCH + px * 16);
+        const long long poff = (long long)(s.up ? ix >> 1 : ix) * s.C + (lo + ch) * 8;
+        if (vec) {
+          const bool ok = inb && (lo + ch) < nchv;
+          cp_async16(dst, ok ? (const void *)(row + poff) : (const void *)s.ptr, ok ? 16u : 0u);
+        } else {
+          uint32_t v[4] = {0u, 0u, 0u, 0u};
+          if (inb) {
+            const unsigned short *p = reinterpret_cast<const unsigned short *>(row + poff);
 #pragma unroll
-          for (int e = 0; e < 8; ++e)
-            if (ch * 8 + e < s.C) v[e >> 1] |= (uint32_t)__ldg(p + e) << ((e & 1) * 16);
+            for (int e = 0; e < 8; ++e)
+              if ((lo + ch) * 8 + e < s.C) v[e >> 1] |= (uint32_t)__ldg(p + e) << ((e & 1) * 16);
+          }
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                       "r"(v[3])
+                       : "memory");
         }
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
-                     : "memory");
       }
     }
     chbase += s.nch;
   }
 }
 
+// Epilogue of NC accumulator columns [c0, c0 + NC) for RSTEP output rows of one
+// pixel: TMEM -> registers, (+bias), (ReLU), binary16, stores; with RSTEP == 2
+// optionally the 2x2 max pool (vertical max in registers, horizontal max with
+// the neighbouring lane; max commutes with the rounding, basic_pool.comp:44-82).
+template <int NC, int RSTEP>
+__device__ __forceinline__ void epilogue_block(const TcArgs &g, uint32_t t0, uint32_t t1, int c0, int x, int y,
+                                               bool xin, int lane) {
+  uint32_t v0[NC], v1[RSTEP == 2 ? NC : 1];
+  if constexpr (NC == 32) {
+    tc_ld32(t0 + (uint32_t)c0, v0);
+    if constexpr (RSTEP == 2) tc_ld32(t1 + (uint32_t)c0, v1);
+  } else {
+    tc_ld16(t0 + (uint32_t)c0, v0);
+    if constexpr (RSTEP == 2) tc_ld16(t1 + (uint32_t)c0, v1);
+  }
+  tc_wait_ld();
+  const bool vec_out = (g.K & 7) == 0;
+  const bool row1 = RSTEP == 2 && (y + 1 < g.H);
+  const bool do_pool = RSTEP == 2 && g.pool;
+  __half *o0 = g.out + ((long long)y * g.W + x) * g.K + c0;
+  __half *o1 = o0 + (long long)g.W * g.K;
+  __half *op = g.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (x >> 1)) * g.K + c0;
+  const bool st_full = g.full_out && xin && !(g.skip & 4);
+  const bool st_pool = do_pool && xin && !(lane & 1) && row1;
+#pragma unroll
+  for (int j8 = 0; j8 < NC; j8 += 8) {
+    float f0[8], f1[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float bj = 0.0f;
+      if (g.bias && c0 + j8 + j < g.K) bj = __half2float(__ldg(g.bias + c0 + j8 + j));
+      f0[j] = __uint_as_float(v0[j8 + j]) + bj;
+      if (g.relu) f0[j] = fmaxf(f0[j], 0.0f);
+      if constexpr (RSTEP == 2) {
+        f1[j] = __uint_as_float(v1[j8 + j]) + bj;
+        if (g.relu) f1[j] = fmaxf(f1[j], 0.0f);
+      } else {
+        f1[j] = 0.0f;
+      }
+    }
+    const bool whole = vec_out && (c0 + j8 + 8 <= g.K);
+    if (st_full) {
+      if (whole) {
+        *reinterpret_cast<uint4 *>(o0 + j8) =
+            make_uint4(pack_h2(f0[0], f0[1]), pack_h2(f0[2], f0[3]), pack_h2(f0[4], f0[5]), pack_h2(f0[6], f0[7]));
+        if (row1)
+          *reinterpret_cast<uint4 *>(o1 + j8) =
+              make_uint4(pack_h2(f1[0], f1[1]), pack_h2(f1[2], f1[3]), pack_h2(f1[4], f1[5]), pack_h2(f1[6], f1[7]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (c0 + j8 + j < g.K) {
+            o0[j8 + j] = __float2half_rn(f0[j]);
+            if (row1) o1[j8 + j] = __float2half_rn(f1[j]);
+          }
+      }
+    }
+    if (do_pool) {
+      float pm[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float vmax = fmaxf(f0[j], f1[j]);
+        pm[j] = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1));
+      }
+      if (st_pool) {
+        if (whole) {
+          *reinterpret_cast<uint4 *>(op + j8) =
+              make_uint4(pack_h2(pm[0], pm[1]), pack_h2(pm[2], pm[3]), pack_h2(pm[4], pm[5]), pack_h2(pm[6], pm[7]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (c0 + j8 + j < g.K) op[j8 + j] = __float2half_rn(pm[j]);
+        }
+      }
+    }
+  }
+}
+
 template <int R>
-__global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const TcArgs g) {
+__global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__ TcArgs g) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -254,16 +432,21 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const TcArgs g) {
   auto bar = [&](int i) { return sbase + (uint32_t)i * 8u; };
 
   const int nch = g.a.nch + g.b.nch;
-  const uint32_t wtap_bytes = (uint32_t)nch * g.N * 16u;
+  const uint32_t wtap_bytes = (uint32_t)nch * g.N * 16u;        // one tap, all chunks
+  const uint32_t wstage_bytes = (uint32_t)g.gmax * g.N * 16u;   // one (tap, group) block
   const uint32_t w_addr = sbase + HEADER_BYTES;
-  const uint32_t wregion = g.wstream ? wtap_bytes * g.WST : wtap_bytes * 9u;
-  const uint32_t slot_bytes = (uint32_t)nch * CHUNK_PITCH;
+  const uint32_t wregion = g.wstream ? wstage_bytes * g.WST : wtap_bytes * 9u;
+  const uint32_t slot_bytes = (uint32_t)g.gmax * CHUNK_PITCH;
   const uint32_t slots_addr = w_addr + ((wregion + 127u) & ~127u);
+  const int S = g.S;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    // a slot is full when the TMA bytes have landed (one arrival with the byte count by the
+    // issuing thread) and, when producer warps copy part of the rows, those four warps arrived
+    const uint32_t full_count = g.cpa ? 5u : 1u;
     for (int i = 0; i < MAX_SLOTS; ++i) {
-      mbar_init(bar(BAR_FULL + i), 4);
+      mbar_init(bar(BAR_FULL + i), full_count);
       mbar_init(bar(BAR_EMPTY + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -288,70 +471,123 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const TcArgs g) {
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
 
+  // Ring bookkeeping shared by the producer and the MMA issuer: entry number `pos`
+  // (0, 1, 2, ... in load order) lives in slot pos % S with phase (pos / S) & 1.
+  // G == 1: the entries of a unit are its input rows y0-1 .. y0+rows, loaded once
+  //         and reused by up to three passes (rolling window).
+  // G  > 1: every (pass, group) loads its own R + 2 rows (no reuse across passes).
+
   if (warp == 0) {
     // ---------------- MMA issue ----------------
-    if (lane == 0) {
-      const uint32_t idesc = (1u << 4) | ((uint32_t)(g.N >> 3) << 17) | ((uint32_t)(STRIP >> 4) << 24);
-      const uint32_t a_lbo = g.desc_swap ? 128u : (uint32_t)CHUNK_PITCH;
-      const uint32_t a_sbo = g.desc_swap ? (uint32_t)CHUNK_PITCH : 128u;
-      const uint32_t b_lbo = g.desc_swap ? 128u : (uint32_t)g.N * 16u;
-      const uint32_t b_sbo = g.desc_swap ? (uint32_t)g.N * 16u : 128u;
-      const int nk16 = nch >> 1;
-      bool ok = true;
-      if (!g.wstream) ok = mbar_wait(bar(BAR_WRES), 0, abort_flag, g.status, 1);
-      int gbase = 0, gpass = 0, gw = 0;
-      for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
-        const Unit t = unit_of<R>(g, u);
-        int waited = 0;
-        for (int p = 0; ok && p < t.npass; ++p) {
-          const int need = p * R + R + 1;
-          while (ok && waited <= need) {
-            const int gg = gbase + waited;
-            ok = mbar_wait(bar(BAR_FULL + gg % g.S), (uint32_t)(gg / g.S) & 1u, abort_flag, g.status, 2);
-            ++waited;
+    // The whole warp walks the loop (uniform control flow keeps the descriptors in
+    // uniform registers); lane 0 alone issues the tcgen05 instructions.
+    const bool issuer = lane == 0;
+    const uint32_t idesc = (1u << 4) | ((uint32_t)(g.N >> 3) << 17) | ((uint32_t)(STRIP >> 4) << 24);
+    const uint32_t a_lbo = g.desc_swap ? 128u : (uint32_t)CHUNK_PITCH;
+    const uint32_t a_sbo = g.desc_swap ? (uint32_t)CHUNK_PITCH : 128u;
+    const uint32_t b_lbo = g.desc_swap ? 128u : (uint32_t)g.N * 16u;
+    const uint32_t b_sbo = g.desc_swap ? (uint32_t)g.N * 16u : 128u;
+    // descriptor = hi word (stride offset + version, constant) : lo word (start address + leading offset)
+    const uint32_t a_hi = (a_sbo >> 4) | (1u << 14), b_hi = (b_sbo >> 4) | (1u << 14);
+    const uint32_t a_lo0 = (a_lbo >> 4) << 16, b_lo0 = (b_lbo >> 4) << 16;
+    const uint32_t kstep_a = (2u * CHUNK_PITCH) >> 4, kstep_b = (2u * (uint32_t)g.N * 16u) >> 4;
+    bool ok = true;
+    if (!g.wstream) ok = mbar_wait(bar(BAR_WRES), 0, abort_flag, g.status, 1);
+    int pos_base = 0;  // ring position of the current unit's first entry (G == 1) / next entry (G > 1)
+    int gpass = 0, gw = 0;
+    for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
+      const Unit t = unit_of<R>(g, u);
+      int waited = 0;  // G == 1: entries of this unit already waited for
+      for (int p = 0; ok && p < t.npass; ++p) {
+        const int set = gpass & 1;
+        if (issuer) trace(g, 0, gpass, 0);
+        ok = mbar_wait(bar(BAR_TEMPTY + set), ((uint32_t)(gpass >> 1) & 1u) ^ 1u, abort_flag, g.status, 3);
+        if (!ok) break;
+        if (issuer) trace(g, 0, gpass, 1);
+        for (int gi = 0; ok && gi < g.G; ++gi) {
+          int first;  // ring position of input row (pass row 0, dy = 0)
+          if (g.G == 1) {
+            first = pos_base + p * R;
+            const int need = p * R + R + 1;
+            while (ok && waited <= need) {
+              const int gg = pos_base + waited;
+              ok = mbar_wait(bar(BAR_FULL + gg % S), (uint32_t)(gg / S) & 1u, abort_flag, g.status, 2);
+              ++waited;
+            }
+          } else {
+            first = pos_base;
+            for (int q = 0; ok && q < R + 2; ++q) {
+              const int gg = pos_base + q;
+              ok = mbar_wait(bar(BAR_FULL + gg % S), (uint32_t)(gg / S) & 1u, abort_flag, g.status, 2);
+            }
           }
           if (!ok) break;
-          const int set = gpass & 1;
-          ok = mbar_wait(bar(BAR_TEMPTY + set), ((uint32_t)(gpass >> 1) & 1u) ^ 1u, abort_flag, g.status, 3);
-          if (!ok) break;
+          if (issuer) trace(g, 0, gpass, 2);
           tc_fence_after();
-          for (int tap = 0; ok && tap < 9; ++tap) {
+          uint32_t row_lo[R + 2];
+#pragma unroll
+          for (int q = 0; q < R + 2; ++q)
+            row_lo[q] = (((slots_addr + (uint32_t)((first + q) % S) * slot_bytes) & 0x3FFFFu) >> 4) | a_lo0;
+          const int nk16 = g.gch[gi] >> 1;
+          const uint32_t wgrp = (uint32_t)g.gc0[gi] * g.N * 16u;
+          // The tap loop is unrolled so that the row word (dy) and the pixel offset (dx) are
+          // compile time: per MMA the issuing thread spends one add on the descriptor.
+#pragma unroll
+          for (int tap = 0; tap < 9; ++tap) {
             const int dy = tap / 3, dx = tap - dy * 3;
             uint32_t wb;
             int ws = 0;
             if (g.wstream) {
+              if (!ok) continue;
               ws = gw % g.WST;
               ok = mbar_wait(bar(BAR_WFULL + ws), (uint32_t)(gw / g.WST) & 1u, abort_flag, g.status, 4);
-              if (!ok) break;
+              if (!ok) continue;
               tc_fence_after();
-              wb = w_addr + (uint32_t)ws * wtap_bytes;
+              wb = w_addr + (uint32_t)ws * wstage_bytes;
             } else {
-              wb = w_addr + (uint32_t)tap * wtap_bytes;
+              wb = w_addr + (uint32_t)tap * wtap_bytes + wgrp;
             }
+            uint32_t b_lo = ((wb & 0x3FFFFu) >> 4) | b_lo0;
+            uint32_t a_off = (uint32_t)dx;  // 16 bytes per pixel
+            uint32_t acc = (gi | tap) == 0 ? 0u : 1u;
+#pragma unroll 1
             for (int kc = 0; kc < nk16; ++kc) {
-              const uint64_t bdesc = make_desc(wb + (uint32_t)kc * 2u * g.N * 16u, b_lbo, b_sbo);
+              if (issuer && !(g.skip & 2)) {
+                const uint64_t bdesc = ((uint64_t)b_hi << 32) | b_lo;
 #pragma unroll
-              for (int r = 0; r < R; ++r) {
-                const int slot = (gbase + p * R + r + dy) % g.S;
-                const uint32_t aaddr =
-                    slots_addr + (uint32_t)slot * slot_bytes + (uint32_t)kc * 2u * CHUNK_PITCH + (uint32_t)dx * 16u;
-                tc_mma(tmem_base + (uint32_t)((set * R + r) * g.Ns), make_desc(aaddr, a_lbo, a_sbo), bdesc, idesc,
-                       (tap | kc) != 0 ? 1u : 0u);
+                for (int r = 0; r < R; ++r)
+                  tc_mma(tmem_base + (uint32_t)((set * R + r) * g.Ns), ((uint64_t)a_hi << 32) | (row_lo[r + dy] + a_off),
+                         bdesc, idesc, acc);
               }
+              acc = 1u;
+              b_lo += kstep_b;
+              a_off += kstep_a;
             }
             if (g.wstream) {
-              tc_commit(bar(BAR_WEMPTY + ws));
+              if (issuer) tc_commit(bar(BAR_WEMPTY + ws));
               ++gw;
             }
           }
           if (!ok) break;
-          tc_commit(bar(BAR_TFULL + set));
-          const int nrel = (p == t.npass - 1) ? R + 2 : R;
-          for (int q = 0; q < nrel; ++q) tc_commit(bar(BAR_EMPTY + (gbase + p * R + q) % g.S));
-          ++gpass;
+          if (g.G > 1) {
+            if (issuer)
+              for (int q = 0; q < R + 2; ++q) tc_commit(bar(BAR_EMPTY + (pos_base + q) % S));
+            pos_base += R + 2;
+          }
         }
-        gbase += t.rows_in;
+        if (!ok) break;
+        if (issuer) {
+          trace(g, 0, gpass, 3);
+          tc_commit(bar(BAR_TFULL + set));
+          if (g.G == 1) {
+            const int nrel = (p == t.npass - 1) ? R + 2 : R;
+            for (int q = 0; q < nrel; ++q) tc_commit(bar(BAR_EMPTY + (pos_base + p * R + q) % S));
+          }
+          trace(g, 0, gpass, 4);
+        }
+        ++gpass;
       }
+      if (g.G == 1) pos_base += t.npass * R + 2;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -368,14 +604,18 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const TcArgs g) {
         for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
           const Unit t = unit_of<R>(g, u);
           for (int p = 0; ok && p < t.npass; ++p)
-            for (int tap = 0; ok && tap < 9; ++tap) {
-              const int ws = gw % g.WST;
-              ok = mbar_wait(bar(BAR_WEMPTY + ws), ((uint32_t)(gw / g.WST) & 1u) ^ 1u, abort_flag, g.status, 5);
-              if (!ok) break;
-              mbar_expect_tx(bar(BAR_WFULL + ws), wtap_bytes);
-              bulk_g2s(w_addr + (uint32_t)ws * wtap_bytes, wsrc + (size_t)tap * wtap_bytes, wtap_bytes,
-                       bar(BAR_WFULL + ws));
-              ++gw;
+            for (int gi = 0; ok && gi < g.G; ++gi) {
+              const uint32_t bytes = (uint32_t)g.gch[gi] * g.N * 16u;
+              const size_t goff = (size_t)g.gc0[gi] * g.N * 16u;
+              for (int tap = 0; ok && tap < 9; ++tap) {
+                const int ws = gw % g.WST;
+                ok = mbar_wait(bar(BAR_WEMPTY + ws), ((uint32_t)(gw / g.WST) & 1u) ^ 1u, abort_flag, g.status, 5);
+                if (!ok) break;
+                mbar_expect_tx(bar(BAR_WFULL + ws), bytes);
+                bulk_g2s(w_addr + (uint32_t)ws * wstage_bytes, wsrc + (size_t)tap * wtap_bytes + goff, bytes,
+                         bar(BAR_WFULL + ws));
+                ++gw;
+              }
             }
         }
       }
@@ -386,7 +626,6 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const TcArgs g) {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int m = q * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    const bool vec_out = (g.K & 7) == 0;
     bool ok = true;
     int gpass = 0;
     for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
@@ -395,113 +634,102 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const TcArgs g) {
       const bool xin = x < g.W;
       for (int p = 0; ok && p < t.npass; ++p) {
         const int set = gpass & 1;
+        if (threadIdx.x == 64) trace(g, 1, gpass, 0);
         ok = mbar_wait(bar(BAR_TFULL + set), (uint32_t)(gpass >> 1) & 1u, abort_flag, g.status, 6);
         if (!ok) break;
+        if (threadIdx.x == 64) trace(g, 1, gpass, 1);
         tc_fence_after();
         const int yb = t.y0 + p * R;
         constexpr int RSTEP = (R >= 2) ? 2 : 1;
-#pragma unroll 1
+#pragma unroll
         for (int r = 0; r < R; r += RSTEP) {
+          const int y = yb + r;
+          const uint32_t t0 = lane_addr + (uint32_t)((set * R + r) * g.Ns);
+          const uint32_t t1 = t0 + (uint32_t)g.Ns;
+          // rows past the image are computed but never stored
+          const bool yin = xin && y < g.H;
+          int c0 = 0;
 #pragma unroll 1
-          for (int c0 = 0; c0 < g.N; c0 += 16) {
-            uint32_t v0[16], v1[16];
-            tc_ld16(lane_addr + (uint32_t)((set * R + r) * g.Ns + c0), v0);
-            if (RSTEP == 2) tc_ld16(lane_addr + (uint32_t)((set * R + r + 1) * g.Ns + c0), v1);
-            tc_wait_ld();
-            float f0[16], f1[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              float bj = 0.0f;
-              if (g.bias && c0 + j < g.K) bj = __half2float(g.bias[c0 + j]);
-              f0[j] = __uint_as_float(v0[j]) + bj;
-              if (g.relu) f0[j] = fmaxf(f0[j], 0.0f);
-              if (RSTEP == 2) {
-                f1[j] = __uint_as_float(v1[j]) + bj;
-                if (g.relu) f1[j] = fmaxf(f1[j], 0.0f);
-              }
-            }
-            if (g.full_out && xin) {
-#pragma unroll
-              for (int rr = 0; rr < RSTEP; ++rr) {
-                const int y = yb + r + rr;
-                if (y >= g.H) continue;
-                const float *f = rr ? f1 : f0;
-                __half *o = g.out + ((long long)y * g.W + x) * g.K + c0;
-                if (vec_out && c0 + 16 <= g.K) {
-                  uint4 lo = make_uint4(pack_h2(f[0], f[1]), pack_h2(f[2], f[3]), pack_h2(f[4], f[5]),
-                                        pack_h2(f[6], f[7]));
-                  uint4 hi = make_uint4(pack_h2(f[8], f[9]), pack_h2(f[10], f[11]), pack_h2(f[12], f[13]),
-                                        pack_h2(f[14], f[15]));
-                  reinterpret_cast<uint4 *>(o)[0] = lo;
-                  reinterpret_cast<uint4 *>(o)[1] = hi;
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 16; ++j)
-                    if (c0 + j < g.K) o[j] = __float2half_rn(f[j]);
-                }
-              }
-            }
-            if (RSTEP == 2 && g.pool) {
-              // 2x2 max: vertical in registers, horizontal with the neighbouring lane
-              // (basic_pool.comp:44-82; max commutes with the rounding to binary16)
-              float pm[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const float vmax = fmaxf(f0[j], f1[j]);
-                pm[j] = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1));
-              }
-              const int y = yb + r;
-              if (xin && !(lane & 1) && y + 1 < g.H + (g.H & 1) && y < g.H) {
-                __half *o = g.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (x >> 1)) * g.K + c0;
-                if (vec_out && c0 + 16 <= g.K) {
-                  uint4 lo = make_uint4(pack_h2(pm[0], pm[1]), pack_h2(pm[2], pm[3]), pack_h2(pm[4], pm[5]),
-                                        pack_h2(pm[6], pm[7]));
-                  uint4 hi = make_uint4(pack_h2(pm[8], pm[9]), pack_h2(pm[10], pm[11]), pack_h2(pm[12], pm[13]),
-                                        pack_h2(pm[14], pm[15]));
-                  reinterpret_cast<uint4 *>(o)[0] = lo;
-                  reinterpret_cast<uint4 *>(o)[1] = hi;
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 16; ++j)
-                    if (c0 + j < g.K) o[j] = __float2half_rn(pm[j]);
-                }
-              }
-            }
-          }
+          for (; c0 + 32 <= g.N; c0 += 32) epilogue_block<32, RSTEP>(g, t0, t1, c0, x, y, yin, lane);
+          if (c0 < g.N) epilogue_block<16, RSTEP>(g, t0, t1, c0, x, y, yin, lane);
         }
+        if (threadIdx.x == 64) trace(g, 1, gpass, 2);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_TEMPTY + set));
+        if (threadIdx.x == 64) trace(g, 1, gpass, 3);
         ++gpass;
       }
     }
   } else {
     // ---------------- input slots ----------------
+    // Thread 0 of the producer warps issues the TMA copies of an entry and arrives on
+    // the slot's barrier with their byte count.  When some rows need the producer warps
+    // (upsampled operand, channel count not a multiple of 8, halo rows of a row band)
+    // all 128 threads walk the entries: each keeps up to D rows of cp.async in flight
+    // and signals entry pos - D + 1 after issuing entry pos.
     const int tid = threadIdx.x - 6 * 32;
     bool ok = true;
-    int gl = 0;
-    for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
-      const Unit t = unit_of<R>(g, u);
-      for (int j = 0; ok && j < t.rows_in; ++j) {
-        const int slot = gl % g.S;
-        ok = mbar_wait(bar(BAR_EMPTY + slot), ((uint32_t)(gl / g.S) & 1u) ^ 1u, abort_flag, g.status, 7);
-        if (!ok) break;
-        load_row(g, slots_addr + (uint32_t)slot * slot_bytes, t.y0 - 1 + j, t.x0, tid);
+    int pos = 0;        // entries issued
+    int signalled = 0;  // entries signalled full by the producer warps
+    const int D = g.D;
+    auto emit = [&](int iy, int x0, int c_lo, int c_hi) {
+      const int slot = pos % S;
+      if (tid == 0) trace(g, 2, pos, 0);
+      ok = mbar_wait(bar(BAR_EMPTY + slot), ((uint32_t)(pos / S) & 1u) ^ 1u, abort_flag, g.status, 7);
+      if (!ok) return;
+      if (tid == 0) trace(g, 2, pos, 1);
+      const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes;
+      if (tid == 0) {
+        const uint32_t fb = bar(BAR_FULL + slot);
+        // announce the byte count first, then start the copies
+        const uint32_t bytes = (g.skip & 1) ? 0u : tma_row<false>(g, slot_addr, iy, x0, c_lo, c_hi, fb);
+        if (bytes) {
+          mbar_expect_tx(fb, bytes);
+          tma_row<true>(g, slot_addr, iy, x0, c_lo, c_hi, fb);
+        } else {
+          mbar_arrive(fb);
+        }
+      }
+      if (g.cpa) {
+        if (!(g.skip & 1)) load_row(g, slot_addr, iy, x0, tid, c_lo, c_hi);
         cp_async_commit();
-        if (gl >= 1) {
-          cp_async_wait<1>();
+        if (tid == 0) trace(g, 2, pos, 2);
+        ++pos;
+        if (pos - signalled >= D) {
+          cp_async_wait_dyn(D - 1);
           fence_proxy_async();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar(BAR_FULL + (gl - 1) % g.S));
+          if (lane == 0) mbar_arrive(bar(BAR_FULL + signalled % S));
+          ++signalled;
         }
-        ++gl;
+      } else {
+        if (tid == 0) trace(g, 2, pos, 2);
+        ++pos;
       }
-    }
-    cp_async_wait<0>();
-    if (ok && gl >= 1) {
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(BAR_FULL + (gl - 1) % g.S));
+    };
+    if (g.cpa || tid == 0) {
+      for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
+        const Unit t = unit_of<R>(g, u);
+        if (g.G == 1) {
+          const int rows_in = t.npass * R + 2;
+          for (int j = 0; ok && j < rows_in; ++j) emit(t.y0 - 1 + j, t.x0, 0, nch);
+        } else {
+          for (int p = 0; ok && p < t.npass; ++p)
+            for (int gi = 0; ok && gi < g.G; ++gi)
+              for (int q = 0; ok && q < R + 2; ++q)
+                emit(t.y0 - 1 + p * R + q, t.x0, g.gc0[gi], g.gc0[gi] + g.gch[gi]);
+        }
+      }
+      if (g.cpa) {
+        cp_async_wait<0>();
+        if (ok) {
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0)
+            for (; signalled < pos; ++signalled) mbar_arrive(bar(BAR_FULL + signalled % S));
+        }
+      }
     }
   }
 
@@ -538,8 +766,40 @@ int sm_count() {
   return n;
 }
 
-// v.p0 = R (rows per pass), v.p1 = wanted slots, v.p2 = weight mode (0 resident, 1 streamed), v.p3 = weight stages
-int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl) {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// H x W x C binary16 tensor as (8, W, C/8, H) with strides (2, 2C, 16, 2WC) bytes; box (8, 132, 2, 1).
+int make_tensor_map(CUtensorMap *tm, const void *ptr, int H, int W, int C) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return DNXCU_E_CUDA;
+  const cuuint64_t dims[4] = {8, (cuuint64_t)W, (cuuint64_t)(C / 8), (cuuint64_t)H};
+  const cuuint64_t strides[3] = {(cuuint64_t)C * 2, 16, (cuuint64_t)W * C * 2};
+  const cuuint32_t box[4] = {8, (cuuint32_t)WH, 2, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DNXCU_OK : DNXCU_E_CUDA;
+}
+
+// v.p0 = R (rows per pass), v.p1 = K groups, v.p2 = weight mode (0 resident, 1 streamed), v.p3 = weight stages
+int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode) {
   if (!d.in_a || !d.weights || d.c_a <= 0 || d.c_out <= 0 || d.c_b < 0) return DNXCU_E_BAD_ARG;
   if (d.pc[0] == 0 || d.pc[1] == 0) return DNXCU_E_BAD_ARG;
   if (d.c_b > 0 && !d.in_b) return DNXCU_E_BAD_ARG;
@@ -565,8 +825,14 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl) {
     return DNXCU_E_MISALIGNED;
 
   TcArgs &g = pl.args;
-  g.a = {(const __half *)d.in_a, (const __half *)d.halo[0], (const __half *)d.halo[1], d.c_a, nch_of(d.c_a), up ? 1 : 0};
-  g.b = {(const __half *)d.in_b, (const __half *)d.halo[2], (const __half *)d.halo[3], d.c_b, nch_of(d.c_b), 0};
+  g.a = {(const __half *)d.in_a, (const __half *)d.halo[0], (const __half *)d.halo[1], d.c_a, nch_of(d.c_a), up ? 1 : 0, 0};
+  g.b = {(const __half *)d.in_b, (const __half *)d.halo[2], (const __half *)d.halo[3], d.c_b, nch_of(d.c_b), 0, 0};
+  // TMA takes the operands whose pixels are whole 16 byte chunks at full resolution
+  const char *notma = getenv("DNXCU_TC_NO_TMA");
+  const bool allow_tma = !(notma && notma[0] == '1');
+  g.a.tma = allow_tma && !up && (d.c_a % 8 == 0);
+  g.b.tma = allow_tma && d.c_b > 0 && (d.c_b % 8 == 0);
+  g.cpa = (!g.a.tma || (d.c_b > 0 && !g.b.tma) || d.halo[0] || d.halo[1] || d.halo[2] || d.halo[3]) ? 1 : 0;
   g.w = (const __half *)d.weights;
   g.bias = (d.flags & DNXCU_F_BIAS) ? (const __half *)d.bias : nullptr;
   g.out = (__half *)d.out;
@@ -585,6 +851,11 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl) {
   if (g.WST > MAX_WST) g.WST = MAX_WST;
   const char *sw = getenv("DNXCU_TC_DESC_SWAP");
   g.desc_swap = (sw && sw[0] == '1') ? 1 : 0;
+  const char *sk = getenv("DNXCU_TC_SKIP");
+  g.skip = sk ? atoi(sk) : 0;
+  // time line tracing: the caller's status buffer must then hold 8 + 3*64*6 64-bit words
+  const char *tr = getenv("DNXCU_TC_TRACE");
+  g.trace = (tr && tr[0] == '1' && d.device_status) ? reinterpret_cast<long long *>(d.device_status) + 8 : nullptr;
 
   uint32_t cols = 2u * R * g.Ns;
   if (cols > 512) return DNXCU_E_UNSUPPORTED;
@@ -592,37 +863,68 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl) {
   while (p2 < cols) p2 <<= 1;
   g.tmem_cols = p2;
 
+  // K groups: contiguous runs of 8 channel chunks (even counts: one MMA takes two chunks)
   const int nch = g.a.nch + g.b.nch;
+  g.G = v.p1 > 0 ? v.p1 : 1;
+  if (g.G > MAX_GROUPS) g.G = MAX_GROUPS;
+  if (g.G * 2 > nch) g.G = nch / 2;
+  {
+    int per = (nch + g.G - 1) / g.G;
+    per += per & 1;
+    int c = 0, gi = 0;
+    for (; gi < MAX_GROUPS && c < nch; ++gi) {
+      g.gc0[gi] = c;
+      g.gch[gi] = (nch - c < per) ? nch - c : per;
+      c += g.gch[gi];
+    }
+    g.G = gi;
+    for (; gi < MAX_GROUPS; ++gi) g.gc0[gi] = g.gch[gi] = 0;
+    g.gmax = per < nch ? per : nch;
+  }
+
   const size_t wtap = (size_t)nch * g.N * 16;
-  const size_t wregion = ((g.wstream ? wtap * g.WST : wtap * 9) + 127) & ~(size_t)127;
+  const size_t wstage = (size_t)g.gmax * g.N * 16;
+  const size_t wregion = ((g.wstream ? wstage * g.WST : wtap * 9) + 127) & ~(size_t)127;
   if (wtap * 9 >= (1u << 20)) return DNXCU_E_UNSUPPORTED;  // mbarrier transaction count limit
-  const size_t slot_bytes = (size_t)nch * CHUNK_PITCH;
-  if (HEADER_BYTES + wregion + (size_t)(R + 2) * slot_bytes > SMEM_LIMIT) return DNXCU_E_UNSUPPORTED;
+  const size_t slot_bytes = (size_t)g.gmax * CHUNK_PITCH;
+  if (HEADER_BYTES + wregion + (size_t)(R + 3) * slot_bytes > SMEM_LIMIT) return DNXCU_E_UNSUPPORTED;
   int S = (int)((SMEM_LIMIT - HEADER_BYTES - wregion) / slot_bytes);
-  if (S > v.p1) S = v.p1;
   if (S > MAX_SLOTS) S = MAX_SLOTS;
   g.S = S;
+  g.D = S - (R + 2);
+  if (g.D > MAX_DEPTH) g.D = MAX_DEPTH;
+  if (g.D < 1) g.D = 1;
   pl.smem = HEADER_BYTES + wregion + (size_t)S * slot_bytes;
 
   // rows per unit: whole waves of CTAs with little halo re-read
   g.nstrips = (W + STRIP - 1) / STRIP;
   const int sms = sm_count();
   const int step = (R > 2 ? R : 2);
-  double best = 1e30;
-  int bestRB = step;
-  for (int rb = step; rb <= 64; rb += step) {
-    const long long units = (long long)g.nstrips * ((H + rb - 1) / rb);
-    const long long waves = (units + sms - 1) / sms;
-    const double cost = (double)waves * (rb + 2.5);
-    if (cost < best - 1e-9) {
-      best = cost;
-      bestRB = rb;
+  if (g.G > 1) {
+    g.RB = R;  // nothing is reused across passes: the smallest unit balances best
+  } else {
+    double best = 1e30;
+    int bestRB = step;
+    for (int rb = step; rb <= 64; rb += step) {
+      const long long units = (long long)g.nstrips * ((H + rb - 1) / rb);
+      const long long waves = (units + sms - 1) / sms;
+      const double cost = (double)waves * (rb + 2.5);
+      if (cost < best - 1e-9) {
+        best = cost;
+        bestRB = rb;
+      }
     }
+    g.RB = bestRB;
   }
-  g.RB = bestRB;
   g.nunits = g.nstrips * ((H + g.RB - 1) / g.RB);
   pl.grid = g.nunits < sms ? g.nunits : sms;
   pl.R = R;
+  memset(&g.tm_a, 0, sizeof(g.tm_a));
+  memset(&g.tm_b, 0, sizeof(g.tm_b));
+  if (encode) {
+    if (g.a.tma && make_tensor_map(&g.tm_a, d.in_a, H, W, d.c_a)) return DNXCU_E_CUDA;
+    if (g.b.tma && make_tensor_map(&g.tm_b, d.in_b, H, W, d.c_b)) return DNXCU_E_CUDA;
+  }
   return DNXCU_OK;
 }
 
@@ -667,18 +969,18 @@ void conv_tc_prepare(const Variant &, const uint16_t *kcrs, int K, int ca, int c
 
 int conv_tc_validate(const Variant &v, const dnxcu_dispatch &d) {
   Plan pl;
-  return make_plan(v, d, pl);
+  return make_plan(v, d, pl, false);
 }
 
 void conv_tc_grid(const Variant &v, const dnxcu_dispatch &d, uint32_t g[3]) {
   Plan pl;
   g[0] = g[1] = g[2] = 1;
-  if (make_plan(v, d, pl) == DNXCU_OK) g[0] = (uint32_t)pl.grid;
+  if (make_plan(v, d, pl, false) == DNXCU_OK) g[0] = (uint32_t)pl.grid;
 }
 
 int conv_tc_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
   Plan pl;
-  int st = make_plan(v, d, pl);
+  int st = make_plan(v, d, pl, true);
   if (st) return st;
   switch (pl.R) {
     case 1: return launch_r<1>(pl, s);

@@ -65,7 +65,7 @@ def test_f16_conversion_matches_reference_rule():
 def test_prepare_weights_tc_layout():
     k, ca, cb = 24, 9, 16
     w = nets.rng.he_normal_weights(7, k, ca + cb)
-    vid = lib.find_variant("direct-conv-tc", "R=2#SLOTS=8#W=resident")
+    vid = lib.find_variant("direct-conv-tc", "R=2#KG=1#W=resident")
     blob = lib.prepare_weights(vid, w, ca, cb).view(np.float16)
     n, nch = 32, 2 + 2  # K padded to 16 -> 32, 9 -> 16 channels (2 chunks), 16 -> 2 chunks
     t = blob.reshape(9, nch, n, 8)
@@ -127,7 +127,8 @@ def test_validate_rules():
     d.in_a = 0x1002  # 9 channels: 2 byte loads, 2 byte alignment is enough
     assert ok(C.byref(d)) == 0
     assert ok(C.byref(_conv_dispatch(2, ca=176, k=112))) == lib.E_UNSUPPORTED   # weights do not fit: needs streaming
-    assert ok(C.byref(_conv_dispatch(4, ca=112, k=112))) == 0                   # streamed weights fit
+    assert ok(C.byref(_conv_dispatch(4, ca=96, k=96))) == 0                     # streamed weights fit
+    assert ok(C.byref(_conv_dispatch(5, ca=96, cb=80, k=112, flags=lib.F_RELU | lib.F_UP2X_A))) == 0  # two K groups
     d = _conv_dispatch(2, w=1921, flags=lib.F_UP2X_A)
     assert ok(C.byref(d)) == lib.E_BAD_ARG
     d = _conv_dispatch(2)
