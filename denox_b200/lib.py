@@ -107,6 +107,8 @@ SIGNATURES = {
                              C.POINTER(C.c_uint64)]),
     "dnxcu_prepare_weights": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                         C.POINTER(C.c_size_t)]),
+    "dnxcu_conv3x3_pool_static": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                                            C.c_uint32, C.c_void_p, C.c_void_p]),
     "dnxcu_f16_from_float": (C.c_uint16, [C.c_float]),
     "dnxcu_f16_to_float": (C.c_float, [C.c_uint16]),
     "dnxcu_model_create": (C.c_int, [C.POINTER(ModelDesc), C.c_void_p, C.c_int, C.POINTER(C.c_void_p)]),

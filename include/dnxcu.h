@@ -179,6 +179,36 @@ DNXCU_API int dnxcu_cost(const dnxcu_dispatch *d, uint64_t *bytes_read, uint64_t
 DNXCU_API int dnxcu_prepare_weights(int variant, const void *kcrs_f16, int c_out, int c_a, int c_b,
                                     void *out, size_t *bytes);
 
+/* ------------------------------------------------------------------------
+ * conv3x3 (+bias, +ReLU) then 2x2 max pool WITHOUT any device allocation.
+ * No counterpart in the reference: its runtime allocates every buffer itself
+ * (runtime/src/denox/runtime/instance.cpp:25-286).
+ *
+ * Who needs it: hosts that run this inside a frame loop or a latency critical
+ * render thread, where cudaMalloc / cudaFree are off limits because they
+ * serialise the whole device and may block for an unbounded time, and hosts
+ * whose memory budget is fixed at start-up and audited, so that a library may
+ * not grow it later.  dnxcu_instance_create serves everyone else.
+ *
+ * The full resolution conv result, which the pool consumes, is kept in a fixed
+ * array inside the library (DNXCU_STATIC_SCRATCH_BYTES, held by every device
+ * that loads the library until the process exits).  The call fails with
+ * DNXCU_E_LIMIT when height * width * c_out * 2 exceeds that size.
+ *   in       : height x width x c_in binary16 (device)
+ *   weights  : blob from dnxcu_prepare_weights for variant 0 ("direct-conv")
+ *   bias     : c_out binary16 (device) when flags has DNXCU_F_BIAS, else NULL
+ *   flags    : any of DNXCU_F_RELU, DNXCU_F_BIAS
+ *   out_pool : (height/2) x (width/2) x c_out binary16 (device); height, width even
+ * The first call on each device looks up the array's device address (a
+ * synchronous runtime query): make that call before starting a stream capture.
+ * Every call overwrites the array and all calls share it: two calls whose
+ * kernels can overlap on the GPU (different streams) race; keep them on one
+ * stream or order them with events.
+ * ---------------------------------------------------------------------- */
+#define DNXCU_STATIC_SCRATCH_BYTES (8u << 20)
+DNXCU_API int dnxcu_conv3x3_pool_static(const void *in, int height, int width, int c_in, const void *weights,
+                                        const void *bias, int c_out, uint32_t flags, void *out_pool, void *stream);
+
 /* float -> binary16 exactly as the reference converts fp32 model weights:
  * mantissa truncated, sub-normal results flushed to zero
  * (common/src/denox/memory/dtype/f16.cpp:6-20). */
