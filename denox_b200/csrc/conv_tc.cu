@@ -98,6 +98,7 @@ struct TcArgs {
   int gmax;              // largest group
   int D;                 // producer depth (rows in flight per thread)
   int cpa;               // producer warps copy part of the rows (cp.async) besides TMA
+  int NB;                // stacked form: accumulator blocks in the TMEM ring
   uint32_t tmem_cols;
   int desc_swap;  // debugging aid: exchange the two descriptor strides
   long long *trace;  // debugging aid: per role time stamps of CTA 0 (nullptr = off)
@@ -742,6 +743,314 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
   }
 }
 
+// ============================================================================
+// Stacked form ("DY=stack"): one pass per INPUT row.  The three vertical taps are
+// stacked along N: for input row j, horizontal tap dx and a 16 channel step, one
+// MMA with N' = 3N multiplies the row's pixels with [W(r=2) | W(r=1) | W(r=0)] and
+// adds into the accumulators of output rows j-1, j, j+1, which sit side by side
+// in a ring of TMEM blocks.  The A tile (4 KB per MMA, the operand that bounds
+// thin layers: its fetch from shared memory costs more than the math for N < 128)
+// is read three times per input row instead of nine.
+//   - block ring: output row number ob (counted over the CTA's whole life) uses
+//     TMEM block ob % NB, columns [block * N, block * N + N)
+//   - an output row is complete after input row y+1: commit -> tfull[block]
+//   - the block of output row j+1 is fresh at input row j: its first MMA
+//     (dx = 0, first channel step) is issued on its own with accumulate = 0
+//   - runs of blocks are split where the ring wraps and where N' would exceed 256
+//   - an input slot is released as soon as its own row's MMAs are committed
+// Two epilogue teams of four warps take alternate row pairs.
+constexpr int ST_THREADS = 448;        // MMA, weights, 8 epilogue warps, 4 producer warps
+constexpr int ST_MAX_BLOCKS = 16;
+constexpr int ST_BAR_FULL = 0;
+constexpr int ST_BAR_EMPTY = ST_BAR_FULL + MAX_SLOTS;
+constexpr int ST_BAR_TFULL = ST_BAR_EMPTY + MAX_SLOTS;
+constexpr int ST_BAR_TEMPTY = ST_BAR_TFULL + ST_MAX_BLOCKS;
+constexpr int ST_BAR_WRES = ST_BAR_TEMPTY + ST_MAX_BLOCKS;
+constexpr int ST_BAR_COUNT = ST_BAR_WRES + 1;
+static_assert(ST_BAR_COUNT * 8 + 16 <= HEADER_BYTES, "header too small");
+constexpr int ST_OFF_TMEM_PTR = ST_BAR_COUNT * 8;
+constexpr int ST_OFF_ABORT = ST_OFF_TMEM_PTR + 4;
+
+struct StUnit {
+  int x0, y0, rows_out;
+};
+__device__ __forceinline__ StUnit st_unit_of(const TcArgs &g, int u) {
+  StUnit t;
+  const int strip = u % g.nstrips, rb = u / g.nstrips;
+  t.x0 = strip * STRIP;
+  t.y0 = rb * g.RB;
+  t.rows_out = min(g.RB, g.H - t.y0);
+  return t;
+}
+
+struct Run {
+  uint32_t col;    // first TMEM column
+  uint32_t boff;   // byte offset of the run's first weight row inside a stacked chunk, >> 4
+  uint32_t idesc;  // instruction descriptor with this run's N'
+  uint32_t acc;    // 0: overwrite (fresh block), 1: accumulate
+};
+
+__global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_constant__ TcArgs g) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const uint32_t sbase = smem_u32(smem);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + ST_OFF_ABORT);
+  volatile uint32_t *tmem_ptr = reinterpret_cast<volatile uint32_t *>(smem + ST_OFF_TMEM_PTR);
+  auto bar = [&](int i) { return sbase + (uint32_t)i * 8u; };
+
+  const int nch = g.a.nch + g.b.nch;
+  const int N = g.N, NB = g.NB;
+  const uint32_t wdx_bytes = (uint32_t)nch * 3u * N * 16u;  // one horizontal tap: all chunks x 3N rows
+  const uint32_t w_addr = sbase + HEADER_BYTES;
+  const uint32_t slot_bytes = (uint32_t)nch * CHUNK_PITCH;
+  const uint32_t slots_addr = w_addr + ((wdx_bytes * 3u + 127u) & ~127u);
+  const int S = g.S;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    const uint32_t full_count = g.cpa ? 5u : 1u;
+    for (int i = 0; i < MAX_SLOTS; ++i) {
+      mbar_init(bar(ST_BAR_FULL + i), full_count);
+      mbar_init(bar(ST_BAR_EMPTY + i), 1);
+    }
+    for (int i = 0; i < ST_MAX_BLOCKS; ++i) {
+      mbar_init(bar(ST_BAR_TFULL + i), 1);
+      mbar_init(bar(ST_BAR_TEMPTY + i), 4);
+    }
+    mbar_init(bar(ST_BAR_WRES), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + ST_OFF_TMEM_PTR),
+                 "r"(g.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp == 0) {
+    // ---------------- MMA issue (warp-uniform loop, lane 0 issues) ----------------
+    const bool issuer = lane == 0;
+    const uint32_t a_hi = (128u >> 4) | (1u << 14), b_hi = a_hi;
+    const uint32_t a_lo0 = ((uint32_t)CHUNK_PITCH >> 4) << 16;
+    const uint32_t b_lo0 = (3u * N) << 16;  // leading offset = chunk pitch = 3N rows x 16 bytes, >> 4
+    const uint32_t kstep_a = (2u * CHUNK_PITCH) >> 4, kstep_b = 2u * 3u * N;
+    const uint32_t idesc0 = (1u << 4) | ((uint32_t)(STRIP >> 4) << 24);
+    const int maxrun = 256 / N;  // blocks one MMA may cover
+    const int nk16 = nch >> 1;
+    bool ok = mbar_wait(bar(ST_BAR_WRES), 0, abort_flag, g.status, 1);
+    int pos = 0, ob0 = 0;
+    for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
+      const StUnit t = st_unit_of(g, u);
+      const int rows_in = t.rows_out + 2;
+      for (int jj = 0; ok && jj < rows_in; ++jj) {
+        if (issuer) trace(g, 0, pos, 0);
+        const int slot = pos % S;
+        ok = mbar_wait(bar(ST_BAR_FULL + slot), (uint32_t)(pos / S) & 1u, abort_flag, g.status, 2);
+        if (!ok) break;
+        const bool fresh = jj < t.rows_out;
+        if (fresh) {
+          const int ob = ob0 + jj;
+          ok = mbar_wait(bar(ST_BAR_TEMPTY + ob % NB), ((uint32_t)(ob / NB) & 1u) ^ 1u, abort_flag, g.status, 3);
+          if (!ok) break;
+        }
+        if (issuer) trace(g, 0, pos, 1);
+        tc_fence_after();
+        // runs of TMEM blocks this input row adds into: outputs i in [i_lo, i_hi], stack index i - (jj - 2)
+        const int i_lo = max(jj - 2, 0), i_hi = min(jj, t.rows_out - 1);
+        Run runF[3] = {}, runR[3] = {};  // first MMA of the row (fresh block on its own) / all other MMAs
+        int nF = 0, nR = 0;
+        {
+          int startF = i_lo, startR = i_lo;
+          for (int i = i_lo; i <= i_hi + 1; ++i) {
+            const bool end = i > i_hi;
+            const int blk = (ob0 + i) % NB;
+            const bool wrap = !end && i > i_lo && blk == 0;
+            const bool cutR = end || wrap || (i - startR >= maxrun);
+            const bool cutF = end || wrap || (i - startF >= maxrun) || (fresh && i == jj && i > startF);
+            if (cutR && i > startR) {
+              runR[nR].col = (uint32_t)(((ob0 + startR) % NB) * N);
+              runR[nR].boff = (uint32_t)((startR - (jj - 2)) * N);
+              runR[nR].idesc = idesc0 | ((uint32_t)(((i - startR) * N) >> 3) << 17);
+              runR[nR].acc = 1u;
+              ++nR;
+              startR = i;
+            }
+            if (cutF && i > startF) {
+              runF[nF].col = (uint32_t)(((ob0 + startF) % NB) * N);
+              runF[nF].boff = (uint32_t)((startF - (jj - 2)) * N);
+              runF[nF].idesc = idesc0 | ((uint32_t)(((i - startF) * N) >> 3) << 17);
+              runF[nF].acc = (fresh && startF == jj) ? 0u : 1u;
+              ++nF;
+              startF = i;
+            }
+          }
+        }
+        const uint32_t row_lo = (((slots_addr + (uint32_t)slot * slot_bytes) & 0x3FFFFu) >> 4) | a_lo0;
+        const Run R0 = runR[0], R1 = runR[1], R2 = runR[2];
+        if (i_hi >= i_lo) {
+#pragma unroll
+          for (int dx = 0; dx < 3; ++dx) {
+            uint32_t b_lo = (((w_addr + (uint32_t)dx * wdx_bytes) & 0x3FFFFu) >> 4) | b_lo0;
+            uint32_t a_lo = row_lo + (uint32_t)dx;
+#pragma unroll 1
+            for (int kc = 0; kc < nk16; ++kc) {
+              const bool firstmma = dx == 0 && kc == 0;
+              if (issuer && !(g.skip & 2)) {
+                const uint64_t adesc = ((uint64_t)a_hi << 32) | a_lo;
+                if (firstmma) {
+                  for (int q = 0; q < nF; ++q)
+                    tc_mma(tmem_base + runF[q].col, adesc, ((uint64_t)b_hi << 32) | (b_lo + runF[q].boff),
+                           runF[q].idesc, runF[q].acc);
+                } else {
+                  tc_mma(tmem_base + R0.col, adesc, ((uint64_t)b_hi << 32) | (b_lo + R0.boff), R0.idesc, 1u);
+                  if (nR > 1) tc_mma(tmem_base + R1.col, adesc, ((uint64_t)b_hi << 32) | (b_lo + R1.boff), R1.idesc, 1u);
+                  if (nR > 2) tc_mma(tmem_base + R2.col, adesc, ((uint64_t)b_hi << 32) | (b_lo + R2.boff), R2.idesc, 1u);
+                }
+              }
+              b_lo += kstep_b;
+              a_lo += kstep_a;
+            }
+          }
+        }
+        if (issuer) {
+          trace(g, 0, pos, 2);
+          tc_commit(bar(ST_BAR_EMPTY + slot));
+          if (jj >= 2) tc_commit(bar(ST_BAR_TFULL + (ob0 + jj - 2) % NB));
+          trace(g, 0, pos, 3);
+        }
+        ++pos;
+      }
+      ob0 += t.rows_out;
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- weights (resident) ----------------
+    if (lane == 0) {
+      const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(g.w);
+      mbar_expect_tx(bar(ST_BAR_WRES), wdx_bytes * 3u);
+      // copies of at most 32 KB each
+      const uint32_t total = wdx_bytes * 3u;
+      for (uint32_t off = 0; off < total; off += 32768u) {
+        const uint32_t n = min(32768u, total - off);
+        bulk_g2s(w_addr + off, wsrc + off, n, bar(ST_BAR_WRES));
+      }
+    }
+    __syncwarp();
+  } else if (warp < 10) {
+    // ---------------- epilogue: two teams of four warps, alternate row pairs ----------------
+    const int team = (warp - 2) >> 2;
+    const int q = warp & 3;
+    const int m = q * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    bool ok = true;
+    int ob0 = 0, item = 0;
+    for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
+      const StUnit t = st_unit_of(g, u);
+      const int x = t.x0 + m;
+      const bool xin = x < g.W;
+      for (int i = 0; ok && i < t.rows_out; i += 2, ++item) {
+        if ((item & 1) != team) continue;
+        const int nrows = min(2, t.rows_out - i);
+        const int ob = ob0 + i;
+        const int b0 = ob % NB, b1 = (ob + 1) % NB;
+        if (threadIdx.x == 64) trace(g, 1, item >> 1, 0);
+        ok = mbar_wait(bar(ST_BAR_TFULL + b0), (uint32_t)(ob / NB) & 1u, abort_flag, g.status, 6);
+        if (ok && nrows == 2)
+          ok = mbar_wait(bar(ST_BAR_TFULL + b1), (uint32_t)((ob + 1) / NB) & 1u, abort_flag, g.status, 6);
+        if (!ok) break;
+        if (threadIdx.x == 64) trace(g, 1, item >> 1, 1);
+        tc_fence_after();
+        const int y = t.y0 + i;
+        const uint32_t t0 = lane_addr + (uint32_t)(b0 * N), t1 = lane_addr + (uint32_t)(b1 * N);
+        int c0 = 0;
+        if (nrows == 2) {
+#pragma unroll 1
+          for (; c0 + 32 <= N; c0 += 32) epilogue_block<32, 2>(g, t0, t1, c0, x, y, xin, lane);
+          if (c0 < N) epilogue_block<16, 2>(g, t0, t1, c0, x, y, xin, lane);
+        } else {
+#pragma unroll 1
+          for (; c0 + 32 <= N; c0 += 32) epilogue_block<32, 1>(g, t0, t1, c0, x, y, xin, lane);
+          if (c0 < N) epilogue_block<16, 1>(g, t0, t1, c0, x, y, xin, lane);
+        }
+        if (threadIdx.x == 64) trace(g, 1, item >> 1, 2);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar(ST_BAR_TEMPTY + b0));
+          if (nrows == 2) mbar_arrive(bar(ST_BAR_TEMPTY + b1));
+        }
+      }
+      ob0 += t.rows_out;
+    }
+  } else {
+    // ---------------- input slots (same scheme as the pass kernel) ----------------
+    const int tid = threadIdx.x - 10 * 32;
+    bool ok = true;
+    int pos = 0, signalled = 0;
+    const int D = g.D;
+    if (g.cpa || tid == 0) {
+      for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
+        const StUnit t = st_unit_of(g, u);
+        for (int jj = 0; ok && jj < t.rows_out + 2; ++jj) {
+          const int iy = t.y0 - 1 + jj;
+          const int slot = pos % S;
+          if (tid == 0) trace(g, 2, pos, 0);
+          ok = mbar_wait(bar(ST_BAR_EMPTY + slot), ((uint32_t)(pos / S) & 1u) ^ 1u, abort_flag, g.status, 7);
+          if (!ok) break;
+          if (tid == 0) trace(g, 2, pos, 1);
+          const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes;
+          if (tid == 0) {
+            const uint32_t fb = bar(ST_BAR_FULL + slot);
+            const uint32_t bytes = (g.skip & 1) ? 0u : tma_row<false>(g, slot_addr, iy, t.x0, 0, nch, fb);
+            if (bytes) {
+              mbar_expect_tx(fb, bytes);
+              tma_row<true>(g, slot_addr, iy, t.x0, 0, nch, fb);
+            } else {
+              mbar_arrive(fb);
+            }
+          }
+          if (g.cpa) {
+            if (!(g.skip & 1)) load_row(g, slot_addr, iy, t.x0, tid, 0, nch);
+            cp_async_commit();
+            ++pos;
+            if (pos - signalled >= D) {
+              cp_async_wait_dyn(D - 1);
+              fence_proxy_async();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar(ST_BAR_FULL + signalled % S));
+              ++signalled;
+            }
+          } else {
+            ++pos;
+          }
+          if (tid == 0) trace(g, 2, pos - 1, 2);
+        }
+      }
+      if (g.cpa) {
+        cp_async_wait<0>();
+        if (ok) {
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0)
+            for (; signalled < pos; ++signalled) mbar_arrive(bar(ST_BAR_FULL + signalled % S));
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(g.tmem_cols) : "memory");
+  }
+}
+
 // ---- host side --------------------------------------------------------------
 
 inline int pad16(int c) { return (c + 15) / 16 * 16; }
@@ -798,6 +1107,61 @@ int make_tensor_map(CUtensorMap *tm, const void *ptr, int H, int W, int C) {
   return r == CUDA_SUCCESS ? DNXCU_OK : DNXCU_E_CUDA;
 }
 
+// Plan of the stacked form: weights resident, one K group, TMEM ring of NB blocks.
+// Expects pl.args filled up to the operand description (done by make_plan).
+int make_plan_stack(const dnxcu_dispatch &d, Plan &pl, bool encode) {
+  TcArgs &g = pl.args;
+  const int W = g.W, H = g.H;
+  if (g.N > 128) return DNXCU_E_UNSUPPORTED;
+  g.Ns = g.N;
+  g.NB = 512 / g.N;
+  if (g.NB > ST_MAX_BLOCKS) g.NB = ST_MAX_BLOCKS;
+  uint32_t p2 = 32;
+  while (p2 < (uint32_t)(g.NB * g.N)) p2 <<= 1;
+  g.tmem_cols = p2;
+  g.wstream = 0;
+  g.G = 1;
+  const int nch = g.a.nch + g.b.nch;
+  g.gc0[0] = 0;
+  g.gch[0] = nch;
+  for (int i = 1; i < MAX_GROUPS; ++i) g.gc0[i] = g.gch[i] = 0;
+  g.gmax = nch;
+  const size_t wbytes = (size_t)9 * nch * g.N * 16;
+  if (wbytes >= (1u << 20)) return DNXCU_E_UNSUPPORTED;
+  const size_t wregion = (wbytes + 127) & ~(size_t)127;
+  const size_t slot_bytes = (size_t)nch * CHUNK_PITCH;
+  if (HEADER_BYTES + wregion + 4 * slot_bytes > SMEM_LIMIT) return DNXCU_E_UNSUPPORTED;
+  int S = (int)((SMEM_LIMIT - HEADER_BYTES - wregion) / slot_bytes);
+  if (S > MAX_SLOTS) S = MAX_SLOTS;
+  g.S = S;
+  g.D = S - 1 < MAX_DEPTH ? S - 1 : MAX_DEPTH;
+  pl.smem = HEADER_BYTES + wregion + (size_t)S * slot_bytes;
+  g.nstrips = (W + STRIP - 1) / STRIP;
+  const int sms = sm_count();
+  double best = 1e30;
+  int bestRB = 2;
+  for (int rb = 2; rb <= 64; rb += 2) {
+    const long long units = (long long)g.nstrips * ((H + rb - 1) / rb);
+    const long long waves = (units + sms - 1) / sms;
+    const double cost = (double)waves * (rb + 2.5);
+    if (cost < best - 1e-9) {
+      best = cost;
+      bestRB = rb;
+    }
+  }
+  g.RB = bestRB;
+  g.nunits = g.nstrips * ((H + g.RB - 1) / g.RB);
+  pl.grid = g.nunits < sms ? g.nunits : sms;
+  pl.R = 0;
+  memset(&g.tm_a, 0, sizeof(g.tm_a));
+  memset(&g.tm_b, 0, sizeof(g.tm_b));
+  if (encode) {
+    if (g.a.tma && make_tensor_map(&g.tm_a, d.in_a, H, W, d.c_a)) return DNXCU_E_CUDA;
+    if (g.b.tma && make_tensor_map(&g.tm_b, d.in_b, H, W, d.c_b)) return DNXCU_E_CUDA;
+  }
+  return DNXCU_OK;
+}
+
 // v.p0 = R (rows per pass), v.p1 = K groups, v.p2 = weight mode (0 resident, 1 streamed), v.p3 = weight stages
 int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode) {
   if (!d.in_a || !d.weights || d.c_a <= 0 || d.c_out <= 0 || d.c_b < 0) return DNXCU_E_BAD_ARG;
@@ -811,8 +1175,8 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode) 
   if (full && !d.out) return DNXCU_E_BAD_ARG;
   if (pool && !d.out_pool) return DNXCU_E_BAD_ARG;
   if ((up || pool) && ((W | H) & 1)) return DNXCU_E_BAD_ARG;
-  const int R = v.p0;
-  if (pool && R < 2) return DNXCU_E_UNSUPPORTED;
+  const int R = v.p0;  // 0 selects the stacked form
+  if (pool && R == 1) return DNXCU_E_UNSUPPORTED;
   if (d.c_out > 256) return DNXCU_E_UNSUPPORTED;
   // 16 byte rules: vector loads of operands with C % 8 == 0, vector stores when K % 8 == 0, bulk weight copies
   if ((uintptr_t)d.weights & 15) return DNXCU_E_MISALIGNED;
@@ -857,6 +1221,7 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode) 
   const char *tr = getenv("DNXCU_TC_TRACE");
   g.trace = (tr && tr[0] == '1' && d.device_status) ? reinterpret_cast<long long *>(d.device_status) + 8 : nullptr;
 
+  if (R == 0) return make_plan_stack(d, pl, encode);
   uint32_t cols = 2u * R * g.Ns;
   if (cols > 512) return DNXCU_E_UNSUPPORTED;
   uint32_t p2 = 32;
@@ -944,6 +1309,19 @@ int launch_r(const Plan &pl, cudaStream_t s) {
   return DNXCU_OK;
 }
 
+int launch_stack(const Plan &pl, cudaStream_t s) {
+  static bool attr_done[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || !attr_done[dev]) {
+    DNXCU_CUDA(cudaFuncSetAttribute(conv3x3_tc_stack, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
+    if (dev < 16) attr_done[dev] = true;
+  }
+  conv3x3_tc_stack<<<pl.grid, ST_THREADS, pl.smem, s>>>(pl.args);
+  DNXCU_CUDA(cudaGetLastError());
+  return DNXCU_OK;
+}
+
 }  // namespace
 
 size_t conv_tc_weight_bytes(const Variant &, int k, int ca, int cb) {
@@ -954,10 +1332,24 @@ size_t conv_tc_weight_bytes(const Variant &, int k, int ca, int cb) {
 // count padded to a multiple of 16 and the output channels to a multiple of 16,
 // zero filled.  Plays the role of the RSCKC16 / KRSCK16 re-layouts of the
 // reference (common/src/denox/memory/tensor/FilterLayout.hpp:74-78,104-108).
-void conv_tc_prepare(const Variant &, const uint16_t *kcrs, int K, int ca, int cb, uint16_t *out) {
+void conv_tc_prepare(const Variant &v, const uint16_t *kcrs, int K, int ca, int cb, uint16_t *out) {
   const int C = ca + cb, N = pad16(K), nch = nch_of(ca) + nch_of(cb);
   const size_t n = (size_t)9 * nch * N * 8;
   for (size_t i = 0; i < n; ++i) out[i] = 0;
+  if (v.p0 == 0) {
+    // stacked form: [dx][chunk][3N rows][8]; the rows of a chunk are the three vertical taps
+    // r = 2, 1, 0 one after the other (matching output rows j-1, j, j+1 of input row j)
+    for (int seg = 0; seg < 2; ++seg) {
+      const int Cs = seg ? cb : ca, cbase = seg ? ca : 0, chbase = seg ? nch_of(ca) : 0;
+      for (int r = 0; r < 3; ++r)
+        for (int sx = 0; sx < 3; ++sx)
+          for (int c = 0; c < Cs; ++c)
+            for (int k = 0; k < K; ++k)
+              out[((((size_t)sx * nch + chbase + c / 8) * 3 + (2 - r)) * N + k) * 8 + c % 8] =
+                  kcrs[((size_t)k * C + cbase + c) * 9 + r * 3 + sx];
+    }
+    return;
+  }
   for (int seg = 0; seg < 2; ++seg) {
     const int Cs = seg ? cb : ca, cbase = seg ? ca : 0, chbase = seg ? nch_of(ca) : 0;
     for (int t = 0; t < 9; ++t)
@@ -983,6 +1375,7 @@ int conv_tc_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
   int st = make_plan(v, d, pl, true);
   if (st) return st;
   switch (pl.R) {
+    case 0: return launch_stack(pl, s);
     case 1: return launch_r<1>(pl, s);
     case 2: return launch_r<2>(pl, s);
     case 4: return launch_r<4>(pl, s);

@@ -46,7 +46,7 @@ extern "C" int dnxcu_conv3x3_pool_static(const void *in, int height, int width, 
   if (st) return st;
 
   dnxcu_dispatch conv = {};
-  conv.variant = 0;  // direct-conv: runs every shape, never fuses the pool
+  conv.variant = dnxcu_find_variant("direct-conv", "ACC=f32#TILE=16x8#KT=32");  // runs every shape, never fuses the pool
   conv.flags = flags;
   conv.pc[0] = (uint32_t)width;
   conv.pc[1] = (uint32_t)height;
@@ -60,7 +60,7 @@ extern "C" int dnxcu_conv3x3_pool_static(const void *in, int height, int width, 
   if (st) return st;
 
   dnxcu_dispatch pool = {};
-  pool.variant = (c_out % 8 == 0 && ((uintptr_t)out_pool & 15) == 0) ? 6 : 7;  // basic-pool, 128-bit or 2-byte form
+  pool.variant = dnxcu_find_variant("basic-pool", (c_out % 8 == 0 && ((uintptr_t)out_pool & 15) == 0) ? "VEC=8" : "VEC=1");
   pool.pc[0] = (uint32_t)width;
   pool.pc[1] = (uint32_t)height;
   pool.c_a = c_out;

@@ -86,7 +86,7 @@ def test_prepare_weights_direct_layout_and_errors():
     n = C.c_size_t(4)
     small = np.zeros(4, np.uint8)
     assert lib.L.dnxcu_prepare_weights(0, w.ctypes.data, k, ca, 0, small.ctypes.data, C.byref(n)) == lib.E_BAD_ARG
-    assert lib.L.dnxcu_prepare_weights(6, None, k, ca, 0, None, C.byref(n)) == lib.E_BAD_ARG  # not a conv variant
+    assert lib.L.dnxcu_prepare_weights(lib.find_variant("basic-pool", "VEC=8"), None, k, ca, 0, None, C.byref(n)) == lib.E_BAD_ARG
 
 
 def _conv_dispatch(variant, w=1920, h=1088, ca=32, cb=0, k=32, flags=lib.F_RELU):
@@ -135,11 +135,11 @@ def test_validate_rules():
     d.weights = None
     assert ok(C.byref(d)) == lib.E_BAD_ARG
     p = lib.Dispatch()
-    p.variant, p.c_a = 6, 12
+    p.variant, p.c_a = lib.find_variant("basic-pool", "VEC=8"), 12
     p.pc[0], p.pc[1] = 8, 8
     p.in_a = p.out = 0x1000
     assert ok(C.byref(p)) == lib.E_UNSUPPORTED  # 128-bit pool needs C % 8 == 0
-    p.variant = 7
+    p.variant = lib.find_variant("basic-pool", "VEC=1")
     assert ok(C.byref(p)) == 0
 
 
@@ -178,3 +178,15 @@ def test_db_bookkeeping(tmp_path):
     bad.write_text("not a database\n")
     h = C.c_void_p()
     assert lib.L.dnxcu_db_open(str(bad).encode(), C.byref(h)) == lib.E_IO
+
+
+def test_prepare_weights_stacked_layout():
+    """DY=stack: [dx][chunk][3N rows][8], rows of a chunk = vertical taps r = 2, 1, 0."""
+    k, ca = 16, 32
+    w = nets.rng.he_normal_weights(9, k, ca)
+    vid = lib.find_variant("direct-conv-tc", "DY=stack#W=resident")
+    t = lib.prepare_weights(vid, w, ca).view(np.float16).reshape(3, 4, 3, 16, 8)
+    for sx in range(3):
+        for r in range(3):
+            for ch in range(4):
+                assert (t[sx, ch, 2 - r] == w[:, ch * 8:(ch + 1) * 8, r, sx]).all()
