@@ -80,15 +80,16 @@ static const Variant kVariants[] = {
     {{3, DNXCU_OP_CONV3X3, "direct-conv-tc", "R=4#KG=1#W=resident", CONV_ALL, 1, 1, 1, 128, 0}, VK_CONV_TC, 4, 1, 0, 0},
     {{4, DNXCU_OP_CONV3X3, "direct-conv-tc", "R=2#KG=1#W=stream3", CONV_ALL, 1, 1, 1, 256, 0}, VK_CONV_TC, 2, 1, 1, 3},
     {{5, DNXCU_OP_CONV3X3, "direct-conv-tc", "R=2#KG=2#W=stream3", CONV_ALL, 1, 1, 1, 256, 0}, VK_CONV_TC, 2, 2, 1, 3},
-    {{6, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#W=resident", CONV_ALL, 1, 1, 1, 128, 0}, VK_CONV_TC, 0, 1, 0, 0},
-    {{7, DNXCU_OP_MAXPOOL2X2, "basic-pool", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_POOL, 8, 0, 0, 0},
-    {{8, DNXCU_OP_MAXPOOL2X2, "basic-pool", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_POOL, 1, 0, 0, 0},
-    {{9, DNXCU_OP_UPSAMPLE2X, "basic-upsample", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_UPSAMPLE, 8, 0, 0, 0},
-    {{10, DNXCU_OP_UPSAMPLE2X, "basic-upsample", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_UPSAMPLE, 1, 0, 0, 0},
-    {{11, DNXCU_OP_CONCAT, "copy-transform", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_CONCAT, 8, 0, 0, 0},
-    {{12, DNXCU_OP_CONCAT, "copy-transform", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_CONCAT, 1, 0, 0, 0},
-    {{13, DNXCU_OP_RELU, "basic-activation", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_RELU, 8, 0, 0, 0},
-    {{14, DNXCU_OP_RELU, "basic-activation", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_RELU, 1, 0, 0, 0},
+    {{6, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=1#W=resident", CONV_ALL, 1, 1, 1, 128, 0}, VK_CONV_TC, 0, 1, 0, 0},
+    {{7, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=2#W=resident", CONV_ALL, 1, 1, 1, 128, 0}, VK_CONV_TC, 0, 2, 0, 0},
+    {{8, DNXCU_OP_MAXPOOL2X2, "basic-pool", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_POOL, 8, 0, 0, 0},
+    {{9, DNXCU_OP_MAXPOOL2X2, "basic-pool", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_POOL, 1, 0, 0, 0},
+    {{10, DNXCU_OP_UPSAMPLE2X, "basic-upsample", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_UPSAMPLE, 8, 0, 0, 0},
+    {{11, DNXCU_OP_UPSAMPLE2X, "basic-upsample", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_UPSAMPLE, 1, 0, 0, 0},
+    {{12, DNXCU_OP_CONCAT, "copy-transform", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_CONCAT, 8, 0, 0, 0},
+    {{13, DNXCU_OP_CONCAT, "copy-transform", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_CONCAT, 1, 0, 0, 0},
+    {{14, DNXCU_OP_RELU, "basic-activation", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_RELU, 8, 0, 0, 0},
+    {{15, DNXCU_OP_RELU, "basic-activation", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_RELU, 1, 0, 0, 0},
 };
 static const int kVariantCount = (int)(sizeof(kVariants) / sizeof(kVariants[0]));
 

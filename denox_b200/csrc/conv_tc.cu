@@ -75,6 +75,7 @@ struct Seg {
   int nch;            // 8 channel chunks after padding C to a multiple of 16
   int up;
   int tma;            // rows of this operand are fetched by TMA (tensor map below)
+  int tbox;           // 8 channel chunks per TMA copy (box extent of the tensor map's chunk dimension)
 };
 
 struct TcArgs {
@@ -98,7 +99,8 @@ struct TcArgs {
   int gmax;              // largest group
   int D;                 // producer depth (rows in flight per thread)
   int cpa;               // producer warps copy part of the rows (cp.async) besides TMA
-  int NB;                // stacked form: accumulator blocks in the TMEM ring
+  int NB;                // stacked form: accumulator blocks in the TMEM ring (per pipeline)
+  int P;                 // stacked form: pipelines per CTA (1 or 2)
   uint32_t tmem_cols;
   int desc_swap;  // debugging aid: exchange the two descriptor strides
   long long *trace;  // debugging aid: per role time stamps of CTA 0 (nullptr = off)
@@ -133,11 +135,15 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another ran out).
+// SLEEP_NS > 0: back off between polls, so that a waiting warp does not take issue
+// slots from the warps that share its scheduler (the MMA issuer above all).
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
                                           int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
+    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 0) {
       if (*abort_flag) return false;
@@ -285,9 +291,9 @@ __device__ __forceinline__ uint32_t tma_row(const TcArgs &g, uint32_t slot_addr,
     if (hi > lo && row_by_tma(g, s, iy)) {
       const void *tm = sg ? (const void *)&g.tm_b : (const void *)&g.tm_a;
 #pragma unroll 1
-      for (int c = lo; c < hi; c += 2) {
+      for (int c = lo; c < hi; c += s.tbox) {
         if (ISSUE) tma_load_4d(slot_addr + (uint32_t)((chbase + c - c_lo) * CHUNK_PITCH), tm, 0, x0 - 1, c, iy, bar);
-        bytes += 2u * CHUNK_PITCH;
+        bytes += (uint32_t)s.tbox * CHUNK_PITCH;
       }
     }
     chbase += s.nch;
@@ -298,8 +304,8 @@ __device__ __forceinline__ uint32_t tma_row(const TcArgs &g, uint32_t slot_addr,
 // Producer warp part of one ring entry: the operands (or halo rows) TMA does not
 // cover, with 16 byte cp.async (2 byte loads for channel counts that are not a
 // multiple of 8).  Chunk c of the operand list lands at slot chunk c - c_lo.
-__device__ __forceinline__ void load_row(const TcArgs &g, uint32_t slot_addr, int iy, int x0, int tid, int c_lo,
-                                         int c_hi) {
+__device__ __forceinline__ void load_row(const TcArgs &g, uint32_t slot_addr, int iy, int x0, int tid, int nprod,
+                                         int c_lo, int c_hi) {
   int chbase = 0;
 #pragma unroll 1
   for (int sg = 0; sg < 2; ++sg) {
@@ -318,7 +324,7 @@ __device__ __forceinline__ void load_row(const TcArgs &g, uint32_t slot_addr, in
       const int nchv = s.C >> 3;
       const uint32_t dst0 = slot_addr + (uint32_t)((chbase + lo - c_lo) * CHUNK_PITCH);
 #pragma unroll 1
-      for (int i = tid; i < items; i += N_PRODUCER) {
+      for (int i = tid; i < items; i += nprod) {
         const int px = i / n, ch = i - px * n;
         const int ix = x0 - 1 + px;
         const bool inb = row != nullptr && ix >= 0 && ix < g.W;
@@ -610,7 +616,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
               const size_t goff = (size_t)g.gc0[gi] * g.N * 16u;
               for (int tap = 0; ok && tap < 9; ++tap) {
                 const int ws = gw % g.WST;
-                ok = mbar_wait(bar(BAR_WEMPTY + ws), ((uint32_t)(gw / g.WST) & 1u) ^ 1u, abort_flag, g.status, 5);
+                ok = mbar_wait<64>(bar(BAR_WEMPTY + ws), ((uint32_t)(gw / g.WST) & 1u) ^ 1u, abort_flag, g.status, 5);
                 if (!ok) break;
                 mbar_expect_tx(bar(BAR_WFULL + ws), bytes);
                 bulk_g2s(w_addr + (uint32_t)ws * wstage_bytes, wsrc + (size_t)tap * wtap_bytes + goff, bytes,
@@ -636,7 +642,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
       for (int p = 0; ok && p < t.npass; ++p) {
         const int set = gpass & 1;
         if (threadIdx.x == 64) trace(g, 1, gpass, 0);
-        ok = mbar_wait(bar(BAR_TFULL + set), (uint32_t)(gpass >> 1) & 1u, abort_flag, g.status, 6);
+        ok = mbar_wait<64>(bar(BAR_TFULL + set), (uint32_t)(gpass >> 1) & 1u, abort_flag, g.status, 6);
         if (!ok) break;
         if (threadIdx.x == 64) trace(g, 1, gpass, 1);
         tc_fence_after();
@@ -677,7 +683,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
     auto emit = [&](int iy, int x0, int c_lo, int c_hi) {
       const int slot = pos % S;
       if (tid == 0) trace(g, 2, pos, 0);
-      ok = mbar_wait(bar(BAR_EMPTY + slot), ((uint32_t)(pos / S) & 1u) ^ 1u, abort_flag, g.status, 7);
+      ok = mbar_wait<64>(bar(BAR_EMPTY + slot), ((uint32_t)(pos / S) & 1u) ^ 1u, abort_flag, g.status, 7);
       if (!ok) return;
       if (tid == 0) trace(g, 2, pos, 1);
       const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes;
@@ -693,7 +699,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
         }
       }
       if (g.cpa) {
-        if (!(g.skip & 1)) load_row(g, slot_addr, iy, x0, tid, c_lo, c_hi);
+        if (!(g.skip & 1)) load_row(g, slot_addr, iy, x0, tid, N_PRODUCER, c_lo, c_hi);
         cp_async_commit();
         if (tid == 0) trace(g, 2, pos, 2);
         ++pos;
@@ -740,6 +746,88 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
   if (warp == 0) {
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(g.tmem_cols) : "memory");
+  }
+}
+
+// Epilogue of the stacked kernel, specialised at compile time on what the dispatch
+// needs (EPI bits: 1 bias, 2 ReLU, 4 pooled output, 8 full resolution output) so
+// that no flag is tested per value.  Values are rounded to binary16 pairs first;
+// ReLU and the 2x2 max then work on packed pairs (max commutes with the rounding).
+constexpr int EPI_BIAS = 1, EPI_RELU = 2, EPI_POOL = 4, EPI_FULL = 8;
+
+__device__ __forceinline__ uint32_t hmax2_u32(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+template <int NC, int EPI>
+__device__ __forceinline__ void round_row(const TcArgs &g, const uint32_t (&v)[NC], int c0, uint32_t (&h)[NC / 2]) {
+#pragma unroll
+  for (int j = 0; j < NC; j += 2) {
+    float lo = __uint_as_float(v[j]), hi = __uint_as_float(v[j + 1]);
+    if (EPI & EPI_BIAS) {
+      lo += (c0 + j < g.K) ? __half2float(__ldg(g.bias + c0 + j)) : 0.0f;
+      hi += (c0 + j + 1 < g.K) ? __half2float(__ldg(g.bias + c0 + j + 1)) : 0.0f;
+    }
+    uint32_t p = pack_h2(lo, hi);
+    if (EPI & EPI_RELU) p = hmax2_u32(p, 0u);
+    h[j / 2] = p;
+  }
+}
+
+// Stores NC channels [c0, c0 + NC) of one pixel from packed pairs.
+template <int NC>
+__device__ __forceinline__ void store_row(const TcArgs &g, __half *o, const uint32_t (&h)[NC / 2], int c0) {
+  if ((g.K & 7) == 0) {
+#pragma unroll
+    for (int j8 = 0; j8 < NC; j8 += 8)
+      if (c0 + j8 + 8 <= g.K)
+        *reinterpret_cast<uint4 *>(o + j8) = make_uint4(h[j8 / 2], h[j8 / 2 + 1], h[j8 / 2 + 2], h[j8 / 2 + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < NC; ++j)
+      if (c0 + j < g.K) {
+        const uint32_t p = h[j / 2];
+        reinterpret_cast<unsigned short *>(o)[j] = (unsigned short)((j & 1) ? (p >> 16) : (p & 0xffffu));
+      }
+  }
+}
+
+template <int NC, int RSTEP, int EPI>
+__device__ __forceinline__ void epi_fast(const TcArgs &g, uint32_t t0, uint32_t t1, int c0, int x, int y, bool xin,
+                                         int lane) {
+  uint32_t v0[NC], v1[RSTEP == 2 ? NC : 2];
+  if constexpr (NC == 32) {
+    tc_ld32(t0 + (uint32_t)c0, v0);
+    if constexpr (RSTEP == 2) tc_ld32(t1 + (uint32_t)c0, v1);
+  } else {
+    tc_ld16(t0 + (uint32_t)c0, v0);
+    if constexpr (RSTEP == 2) tc_ld16(t1 + (uint32_t)c0, v1);
+  }
+  tc_wait_ld();
+  uint32_t h0[NC / 2], h1[RSTEP == 2 ? NC / 2 : 1];
+  round_row<NC, EPI>(g, v0, c0, h0);
+  if constexpr (RSTEP == 2) round_row<NC, EPI>(g, v1, c0, h1);
+  const bool row1 = RSTEP == 2 && (y + 1 < g.H);
+  if (EPI & EPI_FULL) {
+    if (xin) {
+      __half *o0 = g.out + ((long long)y * g.W + x) * g.K + c0;
+      store_row<NC>(g, o0, h0, c0);
+      if constexpr (RSTEP == 2) {
+        if (row1) store_row<NC>(g, o0 + (long long)g.W * g.K, h1, c0);
+      }
+    }
+  }
+  if constexpr (RSTEP == 2 && (EPI & EPI_POOL) != 0) {
+    uint32_t pm[NC / 2];
+#pragma unroll
+    for (int j = 0; j < NC / 2; ++j) {
+      const uint32_t vm = hmax2_u32(h0[j], h1[j]);
+      pm[j] = hmax2_u32(vm, __shfl_xor_sync(0xffffffffu, vm, 1));
+    }
+    if (xin && !(lane & 1) && row1)
+      store_row<NC>(g, g.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (x >> 1)) * g.K + c0, pm, c0);
   }
 }
 
@@ -790,6 +878,14 @@ struct Run {
   uint32_t acc;    // 0: overwrite (fresh block), 1: accumulate
 };
 
+// P = 1 or 2 independent pipelines share the CTA's resident weights: each pipeline has
+// its own MMA issuing warp, its own input slots, half of the TMEM ring, one epilogue
+// team and its own work units.  The issuing thread's instruction stream, not the tensor
+// pipe, limits one pipeline (about 3000 cycles per input row against 1250 cycles of MMA
+// execution at 64 -> 64 channels), so two of them nearly double the rate.
+constexpr int ST_PIPE_STRIDE = 8;  // barrier index stride between the pipelines (slots / blocks per pipeline <= 8 when P == 2)
+
+template <int EPI>
 __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_constant__ TcArgs g) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t sbase = smem_u32(smem);
@@ -799,16 +895,18 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   auto bar = [&](int i) { return sbase + (uint32_t)i * 8u; };
 
   const int nch = g.a.nch + g.b.nch;
-  const int N = g.N, NB = g.NB;
+  const int N = g.N, NB = g.NB, P = g.P;
   const uint32_t wdx_bytes = (uint32_t)nch * 3u * N * 16u;  // one horizontal tap: all chunks x 3N rows
   const uint32_t w_addr = sbase + HEADER_BYTES;
-  const uint32_t slot_bytes = (uint32_t)nch * CHUNK_PITCH;
-  const uint32_t slots_addr = w_addr + ((wdx_bytes * 3u + 127u) & ~127u);
-  const int S = g.S;
+  const uint32_t slot_bytes = (uint32_t)g.gmax * CHUNK_PITCH;
+  const uint32_t slots_addr0 = w_addr + ((wdx_bytes * 3u + 127u) & ~127u);
+  const int S = g.S;  // slots per pipeline
+  const int unit_stride = (int)gridDim.x * P;
+  const int nprod_warps = P == 2 ? 2 : 4;  // producer warps per pipeline
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    const uint32_t full_count = g.cpa ? 5u : 1u;
+    const uint32_t full_count = g.cpa ? (uint32_t)nprod_warps + 1u : 1u;
     for (int i = 0; i < MAX_SLOTS; ++i) {
       mbar_init(bar(ST_BAR_FULL + i), full_count);
       mbar_init(bar(ST_BAR_EMPTY + i), 1);
@@ -829,215 +927,320 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_ptr;
+  const uint32_t tmem_base0 = *tmem_ptr;
 
-  if (warp == 0) {
-    // ---------------- MMA issue (warp-uniform loop, lane 0 issues) ----------------
+  if (warp == 1 && lane == 0) {
+    // ---------------- weights (resident), copies of at most 32 KB ----------------
+    const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(g.w);
+    const uint32_t total = wdx_bytes * 3u;
+    mbar_expect_tx(bar(ST_BAR_WRES), total);
+    for (uint32_t off = 0; off < total; off += 32768u)
+      bulk_g2s(w_addr + off, wsrc + off, min(32768u, total - off), bar(ST_BAR_WRES));
+  }
+  if (warp == 1) __syncwarp();
+
+  if (warp < P) {
+    // ---------------- MMA issue of pipeline `warp` (warp-uniform loop, lane 0 issues) ----------------
+    const int pipe = warp;
+    const int bofs = pipe * ST_PIPE_STRIDE;
+    const uint32_t tmem_base = tmem_base0 + (uint32_t)(pipe * NB * N);
+    const uint32_t slots_addr = slots_addr0 + (uint32_t)(pipe * S) * slot_bytes;
     const bool issuer = lane == 0;
     const uint32_t a_hi = (128u >> 4) | (1u << 14), b_hi = a_hi;
     const uint32_t a_lo0 = ((uint32_t)CHUNK_PITCH >> 4) << 16;
     const uint32_t b_lo0 = (3u * N) << 16;  // leading offset = chunk pitch = 3N rows x 16 bytes, >> 4
     const uint32_t kstep_a = (2u * CHUNK_PITCH) >> 4, kstep_b = 2u * 3u * N;
     const uint32_t idesc0 = (1u << 4) | ((uint32_t)(STRIP >> 4) << 24);
-    const int maxrun = 256 / N;  // blocks one MMA may cover
-    const int nk16 = nch >> 1;
     bool ok = mbar_wait(bar(ST_BAR_WRES), 0, abort_flag, g.status, 1);
-    int pos = 0, ob0 = 0;
-    for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
+    const bool two = 2 * N <= 256, three = 3 * N <= 256;
+    const uint32_t N16 = (uint32_t)N;  // weight rows of one vertical tap, in 16 byte units of a chunk
+    const uint32_t kb2 = 2u * kstep_b, kb3 = 3u * kstep_b, kb4 = 4u * kstep_b;
+    const bool tr = g.trace != nullptr && blockIdx.x == 0 && issuer && pipe == 0;
+    auto mma1 = [&](uint32_t d, uint32_t alo, uint32_t blo, uint32_t idesc, uint32_t acc) {
+      tc_mma(d, ((uint64_t)a_hi << 32) | alo, ((uint64_t)b_hi << 32) | blo, idesc, acc);
+    };
+    // running ring state (no divisions in the loop): input slot + its phase, newest TMEM block + its phase
+    int slot = 0, pos = 0;
+    uint32_t fphase = 0;
+    int blkC = 0;
+    uint32_t cphase = 1;  // parity to wait for on tempty[blkC]: the first round passes
+    for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
       const StUnit t = st_unit_of(g, u);
       const int rows_in = t.rows_out + 2;
+      int blkA = 0, blkB = 0;  // blocks of output rows jj-2, jj-1 (stack positions 0, 1); blkC: row jj (position 2)
       for (int jj = 0; ok && jj < rows_in; ++jj) {
-        if (issuer) trace(g, 0, pos, 0);
-        const int slot = pos % S;
-        ok = mbar_wait(bar(ST_BAR_FULL + slot), (uint32_t)(pos / S) & 1u, abort_flag, g.status, 2);
-        if (!ok) break;
-        const bool fresh = jj < t.rows_out;
-        if (fresh) {
-          const int ob = ob0 + jj;
-          ok = mbar_wait(bar(ST_BAR_TEMPTY + ob % NB), ((uint32_t)(ob / NB) & 1u) ^ 1u, abort_flag, g.status, 3);
+        const bool vA = jj >= 2, vB = jj >= 1 && jj <= t.rows_out, vC = jj < t.rows_out;
+        if (vC) {
+          ok = mbar_wait(bar(ST_BAR_TEMPTY + bofs + blkC), cphase, abort_flag, g.status, 3);
           if (!ok) break;
         }
-        if (issuer) trace(g, 0, pos, 1);
-        tc_fence_after();
-        // runs of TMEM blocks this input row adds into: outputs i in [i_lo, i_hi], stack index i - (jj - 2)
-        const int i_lo = max(jj - 2, 0), i_hi = min(jj, t.rows_out - 1);
-        Run runF[3] = {}, runR[3] = {};  // first MMA of the row (fresh block on its own) / all other MMAs
-        int nF = 0, nR = 0;
-        {
-          int startF = i_lo, startR = i_lo;
-          for (int i = i_lo; i <= i_hi + 1; ++i) {
-            const bool end = i > i_hi;
-            const int blk = (ob0 + i) % NB;
-            const bool wrap = !end && i > i_lo && blk == 0;
-            const bool cutR = end || wrap || (i - startR >= maxrun);
-            const bool cutF = end || wrap || (i - startF >= maxrun) || (fresh && i == jj && i > startF);
-            if (cutR && i > startR) {
-              runR[nR].col = (uint32_t)(((ob0 + startR) % NB) * N);
-              runR[nR].boff = (uint32_t)((startR - (jj - 2)) * N);
-              runR[nR].idesc = idesc0 | ((uint32_t)(((i - startR) * N) >> 3) << 17);
-              runR[nR].acc = 1u;
-              ++nR;
-              startR = i;
-            }
-            if (cutF && i > startF) {
-              runF[nF].col = (uint32_t)(((ob0 + startF) % NB) * N);
-              runF[nF].boff = (uint32_t)((startF - (jj - 2)) * N);
-              runF[nF].idesc = idesc0 | ((uint32_t)(((i - startF) * N) >> 3) << 17);
-              runF[nF].acc = (fresh && startF == jj) ? 0u : 1u;
-              ++nF;
-              startF = i;
-            }
+        auto mk = [&](int sidx, int len, uint32_t acc) {
+          Run r;
+          const int blk = sidx == 0 ? blkA : (sidx == 1 ? blkB : blkC);
+          r.col = tmem_base + (uint32_t)(blk * N);
+          r.boff = (uint32_t)sidx * N16;
+          r.idesc = idesc0 | ((uint32_t)((len * N) >> 3) << 17);
+          r.acc = acc;
+          return r;
+        };
+        // runs of neighbouring blocks one MMA can cover: R* for every MMA of the row but the
+        // first, F* for the first one (the fresh block C on its own, overwriting); acc == 2: unused
+        Run R0 = {0, 0, 0, 2}, R1 = R0, R2 = R0, F0 = R0, F1 = R0, F2 = R0;
+        if (vA && vB && vC && blkB != 0 && blkC != 0 && three) {  // the common case
+          R0 = mk(0, 3, 1);
+          F0 = mk(0, 2, 1);
+          F1 = mk(2, 1, 0);
+        } else {
+          const bool mAB = vA && vB && blkB != 0 && two;
+          const bool mBC = vB && vC && blkC != 0 && two && (!mAB || three);
+          if (mAB && mBC) {
+            R0 = mk(0, 3, 1);
+          } else if (mAB) {
+            R0 = mk(0, 2, 1);
+            if (vC) R1 = mk(2, 1, 1);
+          } else if (mBC) {
+            if (vA) { R0 = mk(0, 1, 1); R1 = mk(1, 2, 1); } else { R0 = mk(1, 2, 1); }
+          } else {
+            if (vA) R0 = mk(0, 1, 1);
+            if (vB) { if (vA) R1 = mk(1, 1, 1); else R0 = mk(1, 1, 1); }
+            if (vC) { if (vA && vB) R2 = mk(2, 1, 1); else if (vA || vB) R1 = mk(2, 1, 1); else R0 = mk(2, 1, 1); }
+          }
+          if (mAB) {
+            F0 = mk(0, 2, 1);
+            if (vC) F1 = mk(2, 1, 0);
+          } else {
+            if (vA) F0 = mk(0, 1, 1);
+            if (vB) { if (vA) F1 = mk(1, 1, 1); else F0 = mk(1, 1, 1); }
+            if (vC) { if (vA && vB) F2 = mk(2, 1, 0); else if (vA || vB) F1 = mk(2, 1, 0); else F0 = mk(2, 1, 0); }
           }
         }
-        const uint32_t row_lo = (((slots_addr + (uint32_t)slot * slot_bytes) & 0x3FFFFu) >> 4) | a_lo0;
-        const Run R0 = runR[0], R1 = runR[1], R2 = runR[2];
-        if (i_hi >= i_lo) {
+        const bool oneR = R1.acc == 2;
+        for (int gi = 0; ok && gi < g.G; ++gi) {
+          if (tr) trace(g, 0, pos, 0);
+          ok = mbar_wait(bar(ST_BAR_FULL + bofs + slot), fphase, abort_flag, g.status, 2);
+          if (!ok) break;
+          if (tr) trace(g, 0, pos, 1);
+          tc_fence_after();
+          if (issuer && !(g.skip & 2)) {
+            // lane 0 alone walks the taps; per MMA: one or two adds, the descriptor words, the instruction
+            const uint32_t row_lo = (((slots_addr + (uint32_t)slot * slot_bytes) & 0x3FFFFu) >> 4) | a_lo0;
+            const int nk16 = g.gch[gi] >> 1;
+            const uint32_t wgrp = (uint32_t)g.gc0[gi] * 3u * N16;  // group's first chunk, in 16 byte units
 #pragma unroll
-          for (int dx = 0; dx < 3; ++dx) {
-            uint32_t b_lo = (((w_addr + (uint32_t)dx * wdx_bytes) & 0x3FFFFu) >> 4) | b_lo0;
-            uint32_t a_lo = row_lo + (uint32_t)dx;
+            for (int dx = 0; dx < 3; ++dx) {
+              uint32_t b_lo = ((((w_addr + (uint32_t)dx * wdx_bytes) & 0x3FFFFu) >> 4) + wgrp) | b_lo0;
+              uint32_t a_lo = row_lo + (uint32_t)dx;
+              int kc = 0;
+              if (gi == 0 && dx == 0) {
+                if (F0.acc != 2) mma1(F0.col, a_lo, b_lo + F0.boff, F0.idesc, F0.acc);
+                if (F1.acc != 2) mma1(F1.col, a_lo, b_lo + F1.boff, F1.idesc, F1.acc);
+                if (F2.acc != 2) mma1(F2.col, a_lo, b_lo + F2.boff, F2.idesc, F2.acc);
+                b_lo += kstep_b;
+                a_lo += kstep_a;
+                kc = 1;
+              }
+              if (oneR) {
+                uint32_t b0 = b_lo + R0.boff;
+                for (; kc + 4 <= nk16; kc += 4) {
+                  mma1(R0.col, a_lo, b0, R0.idesc, 1u);
+                  mma1(R0.col, a_lo + kstep_a, b0 + kstep_b, R0.idesc, 1u);
+                  mma1(R0.col, a_lo + 2u * kstep_a, b0 + kb2, R0.idesc, 1u);
+                  mma1(R0.col, a_lo + 3u * kstep_a, b0 + kb3, R0.idesc, 1u);
+                  a_lo += 4u * kstep_a;
+                  b0 += kb4;
+                }
+                for (; kc < nk16; ++kc) {
+                  mma1(R0.col, a_lo, b0, R0.idesc, 1u);
+                  a_lo += kstep_a;
+                  b0 += kstep_b;
+                }
+              } else {
 #pragma unroll 1
-            for (int kc = 0; kc < nk16; ++kc) {
-              const bool firstmma = dx == 0 && kc == 0;
-              if (issuer && !(g.skip & 2)) {
-                const uint64_t adesc = ((uint64_t)a_hi << 32) | a_lo;
-                if (firstmma) {
-                  for (int q = 0; q < nF; ++q)
-                    tc_mma(tmem_base + runF[q].col, adesc, ((uint64_t)b_hi << 32) | (b_lo + runF[q].boff),
-                           runF[q].idesc, runF[q].acc);
-                } else {
-                  tc_mma(tmem_base + R0.col, adesc, ((uint64_t)b_hi << 32) | (b_lo + R0.boff), R0.idesc, 1u);
-                  if (nR > 1) tc_mma(tmem_base + R1.col, adesc, ((uint64_t)b_hi << 32) | (b_lo + R1.boff), R1.idesc, 1u);
-                  if (nR > 2) tc_mma(tmem_base + R2.col, adesc, ((uint64_t)b_hi << 32) | (b_lo + R2.boff), R2.idesc, 1u);
+                for (; kc < nk16; ++kc) {
+                  mma1(R0.col, a_lo, b_lo + R0.boff, R0.idesc, 1u);
+                  mma1(R1.col, a_lo, b_lo + R1.boff, R1.idesc, 1u);
+                  if (R2.acc != 2) mma1(R2.col, a_lo, b_lo + R2.boff, R2.idesc, 1u);
+                  b_lo += kstep_b;
+                  a_lo += kstep_a;
                 }
               }
-              b_lo += kstep_b;
-              a_lo += kstep_a;
             }
           }
+          if (issuer) {
+            if (tr) trace(g, 0, pos, 2);
+            tc_commit(bar(ST_BAR_EMPTY + bofs + slot));
+            if (gi == g.G - 1 && vA) tc_commit(bar(ST_BAR_TFULL + bofs + blkA));
+            if (tr) trace(g, 0, pos, 3);
+          }
+          ++pos;
+          if (++slot == S) {
+            slot = 0;
+            fphase ^= 1u;
+          }
         }
-        if (issuer) {
-          trace(g, 0, pos, 2);
-          tc_commit(bar(ST_BAR_EMPTY + slot));
-          if (jj >= 2) tc_commit(bar(ST_BAR_TFULL + (ob0 + jj - 2) % NB));
-          trace(g, 0, pos, 3);
+        blkA = blkB;
+        blkB = blkC;
+        if (vC) {
+          if (++blkC == NB) {
+            blkC = 0;
+            cphase ^= 1u;
+          }
         }
-        ++pos;
-      }
-      ob0 += t.rows_out;
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    // ---------------- weights (resident) ----------------
-    if (lane == 0) {
-      const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(g.w);
-      mbar_expect_tx(bar(ST_BAR_WRES), wdx_bytes * 3u);
-      // copies of at most 32 KB each
-      const uint32_t total = wdx_bytes * 3u;
-      for (uint32_t off = 0; off < total; off += 32768u) {
-        const uint32_t n = min(32768u, total - off);
-        bulk_g2s(w_addr + off, wsrc + off, n, bar(ST_BAR_WRES));
       }
     }
     __syncwarp();
-  } else if (warp < 10) {
-    // ---------------- epilogue: two teams of four warps, alternate row pairs ----------------
+  } else if (warp >= 2 && warp < 10) {
+    // ---------------- epilogue: two teams of four warps ----------------
+    // P == 2: team t drains pipeline t.  P == 1: the teams take alternate row pairs.
     const int team = (warp - 2) >> 2;
+    const int pipe = P == 2 ? team : 0;
+    const int bofs = pipe * ST_PIPE_STRIDE;
+    const uint32_t tmem_base = tmem_base0 + (uint32_t)(pipe * NB * N);
     const int q = warp & 3;
     const int m = q * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const bool tr = g.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64;
     bool ok = true;
-    int ob0 = 0, item = 0;
-    for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
+    int item = 0;
+    int blk = 0;
+    uint32_t tphase = 0;  // parity of tfull[blk] for the current round of the ring
+    for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
       const StUnit t = st_unit_of(g, u);
       const int x = t.x0 + m;
       const bool xin = x < g.W;
       for (int i = 0; ok && i < t.rows_out; i += 2, ++item) {
-        if ((item & 1) != team) continue;
         const int nrows = min(2, t.rows_out - i);
-        const int ob = ob0 + i;
-        const int b0 = ob % NB, b1 = (ob + 1) % NB;
-        if (threadIdx.x == 64) trace(g, 1, item >> 1, 0);
-        ok = mbar_wait(bar(ST_BAR_TFULL + b0), (uint32_t)(ob / NB) & 1u, abort_flag, g.status, 6);
-        if (ok && nrows == 2)
-          ok = mbar_wait(bar(ST_BAR_TFULL + b1), (uint32_t)((ob + 1) / NB) & 1u, abort_flag, g.status, 6);
+        // blocks and phases of this item's rows; the ring state advances for every item, taken or not
+        const int b0 = blk;
+        const uint32_t ph0 = tphase;
+        if (++blk == NB) { blk = 0; tphase ^= 1u; }
+        const int b1 = blk;
+        const uint32_t ph1 = tphase;
+        if (nrows == 2) {
+          if (++blk == NB) { blk = 0; tphase ^= 1u; }
+        }
+        if (P == 1 && (item & 1) != team) continue;
+        if (tr) trace(g, 1, item >> 1, 0);
+        ok = mbar_wait<64>(bar(ST_BAR_TFULL + bofs + b0), ph0, abort_flag, g.status, 6);
+        if (ok && nrows == 2) ok = mbar_wait<64>(bar(ST_BAR_TFULL + bofs + b1), ph1, abort_flag, g.status, 6);
         if (!ok) break;
-        if (threadIdx.x == 64) trace(g, 1, item >> 1, 1);
+        if (tr) trace(g, 1, item >> 1, 1);
         tc_fence_after();
         const int y = t.y0 + i;
         const uint32_t t0 = lane_addr + (uint32_t)(b0 * N), t1 = lane_addr + (uint32_t)(b1 * N);
-        int c0 = 0;
+        int c0 = (g.skip & 8) ? N : 0;
         if (nrows == 2) {
 #pragma unroll 1
-          for (; c0 + 32 <= N; c0 += 32) epilogue_block<32, 2>(g, t0, t1, c0, x, y, xin, lane);
-          if (c0 < N) epilogue_block<16, 2>(g, t0, t1, c0, x, y, xin, lane);
+          for (; c0 + 32 <= N; c0 += 32) epi_fast<32, 2, EPI>(g, t0, t1, c0, x, y, xin, lane);
+          if (c0 < N) epi_fast<16, 2, EPI>(g, t0, t1, c0, x, y, xin, lane);
         } else {
 #pragma unroll 1
-          for (; c0 + 32 <= N; c0 += 32) epilogue_block<32, 1>(g, t0, t1, c0, x, y, xin, lane);
-          if (c0 < N) epilogue_block<16, 1>(g, t0, t1, c0, x, y, xin, lane);
+          for (; c0 + 32 <= N; c0 += 32) epi_fast<32, 1, EPI>(g, t0, t1, c0, x, y, xin, lane);
+          if (c0 < N) epi_fast<16, 1, EPI>(g, t0, t1, c0, x, y, xin, lane);
         }
-        if (threadIdx.x == 64) trace(g, 1, item >> 1, 2);
+        if (tr) trace(g, 1, item >> 1, 2);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(bar(ST_BAR_TEMPTY + b0));
-          if (nrows == 2) mbar_arrive(bar(ST_BAR_TEMPTY + b1));
+          mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b0));
+          if (nrows == 2) mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b1));
         }
       }
-      ob0 += t.rows_out;
     }
-  } else {
-    // ---------------- input slots (same scheme as the pass kernel) ----------------
-    const int tid = threadIdx.x - 10 * 32;
+  } else if (warp >= 10) {
+    // ---------------- input slots ----------------
+    // P == 2: warps 10, 11 feed pipeline 0 and warps 12, 13 pipeline 1; P == 1: all four feed pipeline 0.
+    const int pipe = P == 2 ? (warp - 10) >> 1 : 0;
+    const int bofs = pipe * ST_PIPE_STRIDE;
+    const uint32_t slots_addr = slots_addr0 + (uint32_t)(pipe * S) * slot_bytes;
+    const int nprod = nprod_warps * 32;
+    const int tid = threadIdx.x - (10 + pipe * nprod_warps * (P == 2 ? 1 : 0)) * 32;
     bool ok = true;
-    int pos = 0, signalled = 0;
-    const int D = g.D;
-    if (g.cpa || tid == 0) {
-      for (int u = blockIdx.x; ok && u < g.nunits; u += gridDim.x) {
+    if (!g.cpa) {
+      // everything comes by TMA: one thread per pipeline, one or two copies per entry
+      if (tid == 0) {
+        int slot = 0, pcount = 0;
+        uint32_t phase = 1;  // parity to wait for on the empty barrier: first round passes
+        const int nca = g.a.nch;
+        const bool tr = g.trace != nullptr && blockIdx.x == 0 && pipe == 0;
+        for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
+          const StUnit t = st_unit_of(g, u);
+          for (int jj = 0; ok && jj < t.rows_out + 2; ++jj) {
+            const int iy = t.y0 - 1 + jj;
+            for (int gi = 0; ok && gi < g.G; ++gi) {
+              if (tr) trace(g, 2, pcount, 0);
+              ok = mbar_wait<64>(bar(ST_BAR_EMPTY + bofs + slot), phase, abort_flag, g.status, 7);
+              if (!ok) break;
+              if (tr) trace(g, 2, pcount, 1);
+              const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes;
+              const uint32_t fb = bar(ST_BAR_FULL + bofs + slot);
+              const int c_lo = g.gc0[gi], c_hi = c_lo + g.gch[gi];
+              mbar_expect_tx(fb, (uint32_t)g.gch[gi] * CHUNK_PITCH);
+              if (!(g.skip & 1)) {
+                for (int c = c_lo; c < min(c_hi, nca); c += g.a.tbox)
+                  tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, t.x0 - 1, c, iy, fb);
+                for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
+                  tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, t.x0 - 1, c - nca, iy, fb);
+              } else {
+                // timing aid: nothing will land, so complete the transaction count by hand
+                asm volatile("mbarrier.complete_tx.shared::cta.b64 [%0], %1;" ::"r"(fb),
+                             "r"((uint32_t)g.gch[gi] * CHUNK_PITCH)
+                             : "memory");
+              }
+              if (tr) trace(g, 2, pcount, 2);
+              ++pcount;
+              if (++slot == S) {
+                slot = 0;
+                phase ^= 1u;
+              }
+            }
+          }
+        }
+      }
+    } else {
+      // some rows need the producer warps: all threads of the pipeline's producer warps walk the entries,
+      // thread 0 also issues the TMA part; each thread keeps up to D rows of cp.async in flight
+      int pos = 0, signalled = 0;
+      const int D = g.D;
+      for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
         const StUnit t = st_unit_of(g, u);
         for (int jj = 0; ok && jj < t.rows_out + 2; ++jj) {
           const int iy = t.y0 - 1 + jj;
-          const int slot = pos % S;
-          if (tid == 0) trace(g, 2, pos, 0);
-          ok = mbar_wait(bar(ST_BAR_EMPTY + slot), ((uint32_t)(pos / S) & 1u) ^ 1u, abort_flag, g.status, 7);
-          if (!ok) break;
-          if (tid == 0) trace(g, 2, pos, 1);
-          const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes;
-          if (tid == 0) {
-            const uint32_t fb = bar(ST_BAR_FULL + slot);
-            const uint32_t bytes = (g.skip & 1) ? 0u : tma_row<false>(g, slot_addr, iy, t.x0, 0, nch, fb);
-            if (bytes) {
-              mbar_expect_tx(fb, bytes);
-              tma_row<true>(g, slot_addr, iy, t.x0, 0, nch, fb);
-            } else {
-              mbar_arrive(fb);
+          for (int gi = 0; ok && gi < g.G; ++gi) {
+            const int c_lo = g.gc0[gi], c_hi = c_lo + g.gch[gi];
+            const int slot = pos % S;
+            ok = mbar_wait<64>(bar(ST_BAR_EMPTY + bofs + slot), ((uint32_t)(pos / S) & 1u) ^ 1u, abort_flag, g.status, 7);
+            if (!ok) break;
+            const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes;
+            if (tid == 0) {
+              const uint32_t fb = bar(ST_BAR_FULL + bofs + slot);
+              const uint32_t bytes = (g.skip & 1) ? 0u : tma_row<false>(g, slot_addr, iy, t.x0, c_lo, c_hi, fb);
+              if (bytes) {
+                mbar_expect_tx(fb, bytes);
+                tma_row<true>(g, slot_addr, iy, t.x0, c_lo, c_hi, fb);
+              } else {
+                mbar_arrive(fb);
+              }
             }
-          }
-          if (g.cpa) {
-            if (!(g.skip & 1)) load_row(g, slot_addr, iy, t.x0, tid, 0, nch);
+            if (!(g.skip & 1)) load_row(g, slot_addr, iy, t.x0, tid, nprod, c_lo, c_hi);
             cp_async_commit();
             ++pos;
             if (pos - signalled >= D) {
               cp_async_wait_dyn(D - 1);
               fence_proxy_async();
               __syncwarp();
-              if (lane == 0) mbar_arrive(bar(ST_BAR_FULL + signalled % S));
+              if (lane == 0) mbar_arrive(bar(ST_BAR_FULL + bofs + signalled % S));
               ++signalled;
             }
-          } else {
-            ++pos;
           }
-          if (tid == 0) trace(g, 2, pos - 1, 2);
         }
       }
-      if (g.cpa) {
-        cp_async_wait<0>();
-        if (ok) {
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0)
-            for (; signalled < pos; ++signalled) mbar_arrive(bar(ST_BAR_FULL + signalled % S));
-        }
+      cp_async_wait<0>();
+      if (ok) {
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0)
+          for (; signalled < pos; ++signalled) mbar_arrive(bar(ST_BAR_FULL + bofs + signalled % S));
       }
     }
   }
@@ -1047,7 +1250,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   tc_fence_after();
   if (warp == 0) {
     __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(g.tmem_cols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base0), "r"(g.tmem_cols) : "memory");
   }
 }
 
@@ -1094,12 +1297,12 @@ EncodeTiledFn encode_fn() {
 }
 
 // H x W x C binary16 tensor as (8, W, C/8, H) with strides (2, 2C, 16, 2WC) bytes; box (8, 132, 2, 1).
-int make_tensor_map(CUtensorMap *tm, const void *ptr, int H, int W, int C) {
+int make_tensor_map(CUtensorMap *tm, const void *ptr, int H, int W, int C, int box_chunks) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return DNXCU_E_CUDA;
   const cuuint64_t dims[4] = {8, (cuuint64_t)W, (cuuint64_t)(C / 8), (cuuint64_t)H};
   const cuuint64_t strides[3] = {(cuuint64_t)C * 2, 16, (cuuint64_t)W * C * 2};
-  const cuuint32_t box[4] = {8, (cuuint32_t)WH, 2, 1};
+  const cuuint32_t box[4] = {8, (cuuint32_t)WH, (cuuint32_t)box_chunks, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -1109,40 +1312,66 @@ int make_tensor_map(CUtensorMap *tm, const void *ptr, int H, int W, int C) {
 
 // Plan of the stacked form: weights resident, one K group, TMEM ring of NB blocks.
 // Expects pl.args filled up to the operand description (done by make_plan).
-int make_plan_stack(const dnxcu_dispatch &d, Plan &pl, bool encode) {
+int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode) {
   TcArgs &g = pl.args;
   const int W = g.W, H = g.H;
   if (g.N > 128) return DNXCU_E_UNSUPPORTED;
   g.Ns = g.N;
-  g.NB = 512 / g.N;
-  if (g.NB > ST_MAX_BLOCKS) g.NB = ST_MAX_BLOCKS;
-  uint32_t p2 = 32;
-  while (p2 < (uint32_t)(g.NB * g.N)) p2 <<= 1;
-  g.tmem_cols = p2;
   g.wstream = 0;
-  g.G = 1;
   const int nch = g.a.nch + g.b.nch;
-  g.gc0[0] = 0;
-  g.gch[0] = nch;
-  for (int i = 1; i < MAX_GROUPS; ++i) g.gc0[i] = g.gch[i] = 0;
-  g.gmax = nch;
+  // K groups cost nothing here (every input row is used once): a slot holds one group of one row
+  g.G = v.p1 > 0 ? v.p1 : 1;
+  if (g.G > MAX_GROUPS) g.G = MAX_GROUPS;
+  if (g.G * 2 > nch) g.G = nch / 2;
+  {
+    int per = (nch + g.G - 1) / g.G;
+    per += per & 1;
+    int c = 0, gi = 0;
+    for (; gi < MAX_GROUPS && c < nch; ++gi) {
+      g.gc0[gi] = c;
+      g.gch[gi] = (nch - c < per) ? nch - c : per;
+      c += g.gch[gi];
+    }
+    g.G = gi;
+    for (; gi < MAX_GROUPS; ++gi) g.gc0[gi] = g.gch[gi] = 0;
+    g.gmax = per < nch ? per : nch;
+  }
+  // one TMA copy per operand and row when a slot holds all channels, else two chunks per copy
+  g.a.tbox = (g.G == 1) ? g.a.nch : 2;
+  g.b.tbox = (g.G == 1 && g.b.nch) ? g.b.nch : 2;
   const size_t wbytes = (size_t)9 * nch * g.N * 16;
   if (wbytes >= (1u << 20)) return DNXCU_E_UNSUPPORTED;
   const size_t wregion = (wbytes + 127) & ~(size_t)127;
-  const size_t slot_bytes = (size_t)nch * CHUNK_PITCH;
+  const size_t slot_bytes = (size_t)g.gmax * CHUNK_PITCH;
   if (HEADER_BYTES + wregion + 4 * slot_bytes > SMEM_LIMIT) return DNXCU_E_UNSUPPORTED;
-  int S = (int)((SMEM_LIMIT - HEADER_BYTES - wregion) / slot_bytes);
-  if (S > MAX_SLOTS) S = MAX_SLOTS;
-  g.S = S;
-  g.D = S - 1 < MAX_DEPTH ? S - 1 : MAX_DEPTH;
-  pl.smem = HEADER_BYTES + wregion + (size_t)S * slot_bytes;
+  const int total_slots = (int)((SMEM_LIMIT - HEADER_BYTES - wregion) / slot_bytes);
   g.nstrips = (W + STRIP - 1) / STRIP;
+  // two pipelines when each can have four TMEM blocks and four input slots, and the image has work for both
+  const char *np = getenv("DNXCU_TC_PIPES");
+  int P = (4 * g.N <= 256 && total_slots >= 8 && g.nstrips * ((H + 1) / 2) >= 2) ? 2 : 1;
+  if (np && np[0] == '1') P = 1;
+  g.P = P;
+  if (P == 2) {
+    g.NB = 256 / g.N;
+    if (g.NB > ST_PIPE_STRIDE) g.NB = ST_PIPE_STRIDE;
+    g.S = total_slots / 2 < ST_PIPE_STRIDE ? total_slots / 2 : ST_PIPE_STRIDE;
+  } else {
+    g.NB = 512 / g.N;
+    if (g.NB > ST_MAX_BLOCKS) g.NB = ST_MAX_BLOCKS;
+    g.S = total_slots < MAX_SLOTS ? total_slots : MAX_SLOTS;
+  }
+  uint32_t p2 = 32;
+  while (p2 < (uint32_t)(P * g.NB * g.N)) p2 <<= 1;
+  g.tmem_cols = p2;
+  g.D = g.S - 1 < MAX_DEPTH ? g.S - 1 : MAX_DEPTH;
+  pl.smem = HEADER_BYTES + wregion + (size_t)P * g.S * slot_bytes;
   const int sms = sm_count();
+  const int lanes = sms * P;
   double best = 1e30;
   int bestRB = 2;
   for (int rb = 2; rb <= 64; rb += 2) {
     const long long units = (long long)g.nstrips * ((H + rb - 1) / rb);
-    const long long waves = (units + sms - 1) / sms;
+    const long long waves = (units + lanes - 1) / lanes;
     const double cost = (double)waves * (rb + 2.5);
     if (cost < best - 1e-9) {
       best = cost;
@@ -1151,13 +1380,14 @@ int make_plan_stack(const dnxcu_dispatch &d, Plan &pl, bool encode) {
   }
   g.RB = bestRB;
   g.nunits = g.nstrips * ((H + g.RB - 1) / g.RB);
-  pl.grid = g.nunits < sms ? g.nunits : sms;
+  const int ctas = (g.nunits + P - 1) / P;
+  pl.grid = ctas < sms ? ctas : sms;
   pl.R = 0;
   memset(&g.tm_a, 0, sizeof(g.tm_a));
   memset(&g.tm_b, 0, sizeof(g.tm_b));
   if (encode) {
-    if (g.a.tma && make_tensor_map(&g.tm_a, d.in_a, H, W, d.c_a)) return DNXCU_E_CUDA;
-    if (g.b.tma && make_tensor_map(&g.tm_b, d.in_b, H, W, d.c_b)) return DNXCU_E_CUDA;
+    if (g.a.tma && make_tensor_map(&g.tm_a, d.in_a, H, W, d.c_a, g.a.tbox)) return DNXCU_E_CUDA;
+    if (g.b.tma && make_tensor_map(&g.tm_b, d.in_b, H, W, d.c_b, g.b.tbox)) return DNXCU_E_CUDA;
   }
   return DNXCU_OK;
 }
@@ -1189,8 +1419,8 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode) 
     return DNXCU_E_MISALIGNED;
 
   TcArgs &g = pl.args;
-  g.a = {(const __half *)d.in_a, (const __half *)d.halo[0], (const __half *)d.halo[1], d.c_a, nch_of(d.c_a), up ? 1 : 0, 0};
-  g.b = {(const __half *)d.in_b, (const __half *)d.halo[2], (const __half *)d.halo[3], d.c_b, nch_of(d.c_b), 0, 0};
+  g.a = {(const __half *)d.in_a, (const __half *)d.halo[0], (const __half *)d.halo[1], d.c_a, nch_of(d.c_a), up ? 1 : 0, 0, 2};
+  g.b = {(const __half *)d.in_b, (const __half *)d.halo[2], (const __half *)d.halo[3], d.c_b, nch_of(d.c_b), 0, 0, 2};
   // TMA takes the operands whose pixels are whole 16 byte chunks at full resolution
   const char *notma = getenv("DNXCU_TC_NO_TMA");
   const bool allow_tma = !(notma && notma[0] == '1');
@@ -1221,7 +1451,7 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode) 
   const char *tr = getenv("DNXCU_TC_TRACE");
   g.trace = (tr && tr[0] == '1' && d.device_status) ? reinterpret_cast<long long *>(d.device_status) + 8 : nullptr;
 
-  if (R == 0) return make_plan_stack(d, pl, encode);
+  if (R == 0) return make_plan_stack(v, d, pl, encode);
   uint32_t cols = 2u * R * g.Ns;
   if (cols > 512) return DNXCU_E_UNSUPPORTED;
   uint32_t p2 = 32;
@@ -1287,8 +1517,8 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode) 
   memset(&g.tm_a, 0, sizeof(g.tm_a));
   memset(&g.tm_b, 0, sizeof(g.tm_b));
   if (encode) {
-    if (g.a.tma && make_tensor_map(&g.tm_a, d.in_a, H, W, d.c_a)) return DNXCU_E_CUDA;
-    if (g.b.tma && make_tensor_map(&g.tm_b, d.in_b, H, W, d.c_b)) return DNXCU_E_CUDA;
+    if (g.a.tma && make_tensor_map(&g.tm_a, d.in_a, H, W, d.c_a, g.a.tbox)) return DNXCU_E_CUDA;
+    if (g.b.tma && make_tensor_map(&g.tm_b, d.in_b, H, W, d.c_b, g.b.tbox)) return DNXCU_E_CUDA;
   }
   return DNXCU_OK;
 }
@@ -1309,17 +1539,31 @@ int launch_r(const Plan &pl, cudaStream_t s) {
   return DNXCU_OK;
 }
 
-int launch_stack(const Plan &pl, cudaStream_t s) {
+template <int EPI>
+int launch_stack_epi(const Plan &pl, cudaStream_t s) {
   static bool attr_done[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 16 || !attr_done[dev]) {
-    DNXCU_CUDA(cudaFuncSetAttribute(conv3x3_tc_stack, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
+    DNXCU_CUDA(cudaFuncSetAttribute(conv3x3_tc_stack<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
     if (dev < 16) attr_done[dev] = true;
   }
-  conv3x3_tc_stack<<<pl.grid, ST_THREADS, pl.smem, s>>>(pl.args);
+  conv3x3_tc_stack<EPI><<<pl.grid, ST_THREADS, pl.smem, s>>>(pl.args);
   DNXCU_CUDA(cudaGetLastError());
   return DNXCU_OK;
+}
+
+int launch_stack(const Plan &pl, cudaStream_t s) {
+  const TcArgs &g = pl.args;
+  const int epi = (g.bias ? EPI_BIAS : 0) | (g.relu ? EPI_RELU : 0) | (g.pool ? EPI_POOL : 0) | (g.full_out ? EPI_FULL : 0);
+  switch (epi) {
+#define DNXCU_EPI_CASE(E) case E: return launch_stack_epi<E>(pl, s);
+    DNXCU_EPI_CASE(8) DNXCU_EPI_CASE(9) DNXCU_EPI_CASE(10) DNXCU_EPI_CASE(11)
+    DNXCU_EPI_CASE(4) DNXCU_EPI_CASE(5) DNXCU_EPI_CASE(6) DNXCU_EPI_CASE(7)
+    DNXCU_EPI_CASE(12) DNXCU_EPI_CASE(13) DNXCU_EPI_CASE(14) DNXCU_EPI_CASE(15)
+#undef DNXCU_EPI_CASE
+    default: return DNXCU_E_BAD_ARG;
+  }
 }
 
 }  // namespace

@@ -184,7 +184,7 @@ def test_prepare_weights_stacked_layout():
     """DY=stack: [dx][chunk][3N rows][8], rows of a chunk = vertical taps r = 2, 1, 0."""
     k, ca = 16, 32
     w = nets.rng.he_normal_weights(9, k, ca)
-    vid = lib.find_variant("direct-conv-tc", "DY=stack#W=resident")
+    vid = lib.find_variant("direct-conv-tc", "DY=stack#KG=1#W=resident")
     t = lib.prepare_weights(vid, w, ca).view(np.float16).reshape(3, 4, 3, 16, 8)
     for sx in range(3):
         for r in range(3):
