@@ -90,6 +90,7 @@ static const Variant kVariants[] = {
     {{13, DNXCU_OP_CONCAT, "copy-transform", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_CONCAT, 1, 0, 0, 0},
     {{14, DNXCU_OP_RELU, "basic-activation", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_RELU, 8, 0, 0, 0},
     {{15, DNXCU_OP_RELU, "basic-activation", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_RELU, 1, 0, 0, 0},
+    {{16, DNXCU_OP_PAD_CHANNELS, "copy-transform", "PAD=8", 0, 0, 1, 8, 65536, 0}, VK_PADC, 1, 0, 0, 0},
 };
 static const int kVariantCount = (int)(sizeof(kVariants) / sizeof(kVariants[0]));
 
@@ -170,6 +171,11 @@ int dnxcu_validate(const dnxcu_dispatch *d) {
     default:
       if (!d->in_a || !d->out || d->c_a <= 0 || !d->pc[0] || !d->pc[1]) return DNXCU_E_BAD_ARG;
       if (v->kind == VK_CONCAT && (!d->in_b || d->c_b <= 0)) return DNXCU_E_BAD_ARG;
+      if (v->kind == VK_PADC) {
+        if (d->c_out < d->c_a || d->c_out % 8) return DNXCU_E_BAD_ARG;
+        if (((uintptr_t)d->out & 15) || ((uintptr_t)d->in_a & 1)) return DNXCU_E_MISALIGNED;
+        return DNXCU_OK;
+      }
       if (v->p0 == 8) {
         if (v->kind == VK_RELU) {
           if (((uint64_t)d->pc[0] * d->pc[1] * d->c_a) % 8) return DNXCU_E_UNSUPPORTED;
@@ -231,6 +237,7 @@ int dnxcu_cost(const dnxcu_dispatch *d, uint64_t *rd, uint64_t *wr, uint64_t *fl
     case DNXCU_OP_UPSAMPLE2X: r = 2 * P * d->c_a; w = 8 * P * d->c_a; break;
     case DNXCU_OP_CONCAT: r = 2 * P * ((uint64_t)d->c_a + d->c_b); w = r; break;
     case DNXCU_OP_RELU: r = 2 * P * d->c_a; w = r; break;
+    case DNXCU_OP_PAD_CHANNELS: r = 2 * P * d->c_a; w = 2 * P * d->c_out; break;
     default: return DNXCU_E_BAD_ARG;
   }
   if (rd) *rd = r;

@@ -101,6 +101,8 @@ struct TcArgs {
   int cpa;               // producer warps copy part of the rows (cp.async) besides TMA
   int NB;                // stacked form: accumulator blocks in the TMEM ring (per pipeline)
   int P;                 // stacked form: pipelines per CTA (1 or 2)
+  int stage_pitch;       // stacked form: bytes per pixel row of an epilogue warp's staging tile, 0 = direct stores
+  uint32_t stage_warp_bytes;  // staging bytes per epilogue warp
   uint32_t tmem_cols;
   int desc_swap;  // debugging aid: exchange the two descriptor strides
   long long *trace;  // debugging aid: per role time stamps of CTA 0 (nullptr = off)
@@ -806,6 +808,8 @@ __device__ __forceinline__ void epi_fast(const TcArgs &g, uint32_t t0, uint32_t 
     if constexpr (RSTEP == 2) tc_ld16(t1 + (uint32_t)c0, v1);
   }
   tc_wait_ld();
+  if (g.skip & 16) return;
+  if (g.skip & 4) xin = false;
   uint32_t h0[NC / 2], h1[RSTEP == 2 ? NC / 2 : 1];
   round_row<NC, EPI>(g, v0, c0, h0);
   if constexpr (RSTEP == 2) round_row<NC, EPI>(g, v1, c0, h1);
@@ -877,6 +881,73 @@ struct Run {
   uint32_t idesc;  // instruction descriptor with this run's N'
   uint32_t acc;    // 0: overwrite (fresh block), 1: accumulate
 };
+
+// ---- staged epilogue --------------------------------------------------------
+// A thread owns one pixel after tcgen05.ld, so direct stores put 32 lanes on 32
+// different cache lines (measured: about 170 cycles per store instruction, 2700 of the
+// 3600 cycles of a two row item at 64 channels).  Instead each epilogue warp parks its
+// 32 pixels x K channels in a padded shared memory tile (pitch K*2 + 16 bytes: conflict
+// free for 16 byte accesses) and copies it out with consecutive lanes on consecutive 16
+// byte pieces (512 contiguous bytes per instruction; HWC keeps the 32 pixels contiguous).
+// The 2x2 max pool is taken while copying out, from the two staged rows.
+
+// TMEM -> registers -> (+bias) -> binary16 pairs -> (ReLU) -> this lane's pixel row of the staging tile
+template <int NC, int EPI>
+__device__ __forceinline__ void stage_cols(const TcArgs &g, uint32_t taddr, int c0, uint32_t dst) {
+  uint32_t v[NC];
+  if constexpr (NC == 32) tc_ld32(taddr + (uint32_t)c0, v);
+  else tc_ld16(taddr + (uint32_t)c0, v);
+  tc_wait_ld();
+  uint32_t h[NC / 2];
+  round_row<NC, EPI>(g, v, c0, h);
+#pragma unroll
+  for (int j8 = 0; j8 < NC; j8 += 8)
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (uint32_t)((c0 + j8) * 2)), "r"(h[j8 / 2]),
+                 "r"(h[j8 / 2 + 1]), "r"(h[j8 / 2 + 2]), "r"(h[j8 / 2 + 3])
+                 : "memory");
+}
+
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+// Copies `npx` staged pixels (K channels each) to `dst` (contiguous), lanes on consecutive 16 byte pieces.
+__device__ __forceinline__ void copy_out(uint32_t tile, int pitch, int nck, int npx, __half *dst, int lane) {
+  const int total = npx * nck;
+  int px = lane / nck, ch = lane - px * nck;
+  const int dpx = 32 / nck, dch = 32 - dpx * nck;
+  uint4 *o = reinterpret_cast<uint4 *>(dst);
+  for (int i = lane; i < total; i += 32) {
+    o[i] = lds16(tile + (uint32_t)(px * pitch + ch * 16));
+    px += dpx;
+    ch += dch;
+    if (ch >= nck) { ch -= nck; ++px; }
+  }
+}
+
+__device__ __forceinline__ uint4 hmax8_u(uint4 a, uint4 b) {
+  return make_uint4(hmax2_u32(a.x, b.x), hmax2_u32(a.y, b.y), hmax2_u32(a.z, b.z), hmax2_u32(a.w, b.w));
+}
+
+// 2x2 max of two staged rows (tile0, tile1), `npx` input pixels -> npx / 2 pooled pixels at `dst`.
+__device__ __forceinline__ void copy_out_pooled(uint32_t tile0, uint32_t tile1, int pitch, int nck, int npx,
+                                                __half *dst, int lane) {
+  const int total = (npx >> 1) * nck;
+  int px = lane / nck, ch = lane - px * nck;
+  const int dpx = 32 / nck, dch = 32 - dpx * nck;
+  uint4 *o = reinterpret_cast<uint4 *>(dst);
+  for (int i = lane; i < total; i += 32) {
+    const uint32_t off = (uint32_t)(2 * px * pitch + ch * 16);
+    const uint4 a = hmax8_u(lds16(tile0 + off), lds16(tile0 + off + (uint32_t)pitch));
+    const uint4 b = hmax8_u(lds16(tile1 + off), lds16(tile1 + off + (uint32_t)pitch));
+    o[i] = hmax8_u(a, b);
+    px += dpx;
+    ch += dch;
+    if (ch >= nck) { ch -= nck; ++px; }
+  }
+}
 
 // P = 1 or 2 independent pipelines share the CTA's resident weights: each pipeline has
 // its own MMA issuing warp, its own input slots, half of the TMEM ring, one epilogue
@@ -1100,6 +1171,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     const int m = q * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const bool tr = g.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64;
+    const int pitch = g.stage_pitch;  // 0: no staging tile, direct stores
+    const int nck = g.K >> 3;
+    const uint32_t stage_base = slots_addr0 + (uint32_t)(P * S) * slot_bytes + (uint32_t)(warp - 2) * g.stage_warp_bytes;
     bool ok = true;
     int item = 0;
     int blk = 0;
@@ -1128,6 +1202,60 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         tc_fence_after();
         const int y = t.y0 + i;
         const uint32_t t0 = lane_addr + (uint32_t)(b0 * N), t1 = lane_addr + (uint32_t)(b1 * N);
+        if (pitch) {
+          // staged: all TMEM reads first (the blocks are handed back before the copy-out)
+          const uint32_t tile0 = stage_base, tile1 = stage_base + (uint32_t)(32 * pitch);
+          const uint32_t mine = (uint32_t)(lane * pitch);
+          const int xw = t.x0 + q * 32;                      // first pixel of this warp
+          const int npx = max(0, min(32, g.W - xw));        // pixels of this warp inside the image
+          const bool pool2 = (EPI & EPI_POOL) && nrows == 2;
+          if (!(g.skip & 8)) {
+            for (int r = 0; r < nrows; ++r) {
+              const uint32_t tr_addr = r ? t1 : t0;
+              const uint32_t tile = (pool2 && r) ? tile1 : tile0;
+              int c0 = 0;
+#pragma unroll 1
+              for (; c0 + 32 <= N; c0 += 32) stage_cols<32, EPI>(g, tr_addr, c0, tile + mine);
+              if (c0 < N) stage_cols<16, EPI>(g, tr_addr, c0, tile + mine);
+              if (r == nrows - 1) {
+                // last TMEM read of the item done: give the blocks back
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                  mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b0));
+                  if (nrows == 2) mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b1));
+                }
+              } else {
+                __syncwarp();
+              }
+              if (!pool2) {
+                if ((EPI & EPI_FULL) && !(g.skip & 4))
+                  copy_out(tile, pitch, nck, npx, g.out + ((long long)(y + r) * g.W + xw) * g.K, lane);
+                __syncwarp();
+              }
+            }
+            if (pool2) {
+              if (!(g.skip & 4)) {
+                if (EPI & EPI_FULL) {
+                  copy_out(tile0, pitch, nck, npx, g.out + ((long long)y * g.W + xw) * g.K, lane);
+                  copy_out(tile1, pitch, nck, npx, g.out + ((long long)(y + 1) * g.W + xw) * g.K, lane);
+                }
+                copy_out_pooled(tile0, tile1, pitch, nck, npx,
+                                g.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (xw >> 1)) * g.K, lane);
+              }
+              __syncwarp();
+            }
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b0));
+              if (nrows == 2) mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b1));
+            }
+          }
+          if (tr) trace(g, 1, item >> 1, 2);
+          continue;
+        }
         int c0 = (g.skip & 8) ? N : 0;
         if (nrows == 2) {
 #pragma unroll 1
@@ -1344,7 +1472,21 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   const size_t wregion = (wbytes + 127) & ~(size_t)127;
   const size_t slot_bytes = (size_t)g.gmax * CHUNK_PITCH;
   if (HEADER_BYTES + wregion + 4 * slot_bytes > SMEM_LIMIT) return DNXCU_E_UNSUPPORTED;
-  const int total_slots = (int)((SMEM_LIMIT - HEADER_BYTES - wregion) / slot_bytes);
+  // epilogue staging tiles (8 warps x 32 pixels x (K*2 + 16) bytes, two rows when pooling) if four slots still fit
+  g.stage_pitch = 0;
+  g.stage_warp_bytes = 0;
+  size_t stage_total = 0;
+  const char *nost = getenv("DNXCU_TC_NO_STAGE");
+  if (g.K % 8 == 0 && !(nost && nost[0] == '1')) {
+    const size_t pitch = (size_t)g.K * 2 + 16;
+    const size_t per_warp = (g.pool ? 2 : 1) * 32 * pitch;
+    if (HEADER_BYTES + wregion + 8 * per_warp + 4 * slot_bytes <= SMEM_LIMIT) {
+      g.stage_pitch = (int)pitch;
+      g.stage_warp_bytes = (uint32_t)per_warp;
+      stage_total = 8 * per_warp;
+    }
+  }
+  const int total_slots = (int)((SMEM_LIMIT - HEADER_BYTES - wregion - stage_total) / slot_bytes);
   g.nstrips = (W + STRIP - 1) / STRIP;
   // two pipelines when each can have four TMEM blocks and four input slots, and the image has work for both
   const char *np = getenv("DNXCU_TC_PIPES");
@@ -1364,7 +1506,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   while (p2 < (uint32_t)(P * g.NB * g.N)) p2 <<= 1;
   g.tmem_cols = p2;
   g.D = g.S - 1 < MAX_DEPTH ? g.S - 1 : MAX_DEPTH;
-  pl.smem = HEADER_BYTES + wregion + (size_t)P * g.S * slot_bytes;
+  pl.smem = HEADER_BYTES + wregion + (size_t)P * g.S * slot_bytes + stage_total;
   const int sms = sm_count();
   const int lanes = sms * P;
   double best = 1e30;

@@ -25,6 +25,7 @@ enum VariantKind {
   VK_UPSAMPLE,
   VK_CONCAT,
   VK_RELU,
+  VK_PADC,
 };
 
 struct Variant {

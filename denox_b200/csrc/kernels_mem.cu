@@ -109,6 +109,24 @@ __global__ void relu_s(const __half *__restrict__ in, __half *__restrict__ out, 
     out[i] = __hmax(in[i], __float2half(0.0f));
 }
 
+// out[p][0:C] = in[p][0:C], out[p][C:Cp] = 0: one thread per pixel and 8 channel piece of the output
+// (2 byte loads: C is not a multiple of 8 when this runs; 16 byte stores).
+__global__ void pad_channels(const unsigned short *__restrict__ in, uint4 *__restrict__ out, long long P, int C,
+                             int Cp8) {
+  const long long n = P * Cp8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c8 = (int)(i % Cp8);
+    const long long p = i / Cp8;
+    const unsigned short *src = in + p * C + c8 * 8;
+    unsigned int w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (c8 * 8 + e < C) w[e >> 1] |= (unsigned int)__ldg(src + e) << ((e & 1) * 16);
+    out[i] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 constexpr int kThreads = 256;
 
 // Number of 16-byte (or 2-byte) items the dispatch writes.
@@ -120,6 +138,7 @@ long long item_count(const Variant &v, const dnxcu_dispatch &d) {
     case VK_UPSAMPLE: return 4 * H * W * (d.c_a / vec);
     case VK_CONCAT: return H * W * ((d.c_a + d.c_b) / vec);
     case VK_RELU: return H * W * d.c_a / vec;
+    case VK_PADC: return H * W * (d.c_out / 8);
     default: return 0;
   }
 }
@@ -162,6 +181,16 @@ int mem_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
     if (((uintptr_t)d.in_a | (uintptr_t)d.out | (uintptr_t)d.in_b) & 1) return DNXCU_E_MISALIGNED;
   }
   if (v.kind == VK_POOL && (H < 2 || W < 2)) return DNXCU_E_BAD_ARG;
+  if (v.kind == VK_PADC) {
+    if (d.c_out < d.c_a || d.c_out % 8) return DNXCU_E_BAD_ARG;
+    if (((uintptr_t)d.out & 15) || ((uintptr_t)d.in_a & 1)) return DNXCU_E_MISALIGNED;
+    uint32_t gp[3];
+    mem_grid(v, d, gp);
+    pad_channels<<<gp[0], kThreads, 0, s>>>((const unsigned short *)d.in_a, (uint4 *)d.out, (long long)H * W, d.c_a,
+                                            d.c_out / 8);
+    DNXCU_CUDA(cudaGetLastError());
+    return DNXCU_OK;
+  }
   uint32_t g[3];
   mem_grid(v, d, g);
   const long long P = (long long)H * W;

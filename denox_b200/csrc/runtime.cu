@@ -175,6 +175,46 @@ int build_fused_ops(const dnxcu_model_desc &desc, bool allow_tc, dnxcu_model &m)
     m.ops.push_back(std::move(op));
   }
   m.tensors[desc.input_tensor].materialized = true;
+
+  // An input whose channel count is not a multiple of 8 (the 9 channel colour/albedo/normal image) cannot be
+  // fetched in 16 byte pieces.  Like the reference's layout specialisation (HWC -> HWC8, specialization.cpp:183-340)
+  // the schedule then starts with one copy into a tensor padded with zero channels, and the convs that read the
+  // input get zero weights for the added channels.
+  if (allow_tc && !(desc.options & DNXCU_OPT_NO_PAD_INPUT) && (desc.input_channels % 8) != 0) {
+    const int C = desc.input_channels, Cp = (C + 15) / 16 * 16;
+    const int padded = (int)m.tensors.size();
+    TensorInfo ti;
+    ti.channels = Cp;
+    ti.level = 0;
+    ti.materialized = true;
+    m.tensors.push_back(ti);
+    for (FusedOp &op : m.ops) {
+      if (op.op != DNXCU_OP_CONV3X3) continue;
+      const bool ina = op.in_a == desc.input_tensor, inb = op.in_b == desc.input_tensor;
+      if (!ina && !inb) continue;
+      const int ca = op.c_a, cb = op.c_b, Cold = ca + cb;
+      const int nca = ina ? Cp : ca, ncb = inb ? Cp : cb, Cnew = nca + ncb;
+      std::vector<uint16_t> w((size_t)op.c_out * Cnew * 9, 0);
+      for (int k = 0; k < op.c_out; ++k)
+        for (int c = 0; c < Cold; ++c) {
+          const int cn = c < ca ? c : nca + (c - ca);
+          for (int t = 0; t < 9; ++t) w[((size_t)k * Cnew + cn) * 9 + t] = op.weights_kcrs[((size_t)k * Cold + c) * 9 + t];
+        }
+      op.weights_kcrs.swap(w);
+      if (ina) { op.in_a = padded; op.c_a = Cp; }
+      if (inb) { op.in_b = padded; op.c_b = Cp; }
+    }
+    FusedOp pad;
+    pad.op = DNXCU_OP_PAD_CHANNELS;
+    pad.in_a = desc.input_tensor;
+    pad.out = padded;
+    pad.c_a = C;
+    pad.c_out = Cp;
+    pad.level = 0;
+    pad.src_node = 0;
+    pad.name = "copy-transform(pad)";
+    m.ops.insert(m.ops.begin(), pad);
+  }
   return DNXCU_OK;
 }
 

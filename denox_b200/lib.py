@@ -23,9 +23,10 @@ L = C.CDLL(LIB_PATH)
 OK = 0
 E_BAD_ARG, E_UNSUPPORTED, E_MISALIGNED, E_CUDA, E_DEVICE, E_NO_MEMORY, E_STATE, E_IO, E_LIMIT = range(-1, -10, -1)
 
-OP_CONV3X3, OP_MAXPOOL2X2, OP_UPSAMPLE2X, OP_CONCAT, OP_RELU = 1, 2, 3, 4, 5
+OP_CONV3X3, OP_MAXPOOL2X2, OP_UPSAMPLE2X, OP_CONCAT, OP_RELU, OP_PAD_CHANNELS = 1, 2, 3, 4, 5, 6
 F_RELU, F_BIAS, F_UP2X_A, F_POOL_OUT, F_NO_FULL_OUT = 0x01, 0x02, 0x04, 0x08, 0x10
 OPT_NO_FUSE_ACTIVATION, OPT_NO_FUSE_POOL, OPT_NO_FUSE_UPSAMPLE, OPT_NO_FUSE_CONCAT, OPT_NO_TCGEN05 = 1, 2, 4, 8, 16
+OPT_NO_PAD_INPUT = 32
 
 
 class DnxcuError(RuntimeError):

@@ -86,7 +86,11 @@ typedef enum dnxcu_op {
   DNXCU_OP_MAXPOOL2X2 = 2, /* basic_pool.comp      */
   DNXCU_OP_UPSAMPLE2X = 3, /* basic_upsample.comp  */
   DNXCU_OP_CONCAT = 4,     /* copy_transform.comp  */
-  DNXCU_OP_RELU = 5        /* basic_activation.comp */
+  DNXCU_OP_RELU = 5,       /* basic_activation.comp */
+  DNXCU_OP_PAD_CHANNELS = 6 /* copy_transform.comp used as a layout change: HWC with C channels ->
+                               HWC with c_out >= C channels, the new ones zero (what the reference's
+                               HWC -> HWC8 / CHWC8 layout specialisation does,
+                               specialization/specialization.cpp:183-340) */
 } dnxcu_op;
 
 /* dispatch flags (conv only unless noted) */
@@ -258,6 +262,7 @@ typedef struct dnxcu_model_desc {
 #define DNXCU_OPT_NO_FUSE_UPSAMPLE 0x4u
 #define DNXCU_OPT_NO_FUSE_CONCAT 0x8u
 #define DNXCU_OPT_NO_TCGEN05 0x10u /* reference --fcoopmat off */
+#define DNXCU_OPT_NO_PAD_INPUT 0x20u /* do not copy a ragged input into a zero padded tensor first */
 
 typedef struct dnxcu_model dnxcu_model;
 typedef struct dnxcu_instance dnxcu_instance;

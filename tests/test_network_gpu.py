@@ -48,12 +48,19 @@ def test_network_matches_oracle_and_golden(which, shape, seed, key, options):
     # every materialised tensor, free running
     for info in inst.dispatch_info():
         tid = info.out_tensor
+        if tid not in ref32:
+            # the zero padded copy of a ragged input (not a tensor of the model)
+            got = fetch(inst, tid)
+            c = x.shape[2]
+            assert (got[:, :, :c] == x).all() and (got[:, :, c:] == 0).all()
+            continue
         got = fetch(inst, tid)
         rep = assert_close(got, ref32[tid], f"{which} tensor {tid} ({info.name.decode()})")
         assert rep["max"] < 0.05
     if options == 0:
         n_conv = sum(1 for nd in net.nodes if nd.kind == nets.CONV)
-        assert model.dispatch_count() == n_conv  # pool / upsample / concat / relu all fused away
+        # pool / upsample / concat / relu all fused away; one extra copy pads the ragged input to 16 channels
+        assert model.dispatch_count() == n_conv + 1
     inst.close()
     model.close()
 
