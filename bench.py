@@ -259,7 +259,7 @@ def main():
     for d in infos:
         byts, flops = d.bytes_read + d.bytes_written, d.flops
         nd = net.nodes[d.src_node]
-        if nd.kind == nets.CONV and d.c_out > 0:
+        if nd.kind == nets.CONV and d.flops > 0:
             # algorithmic work from the model's own channel counts (no credit for zero padded channels)
             c_real = net.channels[nd.in0]
             c_run = d.c_a + d.c_b
