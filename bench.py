@@ -144,6 +144,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-db", action="store_true", help="fixed variant preference instead of a benchmark database")
+    ap.add_argument("--db", default=None, help="benchmark database file (default: a temporary file)")
     ap.add_argument("--e2e-steps", type=int, default=0, help="default: same as --steps")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -175,7 +177,16 @@ def main():
         torch.cuda.synchronize()
 
     net = nets.oidn_unet()
-    model = lib.Model(net, device=local_rank)
+    # the reference's flow: populate the benchmark database with every (dispatch, variant) candidate of the
+    # model, time them on this device, then let the schedule selection pick the fastest per dispatch
+    db = None
+    if not args.no_db:
+        import tempfile
+        path = args.db or os.path.join(tempfile.gettempdir(), f"dnxcu_bench_{os.getpid()}.db")
+        db = lib.Db(path)
+        db.populate(net, H, W, device=local_rank)
+        db.bench(device=local_rank, min_samples=5, max_relative_error=0.05, max_rounds=2)
+    model = lib.Model(net, device=local_rank, db=db)
     inst = lib.Instance(model, H, W)
     n_disp = model.dispatch_count()
 

@@ -101,6 +101,8 @@ struct TcArgs {
   int cpa;               // producer warps copy part of the rows (cp.async) besides TMA
   int NB;                // stacked form: accumulator blocks in the TMEM ring (per pipeline)
   int P;                 // stacked form: pipelines per CTA (1 or 2)
+  int xp;                // stacked form: operand a (2x upsampled) comes by TMA at half resolution and is expanded in shared memory
+  uint32_t src_bytes;    // expand mode: bytes of one half resolution staging buffer (one per slot)
   int stage_pitch;       // stacked form: bytes per pixel row of an epilogue warp's staging tile, 0 = direct stores
   uint32_t stage_warp_bytes;  // staging bytes per epilogue warp
   uint32_t tmem_cols;
@@ -858,7 +860,8 @@ constexpr int ST_BAR_EMPTY = ST_BAR_FULL + MAX_SLOTS;
 constexpr int ST_BAR_TFULL = ST_BAR_EMPTY + MAX_SLOTS;
 constexpr int ST_BAR_TEMPTY = ST_BAR_TFULL + ST_MAX_BLOCKS;
 constexpr int ST_BAR_WRES = ST_BAR_TEMPTY + ST_MAX_BLOCKS;
-constexpr int ST_BAR_COUNT = ST_BAR_WRES + 1;
+constexpr int ST_BAR_RAW = ST_BAR_WRES + 1;  // [MAX_SLOTS] expand mode: TMA data of an entry landed (before the expansion)
+constexpr int ST_BAR_COUNT = ST_BAR_RAW + MAX_SLOTS;
 static_assert(ST_BAR_COUNT * 8 + 16 <= HEADER_BYTES, "header too small");
 constexpr int ST_OFF_TMEM_PTR = ST_BAR_COUNT * 8;
 constexpr int ST_OFF_ABORT = ST_OFF_TMEM_PTR + 4;
@@ -954,6 +957,8 @@ __device__ __forceinline__ void copy_out_pooled(uint32_t tile0, uint32_t tile1, 
 // team and its own work units.  The issuing thread's instruction stream, not the tensor
 // pipe, limits one pipeline (about 3000 cycles per input row against 1250 cycles of MMA
 // execution at 64 -> 64 channels), so two of them nearly double the rate.
+constexpr int SRC_PX = 72;                 // half resolution pixels per TMA box in expand mode (66 used)
+constexpr int SRC_PITCH = SRC_PX * 16;     // 1152 bytes per 8 channel chunk: a multiple of 128
 constexpr int ST_PIPE_STRIDE = 8;  // barrier index stride between the pipelines (slots / blocks per pipeline <= 8 when P == 2)
 
 template <int EPI>
@@ -977,10 +982,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    const uint32_t full_count = g.cpa ? (uint32_t)nprod_warps + 1u : 1u;
+    // who completes a slot: the TMA bytes alone; or TMA bytes + the producer warps' cp.async part; or, in expand
+    // mode, the producer warps alone after they have expanded the TMA data that landed on the raw barrier
+    const uint32_t full_count = g.xp ? (uint32_t)nprod_warps : (g.cpa ? (uint32_t)nprod_warps + 1u : 1u);
     for (int i = 0; i < MAX_SLOTS; ++i) {
       mbar_init(bar(ST_BAR_FULL + i), full_count);
       mbar_init(bar(ST_BAR_EMPTY + i), 1);
+      mbar_init(bar(ST_BAR_RAW + i), 1);
     }
     for (int i = 0; i < ST_MAX_BLOCKS; ++i) {
       mbar_init(bar(ST_BAR_TFULL + i), 1);
@@ -1160,11 +1168,11 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
       }
     }
     __syncwarp();
-  } else if (warp >= 2 && warp < 10) {
-    // ---------------- epilogue: two teams of four warps ----------------
-    // P == 2: team t drains pipeline t.  P == 1: the teams take alternate row pairs.
+  } else if (warp >= 2 && warp < 2 + 4 * P) {
+    // ---------------- epilogue: one team of four warps per pipeline ----------------
+    // (with the staged copy-out a team drains a row pair faster than the MMAs produce one)
     const int team = (warp - 2) >> 2;
-    const int pipe = P == 2 ? team : 0;
+    const int pipe = team;
     const int bofs = pipe * ST_PIPE_STRIDE;
     const uint32_t tmem_base = tmem_base0 + (uint32_t)(pipe * NB * N);
     const int q = warp & 3;
@@ -1173,7 +1181,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     const bool tr = g.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64;
     const int pitch = g.stage_pitch;  // 0: no staging tile, direct stores
     const int nck = g.K >> 3;
-    const uint32_t stage_base = slots_addr0 + (uint32_t)(P * S) * slot_bytes + (uint32_t)(warp - 2) * g.stage_warp_bytes;
+    const uint32_t stage_base = slots_addr0 + (uint32_t)(P * S) * (slot_bytes + g.src_bytes) + (uint32_t)(warp - 2) * g.stage_warp_bytes;
     bool ok = true;
     int item = 0;
     int blk = 0;
@@ -1193,7 +1201,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         if (nrows == 2) {
           if (++blk == NB) { blk = 0; tphase ^= 1u; }
         }
-        if (P == 1 && (item & 1) != team) continue;
         if (tr) trace(g, 1, item >> 1, 0);
         ok = mbar_wait<64>(bar(ST_BAR_TFULL + bofs + b0), ph0, abort_flag, g.status, 6);
         if (ok && nrows == 2) ok = mbar_wait<64>(bar(ST_BAR_TFULL + bofs + b1), ph1, abort_flag, g.status, 6);
@@ -1325,6 +1332,75 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           }
         }
       }
+    } else if (g.xp) {
+      // Operand a is the 2x nearest upsample of a half resolution tensor (basic_upsample.comp:49-56:
+      // src = dst / 2).  TMA fetches the half resolution row (66 pixels) into a staging buffer and operand
+      // b's row straight into the slot; both land on the slot's raw barrier.  The producer warps then write
+      // every source pixel to its two destination pixels inside shared memory and signal the slot.
+      const uint32_t src0 = slots_addr0 + (uint32_t)(P * S) * slot_bytes + (uint32_t)(pipe * S) * g.src_bytes;
+      const int nca = g.a.nch;
+      int slot = 0;
+      uint32_t phase = 1, rphase = 0;
+      for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
+        const StUnit t = st_unit_of(g, u);
+        for (int jj = 0; ok && jj < t.rows_out + 2; ++jj) {
+          const int iy = t.y0 - 1 + jj;
+          const bool a_tma = row_by_tma(g, g.a, iy), b_tma = g.b.nch > 0 && row_by_tma(g, g.b, iy);
+          for (int gi = 0; ok && gi < g.G; ++gi) {
+            const int c_lo = g.gc0[gi], c_hi = c_lo + g.gch[gi];
+            const int a_lo = min(c_lo, nca), a_hi = min(c_hi, nca);  // operand a's chunks in this group
+            ok = mbar_wait<64>(bar(ST_BAR_EMPTY + bofs + slot), phase, abort_flag, g.status, 7);
+            if (!ok) break;
+            const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes;
+            const uint32_t src_addr = src0 + (uint32_t)slot * g.src_bytes;
+            const uint32_t rb = bar(ST_BAR_RAW + bofs + slot);
+            if (tid == 0) {
+              uint32_t bytes = 0;
+              if (a_tma) bytes += (uint32_t)(a_hi - a_lo) * SRC_PITCH;
+              if (b_tma) bytes += (uint32_t)(c_hi - max(c_lo, nca)) * CHUNK_PITCH;
+              if (g.skip & 1) bytes = 0;
+              if (bytes) {
+                mbar_expect_tx(rb, bytes);
+                if (a_tma)
+                  for (int c = a_lo; c < a_hi; c += g.a.tbox)
+                    tma_load_4d(src_addr + (uint32_t)((c - a_lo) * SRC_PITCH), &g.tm_a, 0, (t.x0 >> 1) - 1, c, iy >> 1, rb);
+                if (b_tma)
+                  for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
+                    tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, t.x0 - 1, c - nca, iy, rb);
+              } else {
+                mbar_arrive(rb);
+              }
+            }
+            // rows TMA does not cover (halo rows of a row band) come the old way
+            if (!(g.skip & 1) && (!a_tma || (g.b.nch > 0 && !b_tma))) {
+              load_row(g, slot_addr, iy, t.x0, tid, nprod, c_lo, c_hi);
+              cp_async_commit();
+              cp_async_wait<0>();
+            }
+            ok = mbar_wait<32>(rb, rphase, abort_flag, g.status, 8);
+            if (!ok) break;
+            if (a_tma && !(g.skip & 1)) {
+              const int n = a_hi - a_lo;
+              const int items = SLOT_PX * n;
+              for (int i = tid; i < items; i += nprod) {
+                const int ch = i / SLOT_PX, px = i - ch * SLOT_PX;
+                const uint4 v = lds16(src_addr + (uint32_t)(ch * SRC_PITCH + ((px + 1) >> 1) * 16));
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(slot_addr + (uint32_t)((a_lo - c_lo + ch) * CHUNK_PITCH + px * 16)),
+                             "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                             : "memory");
+              }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(ST_BAR_FULL + bofs + slot));
+            if (++slot == S) {
+              slot = 0;
+              phase ^= 1u;
+              rphase ^= 1u;
+            }
+          }
+        }
+      }
     } else {
       // some rows need the producer warps: all threads of the pipeline's producer warps walk the entries,
       // thread 0 also issues the TMA part; each thread keeps up to D rows of cp.async in flight
@@ -1425,12 +1501,12 @@ EncodeTiledFn encode_fn() {
 }
 
 // H x W x C binary16 tensor as (8, W, C/8, H) with strides (2, 2C, 16, 2WC) bytes; box (8, 132, 2, 1).
-int make_tensor_map(CUtensorMap *tm, const void *ptr, int H, int W, int C, int box_chunks) {
+int make_tensor_map(CUtensorMap *tm, const void *ptr, int H, int W, int C, int box_chunks, int box_px = WH) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return DNXCU_E_CUDA;
   const cuuint64_t dims[4] = {8, (cuuint64_t)W, (cuuint64_t)(C / 8), (cuuint64_t)H};
   const cuuint64_t strides[3] = {(cuuint64_t)C * 2, 16, (cuuint64_t)W * C * 2};
-  const cuuint32_t box[4] = {8, (cuuint32_t)WH, (cuuint32_t)box_chunks, 1};
+  const cuuint32_t box[4] = {8, (cuuint32_t)box_px, (cuuint32_t)box_chunks, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -1470,28 +1546,59 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   const size_t wbytes = (size_t)9 * nch * g.N * 16;
   if (wbytes >= (1u << 20)) return DNXCU_E_UNSUPPORTED;
   const size_t wregion = (wbytes + 127) & ~(size_t)127;
-  const size_t slot_bytes = (size_t)g.gmax * CHUNK_PITCH;
-  if (HEADER_BYTES + wregion + 4 * slot_bytes > SMEM_LIMIT) return DNXCU_E_UNSUPPORTED;
-  // epilogue staging tiles (8 warps x 32 pixels x (K*2 + 16) bytes, two rows when pooling) if four slots still fit
-  g.stage_pitch = 0;
-  g.stage_warp_bytes = 0;
-  size_t stage_total = 0;
+  // Shared memory budget.  Wanted, in this order of importance: four input slots; the epilogue staging tiles
+  // (4 warps per pipeline x 32 pixels x (K*2 + 16) bytes, two rows when pooling); expand mode for an upsampled
+  // operand a (TMA at half resolution + one staging buffer per slot); a second pipeline (eight slots).
+  const char *noxp = getenv("DNXCU_TC_NO_EXPAND");
+  const char *notma = getenv("DNXCU_TC_NO_TMA");
   const char *nost = getenv("DNXCU_TC_NO_STAGE");
-  if (g.K % 8 == 0 && !(nost && nost[0] == '1')) {
-    const size_t pitch = (size_t)g.K * 2 + 16;
-    const size_t per_warp = (g.pool ? 2 : 1) * 32 * pitch;
-    if (HEADER_BYTES + wregion + 8 * per_warp + 4 * slot_bytes <= SMEM_LIMIT) {
-      g.stage_pitch = (int)pitch;
-      g.stage_warp_bytes = (uint32_t)per_warp;
-      stage_total = 8 * per_warp;
-    }
-  }
-  const int total_slots = (int)((SMEM_LIMIT - HEADER_BYTES - wregion - stage_total) / slot_bytes);
-  g.nstrips = (W + STRIP - 1) / STRIP;
-  // two pipelines when each can have four TMEM blocks and four input slots, and the image has work for both
   const char *np = getenv("DNXCU_TC_PIPES");
-  int P = (4 * g.N <= 256 && total_slots >= 8 && g.nstrips * ((H + 1) / 2) >= 2) ? 2 : 1;
-  if (np && np[0] == '1') P = 1;
+  const bool xp_possible = g.a.up && (g.a.C % 8) == 0 && (g.b.nch == 0 || g.b.tma) && !(noxp && noxp[0] == '1') &&
+                           !(notma && notma[0] == '1');
+  uint32_t xp_src_bytes = 0;
+  if (xp_possible) {
+    int amax = 0;
+    for (int gi = 0; gi < g.G; ++gi) {
+      const int lo = g.gc0[gi] < g.a.nch ? g.gc0[gi] : g.a.nch;
+      const int hi = g.gc0[gi] + g.gch[gi] < g.a.nch ? g.gc0[gi] + g.gch[gi] : g.a.nch;
+      if (hi - lo > amax) amax = hi - lo;
+    }
+    xp_src_bytes = (uint32_t)amax * SRC_PITCH;
+  }
+  const bool stage_possible = g.K % 8 == 0 && !(nost && nost[0] == '1');
+  const size_t stage_pitch = (size_t)g.K * 2 + 16;
+  const size_t stage_per_warp = (g.pool ? 2 : 1) * 32 * stage_pitch;
+  const size_t base_bytes = HEADER_BYTES + wregion;
+  const size_t plain_slot = (size_t)g.gmax * CHUNK_PITCH;
+  const bool p2_possible = 4 * g.N <= 256 && !(np && np[0] == '1');
+  // candidate configurations, best first: (pipelines, expand, staging)
+  int P = 0;
+  size_t slot_bytes = 0, stage_total = 0;
+  int total_slots = 0;
+  const int tries[8][3] = {{2, 1, 1}, {1, 1, 1}, {2, 1, 0}, {1, 1, 0}, {2, 0, 1}, {1, 0, 1}, {2, 0, 0}, {1, 0, 0}};
+  for (int ti = 0; ti < 8 && P == 0; ++ti) {
+    const int tp = tries[ti][0], txp = tries[ti][1], tst = tries[ti][2];
+    if (tp == 2 && !p2_possible) continue;
+    if (txp != (xp_possible ? 1 : 0) && txp == 1) continue;
+    if (tst && !stage_possible) continue;
+    const size_t sb = plain_slot + (txp ? xp_src_bytes : 0);
+    const size_t st = tst ? (size_t)4 * tp * stage_per_warp : 0;
+    if (base_bytes + st + (size_t)4 * tp * sb > SMEM_LIMIT) continue;
+    P = tp;
+    slot_bytes = sb;
+    stage_total = st;
+    total_slots = (int)((SMEM_LIMIT - base_bytes - st) / sb);
+    g.xp = txp;
+    g.src_bytes = txp ? xp_src_bytes : 0;
+    g.stage_pitch = tst ? (int)stage_pitch : 0;
+    g.stage_warp_bytes = tst ? (uint32_t)stage_per_warp : 0;
+  }
+  if (P == 0) return DNXCU_E_UNSUPPORTED;
+  if (g.xp) {
+    g.cpa = 1;
+    g.a.tma = 1;
+  }
+  g.nstrips = (W + STRIP - 1) / STRIP;
   g.P = P;
   if (P == 2) {
     g.NB = 256 / g.N;
@@ -1528,7 +1635,11 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   memset(&g.tm_a, 0, sizeof(g.tm_a));
   memset(&g.tm_b, 0, sizeof(g.tm_b));
   if (encode) {
-    if (g.a.tma && make_tensor_map(&g.tm_a, d.in_a, H, W, d.c_a, g.a.tbox)) return DNXCU_E_CUDA;
+    if (g.xp) {
+      if (make_tensor_map(&g.tm_a, d.in_a, H / 2, W / 2, d.c_a, g.a.tbox, SRC_PX)) return DNXCU_E_CUDA;
+    } else if (g.a.tma && make_tensor_map(&g.tm_a, d.in_a, H, W, d.c_a, g.a.tbox)) {
+      return DNXCU_E_CUDA;
+    }
     if (g.b.tma && make_tensor_map(&g.tm_b, d.in_b, H, W, d.c_b, g.b.tbox)) return DNXCU_E_CUDA;
   }
   return DNXCU_OK;

@@ -130,6 +130,7 @@ int materialise(const DbEntry &e, Bufs &bufs, dnxcu_dispatch &d) {
     case DNXCU_OP_MAXPOOL2X2: out_bytes = (size_t)(e.w / 2) * (e.h / 2) * e.c_a * 2; break;
     case DNXCU_OP_UPSAMPLE2X: out_bytes = 4 * P * e.c_a * 2; break;
     case DNXCU_OP_CONCAT: out_bytes = P * (e.c_a + e.c_b) * 2; break;
+    case DNXCU_OP_PAD_CHANNELS: out_bytes = P * e.c_out * 2; break;
     default: out_bytes = P * e.c_a * 2; break;
   }
   d.in_a = bufs.get(a_bytes, 1u, true);

@@ -34,6 +34,7 @@ CASES = [
     ("conv 32->32 +relu +pool (dual)", 32, 0, 32, lib.F_RELU | lib.F_POOL_OUT),
     ("up2x(96)+concat(64) -> 96 +relu", 96, 64, 96, lib.F_RELU | lib.F_UP2X_A),
     ("concat(64, 9) up2x -> 64 +relu", 64, 9, 64, lib.F_RELU | lib.F_UP2X_A),
+    ("up2x(64)+concat(16) -> 64 +relu", 64, 16, 64, lib.F_RELU | lib.F_UP2X_A),
     ("conv 64->32 +relu", 64, 0, 32, lib.F_RELU),
     ("conv 32->3", 32, 0, 3, 0),
 ]

@@ -88,3 +88,30 @@ def test_instance_rejects_unaligned_extent():
         lib.Instance(model, 100, 100)  # not a multiple of 16: the reference pads such images first
     assert e.value.status == lib.E_UNSUPPORTED
     model.close()
+
+
+def test_database_populate_bench_select(tmp_path):
+    """populate -> bench -> selection, the reference's `denox populate / bench / compile` flow, on a small frame."""
+    net = nets.tiny_unet()
+    db = lib.Db(tmp_path / "gpu.db")
+    added = db.populate(net, 64, 128)
+    assert added >= 5
+    db.bench(min_samples=3, max_relative_error=0.5, max_rounds=2)
+    db.close()
+    db = lib.Db(tmp_path / "gpu.db")          # resumes from the file (checkpoint semantics of the reference)
+    assert len(db) == added
+    assert db.populate(net, 64, 128) == 0
+    model = lib.Model(net, db=db)
+    inst = lib.Instance(model, 64, 128)
+    x = nets.tiny_input(7, 64, 128)
+    y = inst.infer(x)
+    ref = oracle.run_network(net, x, oracle.ACC_F32)[net.output_tensor]
+    assert_close(y, ref, "tiny with database selected variants")
+    # every chosen variant must be one the database has timed
+    import ctypes as C
+    for info in inst.dispatch_info():
+        d = lib.Dispatch()
+        d.variant, d.flags, d.c_a, d.c_b, d.c_out = info.variant, info.flags, info.c_a, info.c_b, info.c_out
+        d.pc[0], d.pc[1] = info.w, info.h
+        assert db.query(d) is not None, info.name
+    inst.close(); model.close(); db.close()
