@@ -1357,7 +1357,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
             if (tid == 0) {
               uint32_t bytes = 0;
               if (a_tma) bytes += (uint32_t)(a_hi - a_lo) * SRC_PITCH;
-              if (b_tma) bytes += (uint32_t)(c_hi - max(c_lo, nca)) * CHUNK_PITCH;
+              if (b_tma) bytes += (uint32_t)max(0, c_hi - max(c_lo, nca)) * CHUNK_PITCH;
               if (g.skip & 1) bytes = 0;
               if (bytes) {
                 mbar_expect_tx(rb, bytes);
