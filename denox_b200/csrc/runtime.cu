@@ -519,6 +519,34 @@ int dnxcu_instance_enqueue(dnxcu_instance *inst, const void *dev_in, void *dev_o
   return DNXCU_OK;
 }
 
+// Host in, host out, but stream ordered: the copies and the schedule are enqueued on the instance's own
+// stream and the call returns.  Several instances used round robin overlap one frame's copies with another
+// frame's kernels.  The host buffers must stay valid (and should be pinned) until dnxcu_instance_wait returns.
+int dnxcu_instance_infer_async(dnxcu_instance *inst, const void *host_in, void *host_out) {
+  if (!inst || !host_in || !host_out) return DNXCU_E_BAD_ARG;
+  const dnxcu_model *m = inst->model;
+  DNXCU_CUDA(cudaSetDevice(m->device));
+  void *din = inst->tensor_ptr[m->input_tensor], *dout = inst->tensor_ptr[m->output_tensor];
+  if (!din || !dout) return DNXCU_E_STATE;
+  const TensorInfo &ti = m->tensors[m->input_tensor], &to = m->tensors[m->output_tensor];
+  const size_t in_bytes = (size_t)inst->H * inst->W * ti.channels * 2;
+  const size_t out_bytes = (size_t)(inst->H >> to.level) * (inst->W >> to.level) * to.channels * 2;
+  DNXCU_CUDA(cudaMemcpyAsync(din, host_in, in_bytes, cudaMemcpyHostToDevice, inst->stream));
+  int st = dnxcu_instance_enqueue(inst, din, dout, inst->stream);
+  if (st) return st;
+  DNXCU_CUDA(cudaMemcpyAsync(host_out, dout, out_bytes, cudaMemcpyDeviceToHost, inst->stream));
+  return DNXCU_OK;
+}
+
+int dnxcu_instance_wait(dnxcu_instance *inst) {
+  if (!inst) return DNXCU_E_BAD_ARG;
+  DNXCU_CUDA(cudaSetDevice(inst->model->device));
+  DNXCU_CUDA(cudaStreamSynchronize(inst->stream));
+  int hstatus = 0;
+  DNXCU_CUDA(cudaMemcpy(&hstatus, inst->status, sizeof(int), cudaMemcpyDeviceToHost));
+  return hstatus ? DNXCU_E_DEVICE : DNXCU_OK;
+}
+
 int dnxcu_instance_infer(dnxcu_instance *inst, const void *host_in, void *host_out) {
   if (!inst || !host_in || !host_out) return DNXCU_E_BAD_ARG;
   const dnxcu_model *m = inst->model;

@@ -118,6 +118,8 @@ SIGNATURES = {
     "dnxcu_instance_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(Band), C.POINTER(C.c_void_p)]),
     "dnxcu_instance_destroy": (None, [C.c_void_p]),
     "dnxcu_instance_infer": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "dnxcu_instance_infer_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "dnxcu_instance_wait": (C.c_int, [C.c_void_p]),
     "dnxcu_instance_enqueue": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "dnxcu_instance_tensor": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_int),
                                         C.POINTER(C.c_int), C.POINTER(C.c_int)]),
@@ -278,6 +280,13 @@ class Instance:
         y = np.empty((h, w, c), dtype=np.float16)
         check(L.dnxcu_instance_infer(self._h, x.ctypes.data, y.ctypes.data), "dnxcu_instance_infer")
         return y
+
+    def infer_async(self, x: np.ndarray, y: np.ndarray):
+        """Stream ordered infer: x and y must stay alive (pinned for overlap) until wait()."""
+        check(L.dnxcu_instance_infer_async(self._h, x.ctypes.data, y.ctypes.data), "dnxcu_instance_infer_async")
+
+    def wait(self):
+        check(L.dnxcu_instance_wait(self._h), "dnxcu_instance_wait")
 
     def enqueue(self, dev_in: int, dev_out: int, stream: int = 0):
         check(L.dnxcu_instance_enqueue(self._h, dev_in, dev_out, stream), "dnxcu_instance_enqueue")

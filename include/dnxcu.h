@@ -289,6 +289,13 @@ DNXCU_API void dnxcu_instance_destroy(dnxcu_instance *inst);
  * (instance.hpp:59; instance.cpp:322-430): input is H x W x C_in binary16,
  * output H x W x C_out binary16, tightly packed. */
 DNXCU_API int dnxcu_instance_infer(dnxcu_instance *inst, const void *host_in, void *host_out);
+/* Stream ordered form of the same call (no counterpart in the reference, whose infer waits for the queue to
+ * idle): enqueues the host->device copy, the schedule and the device->host copy on the instance's own stream
+ * and returns; dnxcu_instance_wait blocks until they are done and reports kernel time-outs.  Several instances
+ * used round robin overlap the copies of one frame with the kernels of another.  host_in / host_out must stay
+ * valid until the wait returns; pinned memory is needed for the copies to overlap. */
+DNXCU_API int dnxcu_instance_infer_async(dnxcu_instance *inst, const void *host_in, void *host_out);
+DNXCU_API int dnxcu_instance_wait(dnxcu_instance *inst);
 /* Device resident form: input/output are device pointers, work is enqueued on
  * `stream`, nothing is synchronised. */
 DNXCU_API int dnxcu_instance_enqueue(dnxcu_instance *inst, const void *dev_in, void *dev_out,

@@ -115,3 +115,26 @@ def test_database_populate_bench_select(tmp_path):
         d.pc[0], d.pc[1] = info.w, info.h
         assert db.query(d) is not None, info.name
     inst.close(); model.close(); db.close()
+
+
+def test_infer_async_round_robin_matches_infer():
+    import torch
+    net = nets.tiny_unet()
+    model = lib.Model(net)
+    insts = [lib.Instance(model, 64, 128) for _ in range(2)]
+    xs = [nets.tiny_input(20 + i, 64, 128) for i in range(4)]
+    want = [insts[0].infer(x) for x in xs]
+    pin_in = [torch.from_numpy(x).pin_memory() for x in xs]
+    pin_out = [torch.empty((64, 128, 3), dtype=torch.float16).pin_memory() for _ in xs]
+    for i in range(4):
+        k = i % 2
+        if i >= 2:
+            insts[k].wait()
+        insts[k].infer_async(pin_in[i].numpy(), pin_out[i].numpy())
+    for inst in insts:
+        inst.wait()
+    for i in range(4):
+        assert (pin_out[i].numpy() == want[i]).all()
+    for inst in insts:
+        inst.close()
+    model.close()
