@@ -323,31 +323,38 @@ __device__ __forceinline__ void load_row(const TcArgs &g, uint32_t slot_addr, in
       if (iy < 0) row = (iy == -1) ? s.top : nullptr;
       else if (iy >= g.H) row = (iy == g.H) ? s.bot : nullptr;
       else row = s.ptr + (long long)(s.up ? iy >> 1 : iy) * Ws * s.C;
-      const int items = SLOT_PX * n;
       const bool vec = (s.C & 7) == 0;
       const int nchv = s.C >> 3;
       const uint32_t dst0 = slot_addr + (uint32_t)((chbase + lo - c_lo) * CHUNK_PITCH);
+      // a thread owns pixels tid, tid + nprod, ... and walks the chunks of each (no division in the loop)
 #pragma unroll 1
-      for (int i = tid; i < items; i += nprod) {
-        const int px = i / n, ch = i - px * n;
+      for (int px = tid; px < SLOT_PX; px += nprod) {
         const int ix = x0 - 1 + px;
         const bool inb = row != nullptr && ix >= 0 && ix < g.W;
-        const uint32_t dst = dst0 + (uint32_t)(ch * CHUNK_PITCH + px * 16);
-        const long long poff = (long long)(s.up ? ix >> 1 : ix) * s.C + (lo + ch) * 8;
+        const __half *src = inb ? row + (long long)(s.up ? ix >> 1 : ix) * s.C + lo * 8 : s.ptr;
+        uint32_t dst = dst0 + (uint32_t)(px * 16);
         if (vec) {
-          const bool ok = inb && (lo + ch) < nchv;
-          cp_async16(dst, ok ? (const void *)(row + poff) : (const void *)s.ptr, ok ? 16u : 0u);
-        } else {
-          uint32_t v[4] = {0u, 0u, 0u, 0u};
-          if (inb) {
-            const unsigned short *p = reinterpret_cast<const unsigned short *>(row + poff);
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-              if ((lo + ch) * 8 + e < s.C) v[e >> 1] |= (uint32_t)__ldg(p + e) << ((e & 1) * 16);
+#pragma unroll 2
+          for (int ch = 0; ch < n; ++ch) {
+            const bool ok = inb && (lo + ch) < nchv;
+            cp_async16(dst, ok ? (const void *)(src + ch * 8) : (const void *)s.ptr, ok ? 16u : 0u);
+            dst += CHUNK_PITCH;
           }
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[0]), "r"(v[1]), "r"(v[2]),
-                       "r"(v[3])
-                       : "memory");
+        } else {
+#pragma unroll 1
+          for (int ch = 0; ch < n; ++ch) {
+            uint32_t v[4] = {0u, 0u, 0u, 0u};
+            if (inb) {
+              const unsigned short *p = reinterpret_cast<const unsigned short *>(src + ch * 8);
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if ((lo + ch) * 8 + e < s.C) v[e >> 1] |= (uint32_t)__ldg(p + e) << ((e & 1) * 16);
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                         "r"(v[3])
+                         : "memory");
+            dst += CHUNK_PITCH;
+          }
         }
       }
     }
