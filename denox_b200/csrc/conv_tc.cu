@@ -1346,66 +1346,113 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
       // every source pixel to its two destination pixels inside shared memory and signal the slot.
       const uint32_t src0 = slots_addr0 + (uint32_t)(P * S) * slot_bytes + (uint32_t)(pipe * S) * g.src_bytes;
       const int nca = g.a.nch;
-      int slot = 0;
-      uint32_t phase = 1, rphase = 0;
-      for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
-        const StUnit t = st_unit_of(g, u);
-        for (int jj = 0; ok && jj < t.rows_out + 2; ++jj) {
-          const int iy = t.y0 - 1 + jj;
-          const bool a_tma = row_by_tma(g, g.a, iy), b_tma = g.b.nch > 0 && row_by_tma(g, g.b, iy);
-          for (int gi = 0; ok && gi < g.G; ++gi) {
-            const int c_lo = g.gc0[gi], c_hi = c_lo + g.gch[gi];
+      // Two cursors over the same entry sequence: thread 0 starts the TMA copies of up to LA entries ahead of
+      // the entry that is being expanded, so that the copy latency (1-2 us) overlaps the expansion of earlier rows.
+      struct Cursor {
+        int u, jj, gi, slot;
+        uint32_t ephase, rphase;
+        StUnit t;
+        bool valid;
+      };
+      auto start = [&](Cursor &c) {
+        c.u = (int)blockIdx.x * P + pipe;
+        c.jj = c.gi = c.slot = 0;
+        c.ephase = 1;
+        c.rphase = 0;
+        c.valid = c.u < g.nunits;
+        if (c.valid) c.t = st_unit_of(g, c.u);
+      };
+      auto advance = [&](Cursor &c) {
+        if (++c.slot == S) { c.slot = 0; c.ephase ^= 1u; c.rphase ^= 1u; }
+        if (++c.gi < g.G) return;
+        c.gi = 0;
+        if (++c.jj < c.t.rows_out + 2) return;
+        c.jj = 0;
+        c.u += unit_stride;
+        c.valid = c.u < g.nunits;
+        if (c.valid) c.t = st_unit_of(g, c.u);
+      };
+      const int LA = S - 1 < 4 ? S - 1 : 4;
+      Cursor is, ex;
+      start(is);
+      start(ex);
+      int ahead = 0;  // entries issued but not yet expanded (thread 0 only)
+      int xcount = 0;
+      while (ok && ex.valid) {
+        if (tid == 0) {
+          while (ok && is.valid && ahead < LA) {
+            const int iy = is.t.y0 - 1 + is.jj;
+            const bool a_tma = row_by_tma(g, g.a, iy), b_tma = g.b.nch > 0 && row_by_tma(g, g.b, iy);
+            const int c_lo = g.gc0[is.gi], c_hi = c_lo + g.gch[is.gi];
             const int a_lo = min(c_lo, nca), a_hi = min(c_hi, nca);  // operand a's chunks in this group
-            ok = mbar_wait<64>(bar(ST_BAR_EMPTY + bofs + slot), phase, abort_flag, g.status, 7);
+            ok = mbar_wait<64>(bar(ST_BAR_EMPTY + bofs + is.slot), is.ephase, abort_flag, g.status, 7);
             if (!ok) break;
-            const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes;
-            const uint32_t src_addr = src0 + (uint32_t)slot * g.src_bytes;
-            const uint32_t rb = bar(ST_BAR_RAW + bofs + slot);
-            if (tid == 0) {
-              uint32_t bytes = 0;
-              if (a_tma) bytes += (uint32_t)(a_hi - a_lo) * SRC_PITCH;
-              if (b_tma) bytes += (uint32_t)max(0, c_hi - max(c_lo, nca)) * CHUNK_PITCH;
-              if (g.skip & 1) bytes = 0;
-              if (bytes) {
-                mbar_expect_tx(rb, bytes);
-                if (a_tma)
-                  for (int c = a_lo; c < a_hi; c += g.a.tbox)
-                    tma_load_4d(src_addr + (uint32_t)((c - a_lo) * SRC_PITCH), &g.tm_a, 0, (t.x0 >> 1) - 1, c, iy >> 1, rb);
-                if (b_tma)
-                  for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
-                    tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, t.x0 - 1, c - nca, iy, rb);
-              } else {
-                mbar_arrive(rb);
-              }
+            const uint32_t slot_addr = slots_addr + (uint32_t)is.slot * slot_bytes;
+            const uint32_t src_addr = src0 + (uint32_t)is.slot * g.src_bytes;
+            const uint32_t rb = bar(ST_BAR_RAW + bofs + is.slot);
+            uint32_t bytes = 0;
+            if (a_tma) bytes += (uint32_t)(a_hi - a_lo) * SRC_PITCH;
+            if (b_tma) bytes += (uint32_t)max(0, c_hi - max(c_lo, nca)) * CHUNK_PITCH;
+            if (g.skip & 1) bytes = 0;
+            if (bytes) {
+              mbar_expect_tx(rb, bytes);
+              if (a_tma)
+                for (int c = a_lo; c < a_hi; c += g.a.tbox)
+                  tma_load_4d(src_addr + (uint32_t)((c - a_lo) * SRC_PITCH), &g.tm_a, 0, (is.t.x0 >> 1) - 1, c, iy >> 1, rb);
+              if (b_tma)
+                for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
+                  tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, is.t.x0 - 1, c - nca, iy, rb);
+            } else {
+              mbar_arrive(rb);
             }
-            // rows TMA does not cover (halo rows of a row band) come the old way
-            if (!(g.skip & 1) && (!a_tma || (g.b.nch > 0 && !b_tma))) {
-              load_row(g, slot_addr, iy, t.x0, tid, nprod, c_lo, c_hi);
-              cp_async_commit();
-              cp_async_wait<0>();
-            }
-            ok = mbar_wait<32>(rb, rphase, abort_flag, g.status, 8);
-            if (!ok) break;
-            if (a_tma && !(g.skip & 1)) {
-              const int n = a_hi - a_lo;
-              const int items = SLOT_PX * n;
-              for (int i = tid; i < items; i += nprod) {
-                const int ch = i / SLOT_PX, px = i - ch * SLOT_PX;
-                const uint4 v = lds16(src_addr + (uint32_t)(ch * SRC_PITCH + ((px + 1) >> 1) * 16));
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(slot_addr + (uint32_t)((a_lo - c_lo + ch) * CHUNK_PITCH + px * 16)),
-                             "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+            ++ahead;
+            advance(is);
+          }
+          if (!ok) break;
+        }
+        // expand entry `ex`
+        {
+          const int iy = ex.t.y0 - 1 + ex.jj;
+          const bool a_tma = row_by_tma(g, g.a, iy), b_tma = g.b.nch > 0 && row_by_tma(g, g.b, iy);
+          const int c_lo = g.gc0[ex.gi], c_hi = c_lo + g.gch[ex.gi];
+          const int a_lo = min(c_lo, nca), a_hi = min(c_hi, nca);
+          const uint32_t slot_addr = slots_addr + (uint32_t)ex.slot * slot_bytes;
+          const uint32_t src_addr = src0 + (uint32_t)ex.slot * g.src_bytes;
+          const uint32_t rb = bar(ST_BAR_RAW + bofs + ex.slot);
+          if (tid == 32 && pipe == 0) trace(g, 2, xcount, 0);
+          ok = mbar_wait<32>(rb, ex.rphase, abort_flag, g.status, 8);
+          if (!ok) break;
+          if (tid == 32 && pipe == 0) trace(g, 2, xcount, 1);
+          // rows TMA does not cover (halo rows of a row band) come the old way; the raw barrier has completed,
+          // so the slot is free (thread 0 waited for that before it armed the barrier)
+          if (!(g.skip & 1) && (!a_tma || (g.b.nch > 0 && !b_tma))) {
+            load_row(g, slot_addr, iy, ex.t.x0, tid, nprod, c_lo, c_hi);
+            cp_async_commit();
+            cp_async_wait<0>();
+          }
+          if (a_tma && !(g.skip & 1)) {
+            const int n = a_hi - a_lo;
+            for (int px = tid; px < SLOT_PX; px += nprod) {
+              uint32_t sp = src_addr + (uint32_t)(((px + 1) >> 1) * 16);
+              uint32_t dp = slot_addr + (uint32_t)((a_lo - c_lo) * CHUNK_PITCH + px * 16);
+#pragma unroll 4
+              for (int ch = 0; ch < n; ++ch) {
+                const uint4 v = lds16(sp);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dp), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                              : "memory");
+                sp += SRC_PITCH;
+                dp += CHUNK_PITCH;
               }
-            }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(ST_BAR_FULL + bofs + slot));
-            if (++slot == S) {
-              slot = 0;
-              phase ^= 1u;
-              rphase ^= 1u;
             }
           }
+          if (tid == 32 && pipe == 0) trace(g, 2, xcount, 2);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(ST_BAR_FULL + bofs + ex.slot));
+          if (tid == 32 && pipe == 0) trace(g, 2, xcount, 3);
+          ++xcount;
+          if (tid == 0) --ahead;
+          advance(ex);
         }
       }
     } else {
