@@ -92,6 +92,9 @@ static const Variant kVariants[] = {
     {{15, DNXCU_OP_RELU, "basic-activation", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_RELU, 1, 0, 0, 0},
     {{16, DNXCU_OP_PAD_CHANNELS, "copy-transform", "PAD=8", 0, 0, 1, 8, 65536, 0}, VK_PADC, 1, 0, 0, 0},
     {{17, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=4#W=resident", CONV_ALL, 1, 1, 1, 128, 0}, VK_CONV_TC, 0, 4, 0, 0},
+    {{18, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=2#W=resident#NSPLIT=2", CONV_ALL, 1, 1, 16, 256, 0}, VK_CONV_TC, 0, 2, 0, 2},
+    {{19, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=4#W=resident#NSPLIT=2", CONV_ALL, 1, 1, 16, 256, 0}, VK_CONV_TC, 0, 4, 0, 2},
+    {{20, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=4#W=resident#NSPLIT=3", CONV_ALL, 1, 1, 16, 256, 0}, VK_CONV_TC, 0, 4, 0, 3},
 };
 static const int kVariantCount = (int)(sizeof(kVariants) / sizeof(kVariants[0]));
 

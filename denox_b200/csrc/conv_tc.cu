@@ -90,6 +90,7 @@ struct TcArgs {
   __half *out_pool;
   int *status;
   int H, W, K, N, Ns;
+  int os;  // halves between consecutive pixels of the outputs (= K unless the output channels are split over launches)
   int relu, pool, full_out;
   int RB, S, nstrips, nunits;
   int wstream, WST;
@@ -825,10 +826,10 @@ __device__ __forceinline__ void epi_fast(const TcArgs &g, uint32_t t0, uint32_t 
   const bool row1 = RSTEP == 2 && (y + 1 < g.H);
   if (EPI & EPI_FULL) {
     if (xin) {
-      __half *o0 = g.out + ((long long)y * g.W + x) * g.K + c0;
+      __half *o0 = g.out + ((long long)y * g.W + x) * g.os + c0;
       store_row<NC>(g, o0, h0, c0);
       if constexpr (RSTEP == 2) {
-        if (row1) store_row<NC>(g, o0 + (long long)g.W * g.K, h1, c0);
+        if (row1) store_row<NC>(g, o0 + (long long)g.W * g.os, h1, c0);
       }
     }
   }
@@ -840,7 +841,7 @@ __device__ __forceinline__ void epi_fast(const TcArgs &g, uint32_t t0, uint32_t 
       pm[j] = hmax2_u32(vm, __shfl_xor_sync(0xffffffffu, vm, 1));
     }
     if (xin && !(lane & 1) && row1)
-      store_row<NC>(g, g.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (x >> 1)) * g.K + c0, pm, c0);
+      store_row<NC>(g, g.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (x >> 1)) * g.os + c0, pm, c0);
   }
 }
 
@@ -924,13 +925,13 @@ __device__ __forceinline__ uint4 lds16(uint32_t addr) {
 }
 
 // Copies `npx` staged pixels (K channels each) to `dst` (contiguous), lanes on consecutive 16 byte pieces.
-__device__ __forceinline__ void copy_out(uint32_t tile, int pitch, int nck, int npx, __half *dst, int lane) {
+__device__ __forceinline__ void copy_out(uint32_t tile, int pitch, int nck, int os8, int npx, __half *dst, int lane) {
   const int total = npx * nck;
   int px = lane / nck, ch = lane - px * nck;
   const int dpx = 32 / nck, dch = 32 - dpx * nck;
   uint4 *o = reinterpret_cast<uint4 *>(dst);
   for (int i = lane; i < total; i += 32) {
-    o[i] = lds16(tile + (uint32_t)(px * pitch + ch * 16));
+    o[px * os8 + ch] = lds16(tile + (uint32_t)(px * pitch + ch * 16));
     px += dpx;
     ch += dch;
     if (ch >= nck) { ch -= nck; ++px; }
@@ -942,7 +943,7 @@ __device__ __forceinline__ uint4 hmax8_u(uint4 a, uint4 b) {
 }
 
 // 2x2 max of two staged rows (tile0, tile1), `npx` input pixels -> npx / 2 pooled pixels at `dst`.
-__device__ __forceinline__ void copy_out_pooled(uint32_t tile0, uint32_t tile1, int pitch, int nck, int npx,
+__device__ __forceinline__ void copy_out_pooled(uint32_t tile0, uint32_t tile1, int pitch, int nck, int os8, int npx,
                                                 __half *dst, int lane) {
   const int total = (npx >> 1) * nck;
   int px = lane / nck, ch = lane - px * nck;
@@ -952,7 +953,7 @@ __device__ __forceinline__ void copy_out_pooled(uint32_t tile0, uint32_t tile1, 
     const uint32_t off = (uint32_t)(2 * px * pitch + ch * 16);
     const uint4 a = hmax8_u(lds16(tile0 + off), lds16(tile0 + off + (uint32_t)pitch));
     const uint4 b = hmax8_u(lds16(tile1 + off), lds16(tile1 + off + (uint32_t)pitch));
-    o[i] = hmax8_u(a, b);
+    o[px * os8 + ch] = hmax8_u(a, b);
     px += dpx;
     ch += dch;
     if (ch >= nck) { ch -= nck; ++px; }
@@ -1015,6 +1016,65 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   tc_fence_after();
   const uint32_t tmem_base0 = *tmem_ptr;
 
+  // ---- expand mode: cursor over the (unit, input row, K group) entries of one pipeline, and the TMA issue of one entry
+  struct XpCursor {
+    int u, jj, gi, slot;
+    uint32_t ephase, rphase;
+    StUnit t;
+    bool valid;
+  };
+  auto xp_start = [&](XpCursor &c, int pipe) {
+    c.u = (int)blockIdx.x * P + pipe;
+    c.jj = c.gi = c.slot = 0;
+    c.ephase = 1;
+    c.rphase = 0;
+    c.valid = c.u < g.nunits;
+    if (c.valid) c.t = st_unit_of(g, c.u);
+  };
+  auto xp_advance = [&](XpCursor &c) {
+    if (++c.slot == S) { c.slot = 0; c.ephase ^= 1u; c.rphase ^= 1u; }
+    if (++c.gi < g.G) return;
+    c.gi = 0;
+    if (++c.jj < c.t.rows_out + 2) return;
+    c.jj = 0;
+    c.u += unit_stride;
+    c.valid = c.u < g.nunits;
+    if (c.valid) c.t = st_unit_of(g, c.u);
+  };
+  // Waits for the entry's slot to be free, arms its raw barrier with the byte count and starts the copies:
+  // operand a's half resolution row into the slot's staging buffer, operand b's row straight into the slot.
+  auto xp_issue = [&](XpCursor &is, int pipe) -> bool {
+    const int bofs = pipe * ST_PIPE_STRIDE;
+    const uint32_t slots_addr = slots_addr0 + (uint32_t)(pipe * S) * slot_bytes;
+    const uint32_t src0 = slots_addr0 + (uint32_t)(P * S) * slot_bytes + (uint32_t)(pipe * S) * g.src_bytes;
+    const int nca = g.a.nch;
+    const int iy = is.t.y0 - 1 + is.jj;
+    const bool a_tma = row_by_tma(g, g.a, iy), b_tma = g.b.nch > 0 && row_by_tma(g, g.b, iy);
+    const int c_lo = g.gc0[is.gi], c_hi = c_lo + g.gch[is.gi];
+    const int a_lo = min(c_lo, nca), a_hi = min(c_hi, nca);  // operand a's chunks in this group
+    if (!mbar_wait<64>(bar(ST_BAR_EMPTY + bofs + is.slot), is.ephase, abort_flag, g.status, 7)) return false;
+    const uint32_t slot_addr = slots_addr + (uint32_t)is.slot * slot_bytes;
+    const uint32_t src_addr = src0 + (uint32_t)is.slot * g.src_bytes;
+    const uint32_t rb = bar(ST_BAR_RAW + bofs + is.slot);
+    uint32_t bytes = 0;
+    if (a_tma) bytes += (uint32_t)(a_hi - a_lo) * SRC_PITCH;
+    if (b_tma) bytes += (uint32_t)max(0, c_hi - max(c_lo, nca)) * CHUNK_PITCH;
+    if (g.skip & 1) bytes = 0;
+    if (bytes) {
+      mbar_expect_tx(rb, bytes);
+      if (a_tma)
+        for (int c = a_lo; c < a_hi; c += g.a.tbox)
+          tma_load_4d(src_addr + (uint32_t)((c - a_lo) * SRC_PITCH), &g.tm_a, 0, (is.t.x0 >> 1) - 1, c, iy >> 1, rb);
+      if (b_tma)
+        for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
+          tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, is.t.x0 - 1, c - nca, iy, rb);
+    } else {
+      mbar_arrive(rb);
+    }
+    xp_advance(is);
+    return true;
+  };
+
   if (warp == 1 && lane == 0) {
     // ---------------- weights (resident), copies of at most 32 KB ----------------
     const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(g.w);
@@ -1022,6 +1082,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     mbar_expect_tx(bar(ST_BAR_WRES), total);
     for (uint32_t off = 0; off < total; off += 32768u)
       bulk_g2s(w_addr + off, wsrc + off, min(32768u, total - off), bar(ST_BAR_WRES));
+  }
+  if (warp == 1 && lane == 0 && g.xp && P == 1) {
+    // one pipeline: this thread has nothing else to do and feeds the expand mode's TMA copies
+    XpCursor is;
+    xp_start(is, 0);
+    bool ok = true;
+    while (ok && is.valid) ok = xp_issue(is, 0);
   }
   if (warp == 1) __syncwarp();
 
@@ -1188,6 +1255,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     const bool tr = g.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64;
     const int pitch = g.stage_pitch;  // 0: no staging tile, direct stores
     const int nck = g.K >> 3;
+    const int os8 = g.os >> 3;  // output pixel stride in 16 byte units (= nck unless the output channels are split)
     const uint32_t stage_base = slots_addr0 + (uint32_t)(P * S) * (slot_bytes + g.src_bytes) + (uint32_t)(warp - 2) * g.stage_warp_bytes;
     bool ok = true;
     int item = 0;
@@ -1244,18 +1312,18 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
               }
               if (!pool2) {
                 if ((EPI & EPI_FULL) && !(g.skip & 4))
-                  copy_out(tile, pitch, nck, npx, g.out + ((long long)(y + r) * g.W + xw) * g.K, lane);
+                  copy_out(tile, pitch, nck, os8, npx, g.out + ((long long)(y + r) * g.W + xw) * g.os, lane);
                 __syncwarp();
               }
             }
             if (pool2) {
               if (!(g.skip & 4)) {
                 if (EPI & EPI_FULL) {
-                  copy_out(tile0, pitch, nck, npx, g.out + ((long long)y * g.W + xw) * g.K, lane);
-                  copy_out(tile1, pitch, nck, npx, g.out + ((long long)(y + 1) * g.W + xw) * g.K, lane);
+                  copy_out(tile0, pitch, nck, os8, npx, g.out + ((long long)y * g.W + xw) * g.os, lane);
+                  copy_out(tile1, pitch, nck, os8, npx, g.out + ((long long)(y + 1) * g.W + xw) * g.os, lane);
                 }
-                copy_out_pooled(tile0, tile1, pitch, nck, npx,
-                                g.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (xw >> 1)) * g.K, lane);
+                copy_out_pooled(tile0, tile1, pitch, nck, os8, npx,
+                                g.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (xw >> 1)) * g.os, lane);
               }
               __syncwarp();
             }
@@ -1346,67 +1414,21 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
       // every source pixel to its two destination pixels inside shared memory and signal the slot.
       const uint32_t src0 = slots_addr0 + (uint32_t)(P * S) * slot_bytes + (uint32_t)(pipe * S) * g.src_bytes;
       const int nca = g.a.nch;
-      // Two cursors over the same entry sequence: thread 0 starts the TMA copies of up to LA entries ahead of
-      // the entry that is being expanded, so that the copy latency (1-2 us) overlaps the expansion of earlier rows.
-      struct Cursor {
-        int u, jj, gi, slot;
-        uint32_t ephase, rphase;
-        StUnit t;
-        bool valid;
-      };
-      auto start = [&](Cursor &c) {
-        c.u = (int)blockIdx.x * P + pipe;
-        c.jj = c.gi = c.slot = 0;
-        c.ephase = 1;
-        c.rphase = 0;
-        c.valid = c.u < g.nunits;
-        if (c.valid) c.t = st_unit_of(g, c.u);
-      };
-      auto advance = [&](Cursor &c) {
-        if (++c.slot == S) { c.slot = 0; c.ephase ^= 1u; c.rphase ^= 1u; }
-        if (++c.gi < g.G) return;
-        c.gi = 0;
-        if (++c.jj < c.t.rows_out + 2) return;
-        c.jj = 0;
-        c.u += unit_stride;
-        c.valid = c.u < g.nunits;
-        if (c.valid) c.t = st_unit_of(g, c.u);
-      };
+      // Thread 0 of the producer warps (two pipelines) or lane 0 of the otherwise idle weights warp (one
+      // pipeline) starts the TMA copies; it runs ahead of the expansion as far as free slots allow, so the copy
+      // latency overlaps the expansion of earlier rows.
+      const bool self_issue = P == 2;
       const int LA = S - 1 < 4 ? S - 1 : 4;
-      Cursor is, ex;
-      start(is);
-      start(ex);
-      int ahead = 0;  // entries issued but not yet expanded (thread 0 only)
+      XpCursor is, ex;
+      xp_start(is, pipe);
+      xp_start(ex, pipe);
+      int ahead = 0;  // entries issued but not yet expanded (thread 0, self_issue only)
       int xcount = 0;
       while (ok && ex.valid) {
-        if (tid == 0) {
+        if (self_issue && tid == 0) {
           while (ok && is.valid && ahead < LA) {
-            const int iy = is.t.y0 - 1 + is.jj;
-            const bool a_tma = row_by_tma(g, g.a, iy), b_tma = g.b.nch > 0 && row_by_tma(g, g.b, iy);
-            const int c_lo = g.gc0[is.gi], c_hi = c_lo + g.gch[is.gi];
-            const int a_lo = min(c_lo, nca), a_hi = min(c_hi, nca);  // operand a's chunks in this group
-            ok = mbar_wait<64>(bar(ST_BAR_EMPTY + bofs + is.slot), is.ephase, abort_flag, g.status, 7);
-            if (!ok) break;
-            const uint32_t slot_addr = slots_addr + (uint32_t)is.slot * slot_bytes;
-            const uint32_t src_addr = src0 + (uint32_t)is.slot * g.src_bytes;
-            const uint32_t rb = bar(ST_BAR_RAW + bofs + is.slot);
-            uint32_t bytes = 0;
-            if (a_tma) bytes += (uint32_t)(a_hi - a_lo) * SRC_PITCH;
-            if (b_tma) bytes += (uint32_t)max(0, c_hi - max(c_lo, nca)) * CHUNK_PITCH;
-            if (g.skip & 1) bytes = 0;
-            if (bytes) {
-              mbar_expect_tx(rb, bytes);
-              if (a_tma)
-                for (int c = a_lo; c < a_hi; c += g.a.tbox)
-                  tma_load_4d(src_addr + (uint32_t)((c - a_lo) * SRC_PITCH), &g.tm_a, 0, (is.t.x0 >> 1) - 1, c, iy >> 1, rb);
-              if (b_tma)
-                for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
-                  tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, is.t.x0 - 1, c - nca, iy, rb);
-            } else {
-              mbar_arrive(rb);
-            }
+            ok = xp_issue(is, pipe);
             ++ahead;
-            advance(is);
           }
           if (!ok) break;
         }
@@ -1435,13 +1457,20 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
             for (int px = tid; px < SLOT_PX; px += nprod) {
               uint32_t sp = src_addr + (uint32_t)(((px + 1) >> 1) * 16);
               uint32_t dp = slot_addr + (uint32_t)((a_lo - c_lo) * CHUNK_PITCH + px * 16);
-#pragma unroll 4
-              for (int ch = 0; ch < n; ++ch) {
-                const uint4 v = lds16(sp);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dp), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                             : "memory");
-                sp += SRC_PITCH;
-                dp += CHUNK_PITCH;
+              // four loads in flight, then their four stores
+              for (int ch = 0; ch < n; ch += 4) {
+                uint4 v[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  if (ch + q < n) v[q] = lds16(sp + (uint32_t)(q * SRC_PITCH));
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  if (ch + q < n)
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dp + (uint32_t)(q * CHUNK_PITCH)), "r"(v[q].x),
+                                 "r"(v[q].y), "r"(v[q].z), "r"(v[q].w)
+                                 : "memory");
+                sp += 4 * SRC_PITCH;
+                dp += 4 * CHUNK_PITCH;
               }
             }
           }
@@ -1451,8 +1480,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           if (lane == 0) mbar_arrive(bar(ST_BAR_FULL + bofs + ex.slot));
           if (tid == 32 && pipe == 0) trace(g, 2, xcount, 3);
           ++xcount;
-          if (tid == 0) --ahead;
-          advance(ex);
+          if (self_issue && tid == 0) --ahead;
+          xp_advance(ex);
         }
       }
     } else {
@@ -1700,7 +1729,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
 }
 
 // v.p0 = R (rows per pass), v.p1 = K groups, v.p2 = weight mode (0 resident, 1 streamed), v.p3 = weight stages
-int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode) {
+int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, int os_override = 0) {
   if (!d.in_a || !d.weights || d.c_a <= 0 || d.c_out <= 0 || d.c_b < 0) return DNXCU_E_BAD_ARG;
   if (d.pc[0] == 0 || d.pc[1] == 0) return DNXCU_E_BAD_ARG;
   if (d.c_b > 0 && !d.in_b) return DNXCU_E_BAD_ARG;
@@ -1742,6 +1771,7 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode) 
   g.H = H;
   g.W = W;
   g.K = d.c_out;
+  g.os = os_override ? os_override : d.c_out;
   g.N = pad16(d.c_out);
   g.Ns = (g.N + 31) / 32 * 32;
   g.relu = (d.flags & DNXCU_F_RELU) ? 1 : 0;
@@ -1873,34 +1903,61 @@ int launch_stack(const Plan &pl, cudaStream_t s) {
   }
 }
 
-}  // namespace
-
-size_t conv_tc_weight_bytes(const Variant &, int k, int ca, int cb) {
-  return (size_t)9 * (nch_of(ca) + nch_of(cb)) * pad16(k) * 16;
+// Output channel split of the stacked form (variant parameter p3 = parts): a layer whose weights do not fit
+// in shared memory runs as several launches, each producing a run of output channels (a multiple of 16) with
+// its own resident weights; the outputs interleave through the pixel stride.
+int split_parts(const Variant &v, int K, int k0[8], int kp[8]) {
+  const int want = (v.p0 == 0 && v.p3 > 1) ? v.p3 : 1;
+  const int np = ((K + want - 1) / want + 15) / 16 * 16;
+  int n = 0;
+  for (int c = 0; c < K && n < 8; c += np, ++n) {
+    k0[n] = c;
+    kp[n] = K - c < np ? K - c : np;
+  }
+  return n;
 }
 
-// KCRS -> [tap][chunk c8][n][8]: operand a's chunks first, each operand's channel
-// count padded to a multiple of 16 and the output channels to a multiple of 16,
-// zero filled.  Plays the role of the RSCKC16 / KRSCK16 re-layouts of the
-// reference (common/src/denox/memory/tensor/FilterLayout.hpp:74-78,104-108).
+}  // namespace
+
+size_t conv_tc_weight_bytes(const Variant &v, int k, int ca, int cb) {
+  int k0[8], kp[8];
+  const int n = split_parts(v, k, k0, kp);
+  size_t total = 0;
+  for (int p = 0; p < n; ++p) total += (size_t)9 * (nch_of(ca) + nch_of(cb)) * pad16(kp[p]) * 16;
+  return total;
+}
+
+// KCRS -> the shared memory image of the MMA's B operand, operand a's chunks first, each operand's channel
+// count padded to a multiple of 16 and the output channels to a multiple of 16, zero filled.  Plays the role
+// of the RSCKC16 / KRSCK16 re-layouts of the reference (common/src/denox/memory/tensor/FilterLayout.hpp:74-78,104-108).
+//   pass variants:    [tap][chunk c8][n][8]
+//   stacked variants: [dx][chunk c8][3N rows][8], the rows of a chunk being the three vertical taps r = 2, 1, 0
+//                     one after the other (matching output rows j-1, j, j+1 of input row j); one such blob per
+//                     output channel part
 void conv_tc_prepare(const Variant &v, const uint16_t *kcrs, int K, int ca, int cb, uint16_t *out) {
-  const int C = ca + cb, N = pad16(K), nch = nch_of(ca) + nch_of(cb);
-  const size_t n = (size_t)9 * nch * N * 8;
-  for (size_t i = 0; i < n; ++i) out[i] = 0;
+  const int C = ca + cb, nch = nch_of(ca) + nch_of(cb);
+  const size_t total = conv_tc_weight_bytes(v, K, ca, cb) / 2;
+  for (size_t i = 0; i < total; ++i) out[i] = 0;
   if (v.p0 == 0) {
-    // stacked form: [dx][chunk][3N rows][8]; the rows of a chunk are the three vertical taps
-    // r = 2, 1, 0 one after the other (matching output rows j-1, j, j+1 of input row j)
-    for (int seg = 0; seg < 2; ++seg) {
-      const int Cs = seg ? cb : ca, cbase = seg ? ca : 0, chbase = seg ? nch_of(ca) : 0;
-      for (int r = 0; r < 3; ++r)
-        for (int sx = 0; sx < 3; ++sx)
-          for (int c = 0; c < Cs; ++c)
-            for (int k = 0; k < K; ++k)
-              out[((((size_t)sx * nch + chbase + c / 8) * 3 + (2 - r)) * N + k) * 8 + c % 8] =
-                  kcrs[((size_t)k * C + cbase + c) * 9 + r * 3 + sx];
+    int k0[8], kp[8];
+    const int n = split_parts(v, K, k0, kp);
+    size_t off = 0;
+    for (int p = 0; p < n; ++p) {
+      const int N = pad16(kp[p]);
+      for (int seg = 0; seg < 2; ++seg) {
+        const int Cs = seg ? cb : ca, cbase = seg ? ca : 0, chbase = seg ? nch_of(ca) : 0;
+        for (int r = 0; r < 3; ++r)
+          for (int sx = 0; sx < 3; ++sx)
+            for (int c = 0; c < Cs; ++c)
+              for (int k = 0; k < kp[p]; ++k)
+                out[off + ((((size_t)sx * nch + chbase + c / 8) * 3 + (2 - r)) * N + k) * 8 + c % 8] =
+                    kcrs[((size_t)(k0[p] + k) * C + cbase + c) * 9 + r * 3 + sx];
+      }
+      off += (size_t)9 * nch * N * 8;
     }
     return;
   }
+  const int N = pad16(K);
   for (int seg = 0; seg < 2; ++seg) {
     const int Cs = seg ? cb : ca, cbase = seg ? ca : 0, chbase = seg ? nch_of(ca) : 0;
     for (int t = 0; t < 9; ++t)
@@ -1910,28 +1967,71 @@ void conv_tc_prepare(const Variant &v, const uint16_t *kcrs, int K, int ca, int 
   }
 }
 
+namespace {
+// The dispatch of one output channel part: pointers advanced to the part's first channel.
+dnxcu_dispatch part_dispatch(const dnxcu_dispatch &d, int k0, int kp, size_t woff) {
+  dnxcu_dispatch p = d;
+  p.c_out = kp;
+  if (p.out) p.out = (char *)p.out + (size_t)k0 * 2;
+  if (p.out_pool) p.out_pool = (char *)p.out_pool + (size_t)k0 * 2;
+  if (p.bias) p.bias = (const char *)p.bias + (size_t)k0 * 2;
+  p.weights = (const char *)p.weights + woff;
+  return p;
+}
+}  // namespace
+
 int conv_tc_validate(const Variant &v, const dnxcu_dispatch &d) {
-  Plan pl;
-  return make_plan(v, d, pl, false);
+  if (d.c_out <= 0) return DNXCU_E_BAD_ARG;
+  int k0[8], kp[8];
+  const int n = split_parts(v, d.c_out, k0, kp);
+  if (n == 1) {
+    Plan pl;
+    return make_plan(v, d, pl, false);
+  }
+  if (d.c_out % 16) return DNXCU_E_UNSUPPORTED;
+  size_t woff = 0;
+  for (int p = 0; p < n; ++p) {
+    Plan pl;
+    const dnxcu_dispatch dp = part_dispatch(d, k0[p], kp[p], woff);
+    const int st = make_plan(v, dp, pl, false, d.c_out);
+    if (st) return st;
+    woff += (size_t)9 * (nch_of(d.c_a) + nch_of(d.c_b)) * pad16(kp[p]) * 16;
+  }
+  return DNXCU_OK;
 }
 
 void conv_tc_grid(const Variant &v, const dnxcu_dispatch &d, uint32_t g[3]) {
+  int k0[8], kp[8];
+  const int n = split_parts(v, d.c_out, k0, kp);
   Plan pl;
   g[0] = g[1] = g[2] = 1;
-  if (make_plan(v, d, pl, false) == DNXCU_OK) g[0] = (uint32_t)pl.grid;
+  const dnxcu_dispatch dp = n == 1 ? d : part_dispatch(d, k0[0], kp[0], 0);
+  if (make_plan(v, dp, pl, false, n == 1 ? 0 : d.c_out) == DNXCU_OK) g[0] = (uint32_t)pl.grid;
+  g[2] = (uint32_t)n;  // launches
 }
 
 int conv_tc_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
-  Plan pl;
-  int st = make_plan(v, d, pl, true);
-  if (st) return st;
-  switch (pl.R) {
-    case 0: return launch_stack(pl, s);
-    case 1: return launch_r<1>(pl, s);
-    case 2: return launch_r<2>(pl, s);
-    case 4: return launch_r<4>(pl, s);
-    default: return DNXCU_E_UNSUPPORTED;
+  if (d.c_out <= 0) return DNXCU_E_BAD_ARG;
+  int k0[8], kp[8];
+  const int n = split_parts(v, d.c_out, k0, kp);
+  if (n > 1 && d.c_out % 16) return DNXCU_E_UNSUPPORTED;
+  size_t woff = 0;
+  for (int p = 0; p < n; ++p) {
+    Plan pl;
+    const dnxcu_dispatch dp = n == 1 ? d : part_dispatch(d, k0[p], kp[p], woff);
+    int st = make_plan(v, dp, pl, true, n == 1 ? 0 : d.c_out);
+    if (st) return st;
+    switch (pl.R) {
+      case 0: st = launch_stack(pl, s); break;
+      case 1: st = launch_r<1>(pl, s); break;
+      case 2: st = launch_r<2>(pl, s); break;
+      case 4: st = launch_r<4>(pl, s); break;
+      default: st = DNXCU_E_UNSUPPORTED; break;
+    }
+    if (st) return st;
+    woff += (size_t)9 * (nch_of(d.c_a) + nch_of(d.c_b)) * pad16(kp[p]) * 16;
   }
+  return DNXCU_OK;
 }
 
 }  // namespace dnxcu

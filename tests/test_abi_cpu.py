@@ -190,3 +190,17 @@ def test_prepare_weights_stacked_layout():
         for r in range(3):
             for ch in range(4):
                 assert (t[sx, ch, 2 - r] == w[:, ch * 8:(ch + 1) * 8, r, sx]).all()
+
+
+def test_prepare_weights_stacked_split_layout():
+    """NSPLIT=2: one stacked blob per run of output channels (here 96 -> 48 + 48)."""
+    k, ca = 96, 16
+    w = nets.rng.he_normal_weights(10, k, ca)
+    vid = lib.find_variant("direct-conv-tc", "DY=stack#KG=2#W=resident#NSPLIT=2")
+    t = lib.prepare_weights(vid, w, ca).view(np.float16).reshape(2, 3, 2, 3, 48, 8)
+    for part in range(2):
+        for sx in range(3):
+            for r in range(3):
+                for ch in range(2):
+                    want = w[part * 48:(part + 1) * 48, ch * 8:(ch + 1) * 8, r, sx]
+                    assert (t[part, sx, ch, 2 - r] == want).all()
