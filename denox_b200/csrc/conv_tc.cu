@@ -109,6 +109,7 @@ struct TcArgs {
   uint32_t tmem_cols;
   int desc_swap;  // debugging aid: exchange the two descriptor strides
   long long *trace;  // debugging aid: per role time stamps of CTA 0 (nullptr = off)
+  int loop_issue;  // debugging aid: MMAs issued by the generic loops instead of the straight line code
   int skip;       // debugging aid (timing only, results wrong): 1 no input loads, 2 no MMAs, 4 no output stores
 };
 
@@ -142,10 +143,23 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another ran out).
 // SLEEP_NS > 0: back off between polls, so that a waiting warp does not take issue
 // slots from the warps that share its scheduler (the MMA issuer above all).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
 template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
                                           int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_test_wait(bar, parity)) return true;  // the cheap probe: about half the cost of try_wait when it passes
   const unsigned long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
     if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
@@ -893,6 +907,42 @@ struct Run {
   uint32_t acc;    // 0: overwrite (fresh block), 1: accumulate
 };
 
+// The MMAs of one input row (all horizontal taps, NK K steps, NR runs of TMEM blocks) as straight
+// line code.  Every instruction gets descriptor registers of its own, so the issuing thread keeps
+// several MMAs in flight; a loop that reuses the registers issues three times slower (measured).
+// `skip00`: the row's first MMA position (tap 0, K step 0) was issued by the caller.
+template <int NK, int NR>
+__device__ __forceinline__ void st_issue_row(uint32_t hi, uint32_t row_lo, uint32_t b_lo, uint32_t wdx16, uint32_t kstep_b,
+                                             const Run &r0, const Run &r1, bool skip00) {
+  constexpr uint32_t kstep_a = (2u * CHUNK_PITCH) >> 4;
+#pragma unroll
+  for (int dx = 0; dx < 3; ++dx) {
+#pragma unroll
+    for (int kc = 0; kc < NK; ++kc) {
+      if (dx == 0 && kc == 0 && skip00) continue;
+      const uint32_t a = row_lo + (uint32_t)dx + (uint32_t)kc * kstep_a;
+      const uint32_t b = b_lo + (uint32_t)dx * wdx16 + (uint32_t)kc * kstep_b;
+      tc_mma(r0.col, ((uint64_t)hi << 32) | a, ((uint64_t)hi << 32) | (b + r0.boff), r0.idesc, 1u);
+      if (NR == 2) tc_mma(r1.col, ((uint64_t)hi << 32) | a, ((uint64_t)hi << 32) | (b + r1.boff), r1.idesc, 1u);
+    }
+  }
+}
+template <int NR>
+__device__ __forceinline__ bool st_issue_nk(int nk, uint32_t hi, uint32_t row_lo, uint32_t b_lo, uint32_t wdx16,
+                                            uint32_t kstep_b, const Run &r0, const Run &r1, bool skip00) {
+  switch (nk) {
+    case 1: st_issue_row<1, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
+    case 2: st_issue_row<2, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
+    case 3: st_issue_row<3, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
+    case 4: st_issue_row<4, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
+    case 5: st_issue_row<5, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
+    case 6: st_issue_row<6, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
+    case 7: st_issue_row<7, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
+    case 8: st_issue_row<8, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
+    default: return false;
+  }
+}
+
 // ---- staged epilogue --------------------------------------------------------
 // A thread owns one pixel after tcgen05.ld, so direct stores put 32 lanes on 32
 // different cache lines (measured: about 170 cycles per store instruction, 2700 of the
@@ -1179,8 +1229,19 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
             const uint32_t row_lo = (((slots_addr + (uint32_t)slot * slot_bytes) & 0x3FFFFu) >> 4) | a_lo0;
             const int nk16 = g.gch[gi] >> 1;
             const uint32_t wgrp = (uint32_t)g.gc0[gi] * 3u * N16;  // group's first chunk, in 16 byte units
+            bool done = false;
+            if (nk16 <= 8 && R2.acc == 2 && !g.loop_issue) {
+              const uint32_t b_lo = (((w_addr & 0x3FFFFu) >> 4) + wgrp) | b_lo0;
+              if (gi == 0) {
+                if (F0.acc != 2) mma1(F0.col, row_lo, b_lo + F0.boff, F0.idesc, F0.acc);
+                if (F1.acc != 2) mma1(F1.col, row_lo, b_lo + F1.boff, F1.idesc, F1.acc);
+                if (F2.acc != 2) mma1(F2.col, row_lo, b_lo + F2.boff, F2.idesc, F2.acc);
+              }
+              done = oneR ? st_issue_nk<1>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0, gi == 0)
+                          : st_issue_nk<2>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1, gi == 0);
+            }
 #pragma unroll
-            for (int dx = 0; dx < 3; ++dx) {
+            for (int dx = 0; dx < 3 && !done; ++dx) {
               uint32_t b_lo = ((((w_addr + (uint32_t)dx * wdx_bytes) & 0x3FFFFu) >> 4) + wgrp) | b_lo0;
               uint32_t a_lo = row_lo + (uint32_t)dx;
               int kc = 0;
@@ -1784,6 +1845,8 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   g.desc_swap = (sw && sw[0] == '1') ? 1 : 0;
   const char *sk = getenv("DNXCU_TC_SKIP");
   g.skip = sk ? atoi(sk) : 0;
+  const char *li = getenv("DNXCU_TC_LOOP_ISSUE");
+  g.loop_issue = (li && li[0] == '1') ? 1 : 0;
   // time line tracing: the caller's status buffer must then hold 8 + 3*64*6 64-bit words
   const char *tr = getenv("DNXCU_TC_TRACE");
   g.trace = (tr && tr[0] == '1' && d.device_status) ? reinterpret_cast<long long *>(d.device_status) + 8 : nullptr;
