@@ -875,7 +875,7 @@ __device__ __forceinline__ void epi_fast(const TcArgs &g, uint32_t t0, uint32_t 
 //   - runs of blocks are split where the ring wraps and where N' would exceed 256
 //   - an input slot is released as soon as its own row's MMAs are committed
 // Two epilogue teams of four warps take alternate row pairs.
-constexpr int ST_THREADS = 448;        // MMA, weights, 8 epilogue warps, 4 producer warps
+constexpr int ST_THREADS = 512;        // MMA, weights, 8 epilogue warps, 4 producer warps, 2 descriptor warps
 constexpr int ST_MAX_BLOCKS = 16;
 constexpr int ST_BAR_FULL = 0;
 constexpr int ST_BAR_EMPTY = ST_BAR_FULL + MAX_SLOTS;
@@ -887,6 +887,14 @@ constexpr int ST_BAR_COUNT = ST_BAR_RAW + MAX_SLOTS;
 static_assert(ST_BAR_COUNT * 8 + 16 <= HEADER_BYTES, "header too small");
 constexpr int ST_OFF_TMEM_PTR = ST_BAR_COUNT * 8;
 constexpr int ST_OFF_ABORT = ST_OFF_TMEM_PTR + 4;
+// entry descriptors, one per slot (index: pipeline's barrier offset + slot), written by the descriptor threads
+constexpr int ST_DESC_BYTES = 96;
+constexpr int ST_OFF_DESC = HEADER_BYTES;
+constexpr int ST_HEADER_BYTES = HEADER_BYTES + MAX_SLOTS * ST_DESC_BYTES;
+static_assert(ST_HEADER_BYTES % 128 == 0, "weights must start on a 128 byte boundary");
+// descriptor flag word: bits 0-3 K steps of 16, then
+constexpr uint32_t DF_NR2 = 1u << 4, DF_FIRST = 1u << 5, DF_NEEDC = 1u << 6, DF_LAST = 1u << 7;
+constexpr uint32_t DF_F0 = 1u << 8, DF_F1 = 1u << 9, DF_F2 = 1u << 10;  // bits 11-13: their accumulate flags
 
 struct StUnit {
   int x0, y0, rows_out;
@@ -968,6 +976,9 @@ __device__ __forceinline__ void stage_cols(const TcArgs &g, uint32_t taddr, int 
                  : "memory");
 }
 
+__device__ __forceinline__ void sts16(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 __device__ __forceinline__ uint4 lds16(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
@@ -1031,7 +1042,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   const int nch = g.a.nch + g.b.nch;
   const int N = g.N, NB = g.NB, P = g.P;
   const uint32_t wdx_bytes = (uint32_t)nch * 3u * N * 16u;  // one horizontal tap: all chunks x 3N rows
-  const uint32_t w_addr = sbase + HEADER_BYTES;
+  const uint32_t w_addr = sbase + ST_HEADER_BYTES;
   const uint32_t slot_bytes = (uint32_t)g.gmax * CHUNK_PITCH;
   const uint32_t slots_addr0 = w_addr + ((wdx_bytes * 3u + 127u) & ~127u);
   const int S = g.S;  // slots per pipeline
@@ -1042,7 +1053,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     *abort_flag = 0;
     // who completes a slot: the TMA bytes alone; or TMA bytes + the producer warps' cp.async part; or, in expand
     // mode, the producer warps alone after they have expanded the TMA data that landed on the raw barrier
-    const uint32_t full_count = g.xp ? (uint32_t)nprod_warps : (g.cpa ? (uint32_t)nprod_warps + 1u : 1u);
+    const uint32_t full_count = 1u + (g.xp ? (uint32_t)nprod_warps : (g.cpa ? (uint32_t)nprod_warps + 1u : 1u));  // + the descriptor thread
     for (int i = 0; i < MAX_SLOTS; ++i) {
       mbar_init(bar(ST_BAR_FULL + i), full_count);
       mbar_init(bar(ST_BAR_EMPTY + i), 1);
@@ -1143,162 +1154,68 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   if (warp == 1) __syncwarp();
 
   if (warp < P) {
-    // ---------------- MMA issue of pipeline `warp` (warp-uniform loop, lane 0 issues) ----------------
+    // ---------------- MMA issue of pipeline `warp`: one thread, one descriptor per entry ----------------
+    // Everything that depends on where an entry sits in its unit (TMEM blocks, runs, barriers) was worked
+    // out by the pipeline's descriptor thread and lies in shared memory when the slot's barrier completes;
+    // this thread only waits, loads six vectors and issues.  It is the thread the kernel's speed hangs on.
     const int pipe = warp;
     const int bofs = pipe * ST_PIPE_STRIDE;
-    const uint32_t tmem_base = tmem_base0 + (uint32_t)(pipe * NB * N);
-    const uint32_t slots_addr = slots_addr0 + (uint32_t)(pipe * S) * slot_bytes;
-    const bool issuer = lane == 0;
     const uint32_t a_hi = (128u >> 4) | (1u << 14), b_hi = a_hi;
-    const uint32_t a_lo0 = ((uint32_t)CHUNK_PITCH >> 4) << 16;
-    const uint32_t b_lo0 = (3u * N) << 16;  // leading offset = chunk pitch = 3N rows x 16 bytes, >> 4
     const uint32_t kstep_a = (2u * CHUNK_PITCH) >> 4, kstep_b = 2u * 3u * N;
-    const uint32_t idesc0 = (1u << 4) | ((uint32_t)(STRIP >> 4) << 24);
     bool ok = mbar_wait(bar(ST_BAR_WRES), 0, abort_flag, g.status, 1);
-    const bool two = 2 * N <= 256, three = 3 * N <= 256;
-    const uint32_t N16 = (uint32_t)N;  // weight rows of one vertical tap, in 16 byte units of a chunk
-    const uint32_t kb2 = 2u * kstep_b, kb3 = 3u * kstep_b, kb4 = 4u * kstep_b;
-    const bool tr = g.trace != nullptr && blockIdx.x == 0 && issuer && pipe == 0;
+    const bool tr = g.trace != nullptr && blockIdx.x == 0 && lane == 0 && pipe == 0;
     auto mma1 = [&](uint32_t d, uint32_t alo, uint32_t blo, uint32_t idesc, uint32_t acc) {
       tc_mma(d, ((uint64_t)a_hi << 32) | alo, ((uint64_t)b_hi << 32) | blo, idesc, acc);
     };
-    // running ring state (no divisions in the loop): input slot + its phase, newest TMEM block + its phase
-    int slot = 0, pos = 0;
-    uint32_t fphase = 0;
-    int blkC = 0;
-    uint32_t cphase = 1;  // parity to wait for on tempty[blkC]: the first round passes
-    for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
-      const StUnit t = st_unit_of(g, u);
-      const int rows_in = t.rows_out + 2;
-      int blkA = 0, blkB = 0;  // blocks of output rows jj-2, jj-1 (stack positions 0, 1); blkC: row jj (position 2)
-      for (int jj = 0; ok && jj < rows_in; ++jj) {
-        const bool vA = jj >= 2, vB = jj >= 1 && jj <= t.rows_out, vC = jj < t.rows_out;
-        if (vC) {
-          ok = mbar_wait(bar(ST_BAR_TEMPTY + bofs + blkC), cphase, abort_flag, g.status, 3);
-          if (!ok) break;
+    if (lane == 0 && ok && (int)blockIdx.x * P + pipe < g.nunits) {
+      int slot = 0, pos = 0;
+      uint32_t fphase = 0;
+      for (;;) {
+        if (tr) trace(g, 0, pos, 0);
+        if (!mbar_wait(bar(ST_BAR_FULL + bofs + slot), fphase, abort_flag, g.status, 2)) break;
+        if (tr) trace(g, 0, pos, 1);
+        const uint32_t da = sbase + ST_OFF_DESC + (uint32_t)(bofs + slot) * ST_DESC_BYTES;
+        const uint4 q0 = lds16(da), q1 = lds16(da + 16), q2 = lds16(da + 32), q3 = lds16(da + 48), q4 = lds16(da + 64),
+                    q5 = lds16(da + 80);
+        const uint32_t flags = q0.z;
+        if (flags & DF_NEEDC) {
+          if (!mbar_wait(q0.w, q1.x, abort_flag, g.status, 3)) break;
         }
-        auto mk = [&](int sidx, int len, uint32_t acc) {
-          Run r;
-          const int blk = sidx == 0 ? blkA : (sidx == 1 ? blkB : blkC);
-          r.col = tmem_base + (uint32_t)(blk * N);
-          r.boff = (uint32_t)sidx * N16;
-          r.idesc = idesc0 | ((uint32_t)((len * N) >> 3) << 17);
-          r.acc = acc;
-          return r;
-        };
-        // runs of neighbouring blocks one MMA can cover: R* for every MMA of the row but the
-        // first, F* for the first one (the fresh block C on its own, overwriting); acc == 2: unused
-        Run R0 = {0, 0, 0, 2}, R1 = R0, R2 = R0, F0 = R0, F1 = R0, F2 = R0;
-        if (vA && vB && vC && blkB != 0 && blkC != 0 && three) {  // the common case
-          R0 = mk(0, 3, 1);
-          F0 = mk(0, 2, 1);
-          F1 = mk(2, 1, 0);
-        } else {
-          const bool mAB = vA && vB && blkB != 0 && two;
-          const bool mBC = vB && vC && blkC != 0 && two && (!mAB || three);
-          if (mAB && mBC) {
-            R0 = mk(0, 3, 1);
-          } else if (mAB) {
-            R0 = mk(0, 2, 1);
-            if (vC) R1 = mk(2, 1, 1);
-          } else if (mBC) {
-            if (vA) { R0 = mk(0, 1, 1); R1 = mk(1, 2, 1); } else { R0 = mk(1, 2, 1); }
-          } else {
-            if (vA) R0 = mk(0, 1, 1);
-            if (vB) { if (vA) R1 = mk(1, 1, 1); else R0 = mk(1, 1, 1); }
-            if (vC) { if (vA && vB) R2 = mk(2, 1, 1); else if (vA || vB) R1 = mk(2, 1, 1); else R0 = mk(2, 1, 1); }
+        tc_fence_after();
+        if (!(g.skip & 2)) {
+          const uint32_t row_lo = q0.x, b_lo = q0.y;
+          const int nk16 = (int)(flags & 15u);
+          const bool first = (flags & DF_FIRST) != 0;
+          const Run R0 = {q2.x, q2.y, q2.z, 1u}, R1 = {q2.w, q3.x, q3.y, 1u};
+          if (first) {
+            if (flags & DF_F0) mma1(q3.z, row_lo, b_lo + q3.w, q4.x, (flags >> 11) & 1u);
+            if (flags & DF_F1) mma1(q4.y, row_lo, b_lo + q4.z, q4.w, (flags >> 12) & 1u);
+            if (flags & DF_F2) mma1(q5.x, row_lo, b_lo + q5.y, q5.z, (flags >> 13) & 1u);
           }
-          if (mAB) {
-            F0 = mk(0, 2, 1);
-            if (vC) F1 = mk(2, 1, 0);
-          } else {
-            if (vA) F0 = mk(0, 1, 1);
-            if (vB) { if (vA) F1 = mk(1, 1, 1); else F0 = mk(1, 1, 1); }
-            if (vC) { if (vA && vB) F2 = mk(2, 1, 0); else if (vA || vB) F1 = mk(2, 1, 0); else F0 = mk(2, 1, 0); }
+          bool done = false;
+          if (!g.loop_issue)
+            done = (flags & DF_NR2) ? st_issue_nk<2>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1, first)
+                                    : st_issue_nk<1>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0, first);
+          if (!done) {
+            // more K steps than the straight line forms cover
+            for (int dx = 0; dx < 3; ++dx)
+              for (int kc = (first && dx == 0) ? 1 : 0; kc < nk16; ++kc) {
+                const uint32_t a = row_lo + (uint32_t)dx + (uint32_t)kc * kstep_a;
+                const uint32_t b = b_lo + (uint32_t)dx * (wdx_bytes >> 4) + (uint32_t)kc * kstep_b;
+                mma1(R0.col, a, b + R0.boff, R0.idesc, 1u);
+                if (flags & DF_NR2) mma1(R1.col, a, b + R1.boff, R1.idesc, 1u);
+              }
           }
         }
-        const bool oneR = R1.acc == 2;
-        for (int gi = 0; ok && gi < g.G; ++gi) {
-          if (tr) trace(g, 0, pos, 0);
-          ok = mbar_wait(bar(ST_BAR_FULL + bofs + slot), fphase, abort_flag, g.status, 2);
-          if (!ok) break;
-          if (tr) trace(g, 0, pos, 1);
-          tc_fence_after();
-          if (issuer && !(g.skip & 2)) {
-            // lane 0 alone walks the taps; per MMA: one or two adds, the descriptor words, the instruction
-            const uint32_t row_lo = (((slots_addr + (uint32_t)slot * slot_bytes) & 0x3FFFFu) >> 4) | a_lo0;
-            const int nk16 = g.gch[gi] >> 1;
-            const uint32_t wgrp = (uint32_t)g.gc0[gi] * 3u * N16;  // group's first chunk, in 16 byte units
-            bool done = false;
-            if (nk16 <= 8 && R2.acc == 2 && !g.loop_issue) {
-              const uint32_t b_lo = (((w_addr & 0x3FFFFu) >> 4) + wgrp) | b_lo0;
-              if (gi == 0) {
-                if (F0.acc != 2) mma1(F0.col, row_lo, b_lo + F0.boff, F0.idesc, F0.acc);
-                if (F1.acc != 2) mma1(F1.col, row_lo, b_lo + F1.boff, F1.idesc, F1.acc);
-                if (F2.acc != 2) mma1(F2.col, row_lo, b_lo + F2.boff, F2.idesc, F2.acc);
-              }
-              done = oneR ? st_issue_nk<1>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0, gi == 0)
-                          : st_issue_nk<2>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1, gi == 0);
-            }
-#pragma unroll
-            for (int dx = 0; dx < 3 && !done; ++dx) {
-              uint32_t b_lo = ((((w_addr + (uint32_t)dx * wdx_bytes) & 0x3FFFFu) >> 4) + wgrp) | b_lo0;
-              uint32_t a_lo = row_lo + (uint32_t)dx;
-              int kc = 0;
-              if (gi == 0 && dx == 0) {
-                if (F0.acc != 2) mma1(F0.col, a_lo, b_lo + F0.boff, F0.idesc, F0.acc);
-                if (F1.acc != 2) mma1(F1.col, a_lo, b_lo + F1.boff, F1.idesc, F1.acc);
-                if (F2.acc != 2) mma1(F2.col, a_lo, b_lo + F2.boff, F2.idesc, F2.acc);
-                b_lo += kstep_b;
-                a_lo += kstep_a;
-                kc = 1;
-              }
-              if (oneR) {
-                uint32_t b0 = b_lo + R0.boff;
-                for (; kc + 4 <= nk16; kc += 4) {
-                  mma1(R0.col, a_lo, b0, R0.idesc, 1u);
-                  mma1(R0.col, a_lo + kstep_a, b0 + kstep_b, R0.idesc, 1u);
-                  mma1(R0.col, a_lo + 2u * kstep_a, b0 + kb2, R0.idesc, 1u);
-                  mma1(R0.col, a_lo + 3u * kstep_a, b0 + kb3, R0.idesc, 1u);
-                  a_lo += 4u * kstep_a;
-                  b0 += kb4;
-                }
-                for (; kc < nk16; ++kc) {
-                  mma1(R0.col, a_lo, b0, R0.idesc, 1u);
-                  a_lo += kstep_a;
-                  b0 += kstep_b;
-                }
-              } else {
-#pragma unroll 1
-                for (; kc < nk16; ++kc) {
-                  mma1(R0.col, a_lo, b_lo + R0.boff, R0.idesc, 1u);
-                  mma1(R1.col, a_lo, b_lo + R1.boff, R1.idesc, 1u);
-                  if (R2.acc != 2) mma1(R2.col, a_lo, b_lo + R2.boff, R2.idesc, 1u);
-                  b_lo += kstep_b;
-                  a_lo += kstep_a;
-                }
-              }
-            }
-          }
-          if (issuer) {
-            if (tr) trace(g, 0, pos, 2);
-            tc_commit(bar(ST_BAR_EMPTY + bofs + slot));
-            if (gi == g.G - 1 && vA) tc_commit(bar(ST_BAR_TFULL + bofs + blkA));
-            if (tr) trace(g, 0, pos, 3);
-          }
-          ++pos;
-          if (++slot == S) {
-            slot = 0;
-            fphase ^= 1u;
-          }
-        }
-        blkA = blkB;
-        blkB = blkC;
-        if (vC) {
-          if (++blkC == NB) {
-            blkC = 0;
-            cphase ^= 1u;
-          }
+        if (tr) trace(g, 0, pos, 2);
+        tc_commit(bar(ST_BAR_EMPTY + bofs + slot));
+        if (q1.y) tc_commit(q1.y);
+        if (tr) trace(g, 0, pos, 3);
+        if (flags & DF_LAST) break;
+        ++pos;
+        if (++slot == S) {
+          slot = 0;
+          fphase ^= 1u;
         }
       }
     }
@@ -1418,7 +1335,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         }
       }
     }
-  } else if (warp >= 10) {
+  } else if (warp >= 10 && warp < 14) {
     // ---------------- input slots ----------------
     // P == 2: warps 10, 11 feed pipeline 0 and warps 12, 13 pipeline 1; P == 1: all four feed pipeline 0.
     const int pipe = P == 2 ? (warp - 10) >> 1 : 0;
@@ -1591,6 +1508,118 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           for (; signalled < pos; ++signalled) mbar_arrive(bar(ST_BAR_FULL + bofs + signalled % S));
       }
     }
+  } else if (warp >= 14 && warp - 14 < P && lane == 0) {
+    // ---------------- entry descriptors: one thread per pipeline ----------------
+    // Walks the same (unit, input row, K group) sequence as the producers, keeps the ring of TMEM blocks
+    // and writes what the MMA thread needs for the entry into the slot's descriptor, then arrives on the
+    // slot's barrier: the descriptor is visible when the barrier completes.
+    const int pipe = warp - 14;
+    const int bofs = pipe * ST_PIPE_STRIDE;
+    const uint32_t tmem_base = tmem_base0 + (uint32_t)(pipe * NB * N);
+    const uint32_t slots_addr = slots_addr0 + (uint32_t)(pipe * S) * slot_bytes;
+    const uint32_t a_lo0 = ((uint32_t)CHUNK_PITCH >> 4) << 16;
+    const uint32_t b_lo0 = (3u * N) << 16;  // leading offset = chunk pitch = 3N rows x 16 bytes, >> 4
+    const uint32_t idesc0 = (1u << 4) | ((uint32_t)(STRIP >> 4) << 24);
+    const bool two = 2 * N <= 256, three = 3 * N <= 256;
+    const uint32_t N16 = (uint32_t)N;  // weight rows of one vertical tap, in 16 byte units of a chunk
+    int slot = 0;
+    uint32_t ephase = 1;  // parity to wait for on the empty barrier: first round passes
+    int blkC = 0;
+    uint32_t cphase = 1;  // parity to wait for on tempty[blkC]: the first round passes
+    bool ok = true;
+    for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
+      const StUnit t = st_unit_of(g, u);
+      const int rows_in = t.rows_out + 2;
+      const bool last_unit = u + unit_stride >= g.nunits;
+      int blkA = 0, blkB = 0;  // blocks of output rows jj-2, jj-1 (stack positions 0, 1); blkC: row jj (position 2)
+      for (int jj = 0; ok && jj < rows_in; ++jj) {
+        const bool vA = jj >= 2, vB = jj >= 1 && jj <= t.rows_out, vC = jj < t.rows_out;
+        auto mk = [&](int sidx, int len, uint32_t acc) {
+          Run r;
+          const int blk = sidx == 0 ? blkA : (sidx == 1 ? blkB : blkC);
+          r.col = tmem_base + (uint32_t)(blk * N);
+          r.boff = (uint32_t)sidx * N16;
+          r.idesc = idesc0 | ((uint32_t)((len * N) >> 3) << 17);
+          r.acc = acc;
+          return r;
+        };
+        // runs of neighbouring blocks one MMA can cover: R* for every MMA of the row but the
+        // first, F* for the first one (the fresh block C on its own, overwriting); acc == 2: unused
+        Run R0 = {0, 0, 0, 2}, R1 = R0, R2 = R0, F0 = R0, F1 = R0, F2 = R0;
+        if (vA && vB && vC && blkB != 0 && blkC != 0 && three) {  // the common case
+          R0 = mk(0, 3, 1);
+          F0 = mk(0, 2, 1);
+          F1 = mk(2, 1, 0);
+        } else {
+          const bool mAB = vA && vB && blkB != 0 && two;
+          const bool mBC = vB && vC && blkC != 0 && two && (!mAB || three);
+          if (mAB && mBC) {
+            R0 = mk(0, 3, 1);
+          } else if (mAB) {
+            R0 = mk(0, 2, 1);
+            if (vC) R1 = mk(2, 1, 1);
+          } else if (mBC) {
+            if (vA) { R0 = mk(0, 1, 1); R1 = mk(1, 2, 1); } else { R0 = mk(1, 2, 1); }
+          } else {
+            if (vA) R0 = mk(0, 1, 1);
+            if (vB) { if (vA) R1 = mk(1, 1, 1); else R0 = mk(1, 1, 1); }
+            if (vC) { if (vA && vB) R2 = mk(2, 1, 1); else if (vA || vB) R1 = mk(2, 1, 1); else R0 = mk(2, 1, 1); }
+          }
+          if (mAB) {
+            F0 = mk(0, 2, 1);
+            if (vC) F1 = mk(2, 1, 0);
+          } else {
+            if (vA) F0 = mk(0, 1, 1);
+            if (vB) { if (vA) F1 = mk(1, 1, 1); else F0 = mk(1, 1, 1); }
+            if (vC) { if (vA && vB) F2 = mk(2, 1, 0); else if (vA || vB) F1 = mk(2, 1, 0); else F0 = mk(2, 1, 0); }
+          }
+        }
+        if (R2.acc != 2) {
+          // three separate runs need a block ring shorter than the plan ever makes: refuse instead of computing wrong
+          *abort_flag = 1;
+          if (g.status) atomicCAS(g.status, 0, 9);
+          ok = false;
+          break;
+        }
+        uint32_t rowflags = 0;
+        if (R1.acc != 2) rowflags |= DF_NR2;
+        if (F0.acc != 2) rowflags |= DF_F0 | (F0.acc << 11);
+        if (F1.acc != 2) rowflags |= DF_F1 | (F1.acc << 12);
+        if (F2.acc != 2) rowflags |= DF_F2 | (F2.acc << 13);
+        for (int gi = 0; ok && gi < g.G; ++gi) {
+          ok = mbar_wait<32>(bar(ST_BAR_EMPTY + bofs + slot), ephase, abort_flag, g.status, 7);
+          if (!ok) break;
+          uint32_t flags = rowflags | (uint32_t)(g.gch[gi] >> 1);
+          if (gi == 0) flags |= DF_FIRST;
+          if (gi == 0 && vC) flags |= DF_NEEDC;
+          if (last_unit && jj == rows_in - 1 && gi == g.G - 1) flags |= DF_LAST;
+          const uint32_t row_lo = (((slots_addr + (uint32_t)slot * slot_bytes) & 0x3FFFFu) >> 4) | a_lo0;
+          const uint32_t wgrp = (uint32_t)g.gc0[gi] * 3u * N16;  // group's first chunk, in 16 byte units
+          const uint32_t b_lo = (((w_addr & 0x3FFFFu) >> 4) + wgrp) | b_lo0;
+          const uint32_t tfbar = (gi == g.G - 1 && vA) ? bar(ST_BAR_TFULL + bofs + blkA) : 0u;
+          const uint32_t da = sbase + ST_OFF_DESC + (uint32_t)(bofs + slot) * ST_DESC_BYTES;
+          sts16(da, make_uint4(row_lo, b_lo, flags, bar(ST_BAR_TEMPTY + bofs + blkC)));
+          sts16(da + 16, make_uint4(cphase, tfbar, 0u, 0u));
+          sts16(da + 32, make_uint4(R0.col, R0.boff, R0.idesc, R1.col));
+          sts16(da + 48, make_uint4(R1.boff, R1.idesc, F0.col, F0.boff));
+          sts16(da + 64, make_uint4(F0.idesc, F1.col, F1.boff, F1.idesc));
+          sts16(da + 80, make_uint4(F2.col, F2.boff, F2.idesc, 0u));
+          mbar_arrive(bar(ST_BAR_FULL + bofs + slot));
+          if (++slot == S) {
+            slot = 0;
+            ephase ^= 1u;
+          }
+        }
+        blkA = blkB;
+        blkB = blkC;
+        if (vC) {
+          if (++blkC == NB) {
+            blkC = 0;
+            cphase ^= 1u;
+          }
+        }
+      }
+    }
   }
 
   tc_fence_before();
@@ -1712,7 +1741,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   const bool stage_possible = g.K % 8 == 0 && !(nost && nost[0] == '1');
   const size_t stage_pitch = (size_t)g.K * 2 + 16;
   const size_t stage_per_warp = (g.pool ? 2 : 1) * 32 * stage_pitch;
-  const size_t base_bytes = HEADER_BYTES + wregion;
+  const size_t base_bytes = ST_HEADER_BYTES + wregion;
   const size_t plain_slot = (size_t)g.gmax * CHUNK_PITCH;
   const bool p2_possible = 4 * g.N <= 256 && !(np && np[0] == '1');
   // candidate configurations, best first: (pipelines, expand, staging)
@@ -1727,7 +1756,8 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
     if (tst && !stage_possible) continue;
     const size_t sb = plain_slot + (txp ? xp_src_bytes : 0);
     const size_t st = tst ? (size_t)4 * tp * stage_per_warp : 0;
-    if (base_bytes + st + (size_t)4 * tp * sb > SMEM_LIMIT) continue;
+    const int min_slots = tp == 2 ? 3 : 4;  // two issuing threads pay for a shorter ring
+    if (base_bytes + st + (size_t)min_slots * tp * sb > SMEM_LIMIT) continue;
     P = tp;
     slot_bytes = sb;
     stage_total = st;
@@ -1757,7 +1787,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   while (p2 < (uint32_t)(P * g.NB * g.N)) p2 <<= 1;
   g.tmem_cols = p2;
   g.D = g.S - 1 < MAX_DEPTH ? g.S - 1 : MAX_DEPTH;
-  pl.smem = HEADER_BYTES + wregion + (size_t)P * g.S * slot_bytes + stage_total;
+  pl.smem = ST_HEADER_BYTES + wregion + (size_t)P * g.S * slot_bytes + stage_total;
   const int sms = sm_count();
   const int lanes = sms * P;
   double best = 1e30;
