@@ -893,7 +893,7 @@ constexpr int ST_OFF_DESC = HEADER_BYTES;
 constexpr int ST_HEADER_BYTES = HEADER_BYTES + MAX_SLOTS * ST_DESC_BYTES;
 static_assert(ST_HEADER_BYTES % 128 == 0, "weights must start on a 128 byte boundary");
 // descriptor flag word: bits 0-3 K steps of 16, then
-constexpr uint32_t DF_NR2 = 1u << 4, DF_FIRST = 1u << 5, DF_NEEDC = 1u << 6, DF_LAST = 1u << 7;
+constexpr uint32_t DF_NR2 = 1u << 4, DF_FIRST = 1u << 5, DF_LAST = 1u << 7;
 constexpr uint32_t DF_F0 = 1u << 8, DF_F1 = 1u << 9, DF_F2 = 1u << 10;  // bits 11-13: their accumulate flags
 
 struct StUnit {
@@ -1178,9 +1178,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         const uint4 q0 = lds16(da), q1 = lds16(da + 16), q2 = lds16(da + 32), q3 = lds16(da + 48), q4 = lds16(da + 64),
                     q5 = lds16(da + 80);
         const uint32_t flags = q0.z;
-        if (flags & DF_NEEDC) {
-          if (!mbar_wait(q0.w, q1.x, abort_flag, g.status, 3)) break;
-        }
         tc_fence_after();
         if (!(g.skip & 2)) {
           const uint32_t row_lo = q0.x, b_lo = q0.y;
@@ -1188,9 +1185,14 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           const bool first = (flags & DF_FIRST) != 0;
           const Run R0 = {q2.x, q2.y, q2.z, 1u}, R1 = {q2.w, q3.x, q3.y, 1u};
           if (first) {
-            if (flags & DF_F0) mma1(q3.z, row_lo, b_lo + q3.w, q4.x, (flags >> 11) & 1u);
+            // F0 always exists; a guarded MMA costs its issue time even when it is predicated off, so the
+            // rare third one gets a branch of its own
+            mma1(q3.z, row_lo, b_lo + q3.w, q4.x, (flags >> 11) & 1u);
             if (flags & DF_F1) mma1(q4.y, row_lo, b_lo + q4.z, q4.w, (flags >> 12) & 1u);
-            if (flags & DF_F2) mma1(q5.x, row_lo, b_lo + q5.y, q5.z, (flags >> 13) & 1u);
+            if (__builtin_expect((flags & DF_F2) != 0, 0)) {
+              mma1(q5.x, row_lo, b_lo + q5.y, q5.z, (flags >> 13) & 1u);
+              asm volatile("" ::: "memory");
+            }
           }
           bool done = false;
           if (!g.loop_issue)
@@ -1591,7 +1593,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           if (!ok) break;
           uint32_t flags = rowflags | (uint32_t)(g.gch[gi] >> 1);
           if (gi == 0) flags |= DF_FIRST;
-          if (gi == 0 && vC) flags |= DF_NEEDC;
           if (last_unit && jj == rows_in - 1 && gi == g.G - 1) flags |= DF_LAST;
           const uint32_t row_lo = (((slots_addr + (uint32_t)slot * slot_bytes) & 0x3FFFFu) >> 4) | a_lo0;
           const uint32_t wgrp = (uint32_t)g.gc0[gi] * 3u * N16;  // group's first chunk, in 16 byte units
@@ -1604,6 +1605,11 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           sts16(da + 48, make_uint4(R1.boff, R1.idesc, F0.col, F0.boff));
           sts16(da + 64, make_uint4(F0.idesc, F1.col, F1.boff, F1.idesc));
           sts16(da + 80, make_uint4(F2.col, F2.boff, F2.idesc, 0u));
+          // the row's fresh TMEM block must have been drained before the MMA thread may start the row
+          if (gi == 0 && vC) {
+            ok = mbar_wait<32>(bar(ST_BAR_TEMPTY + bofs + blkC), cphase, abort_flag, g.status, 3);
+            if (!ok) break;
+          }
           mbar_arrive(bar(ST_BAR_FULL + bofs + slot));
           if (++slot == S) {
             slot = 0;
