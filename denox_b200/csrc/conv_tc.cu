@@ -234,6 +234,25 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, int 
       : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Zeroes `ncols` (a multiple of 16) columns of the calling warp's 32 TMEM lanes.
+__device__ __forceinline__ void tc_zero_cols(uint32_t taddr, int ncols) {
+  const uint32_t z = 0u;
+  int c0 = 0;
+#pragma unroll 1
+  for (; c0 + 32 <= ncols; c0 += 32)
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, "
+        "%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr + (uint32_t)c0),
+        "r"(z)
+        : "memory");
+  if (c0 < ncols)
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(
+            taddr + (uint32_t)c0),
+        "r"(z)
+        : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 
 // Shared memory matrix descriptor, no swizzle, K major:
 // bits [0,14) start >> 4, [16,30) leading byte offset >> 4 (between the two
@@ -888,13 +907,12 @@ static_assert(ST_BAR_COUNT * 8 + 16 <= HEADER_BYTES, "header too small");
 constexpr int ST_OFF_TMEM_PTR = ST_BAR_COUNT * 8;
 constexpr int ST_OFF_ABORT = ST_OFF_TMEM_PTR + 4;
 // entry descriptors, one per slot (index: pipeline's barrier offset + slot), written by the descriptor threads
-constexpr int ST_DESC_BYTES = 96;
+constexpr int ST_DESC_BYTES = 48;
 constexpr int ST_OFF_DESC = HEADER_BYTES;
 constexpr int ST_HEADER_BYTES = HEADER_BYTES + MAX_SLOTS * ST_DESC_BYTES;
 static_assert(ST_HEADER_BYTES % 128 == 0, "weights must start on a 128 byte boundary");
 // descriptor flag word: bits 0-3 K steps of 16, then
-constexpr uint32_t DF_NR2 = 1u << 4, DF_FIRST = 1u << 5, DF_LAST = 1u << 7;
-constexpr uint32_t DF_F0 = 1u << 8, DF_F1 = 1u << 9, DF_F2 = 1u << 10;  // bits 11-13: their accumulate flags
+constexpr uint32_t DF_NR2 = 1u << 4, DF_LAST = 1u << 7;
 
 struct StUnit {
   int x0, y0, rows_out;
@@ -918,16 +936,14 @@ struct Run {
 // The MMAs of one input row (all horizontal taps, NK K steps, NR runs of TMEM blocks) as straight
 // line code.  Every instruction gets descriptor registers of its own, so the issuing thread keeps
 // several MMAs in flight; a loop that reuses the registers issues three times slower (measured).
-// `skip00`: the row's first MMA position (tap 0, K step 0) was issued by the caller.
 template <int NK, int NR>
 __device__ __forceinline__ void st_issue_row(uint32_t hi, uint32_t row_lo, uint32_t b_lo, uint32_t wdx16, uint32_t kstep_b,
-                                             const Run &r0, const Run &r1, bool skip00) {
+                                             const Run &r0, const Run &r1) {
   constexpr uint32_t kstep_a = (2u * CHUNK_PITCH) >> 4;
 #pragma unroll
   for (int dx = 0; dx < 3; ++dx) {
 #pragma unroll
     for (int kc = 0; kc < NK; ++kc) {
-      if (dx == 0 && kc == 0 && skip00) continue;
       const uint32_t a = row_lo + (uint32_t)dx + (uint32_t)kc * kstep_a;
       const uint32_t b = b_lo + (uint32_t)dx * wdx16 + (uint32_t)kc * kstep_b;
       tc_mma(r0.col, ((uint64_t)hi << 32) | a, ((uint64_t)hi << 32) | (b + r0.boff), r0.idesc, 1u);
@@ -937,16 +953,16 @@ __device__ __forceinline__ void st_issue_row(uint32_t hi, uint32_t row_lo, uint3
 }
 template <int NR>
 __device__ __forceinline__ bool st_issue_nk(int nk, uint32_t hi, uint32_t row_lo, uint32_t b_lo, uint32_t wdx16,
-                                            uint32_t kstep_b, const Run &r0, const Run &r1, bool skip00) {
+                                            uint32_t kstep_b, const Run &r0, const Run &r1) {
   switch (nk) {
-    case 1: st_issue_row<1, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
-    case 2: st_issue_row<2, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
-    case 3: st_issue_row<3, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
-    case 4: st_issue_row<4, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
-    case 5: st_issue_row<5, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
-    case 6: st_issue_row<6, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
-    case 7: st_issue_row<7, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
-    case 8: st_issue_row<8, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, skip00); return true;
+    case 1: st_issue_row<1, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
+    case 2: st_issue_row<2, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
+    case 3: st_issue_row<3, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
+    case 4: st_issue_row<4, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
+    case 5: st_issue_row<5, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
+    case 6: st_issue_row<6, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
+    case 7: st_issue_row<7, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
+    case 8: st_issue_row<8, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
     default: return false;
   }
 }
@@ -1175,33 +1191,21 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         if (!mbar_wait(bar(ST_BAR_FULL + bofs + slot), fphase, abort_flag, g.status, 2)) break;
         if (tr) trace(g, 0, pos, 1);
         const uint32_t da = sbase + ST_OFF_DESC + (uint32_t)(bofs + slot) * ST_DESC_BYTES;
-        const uint4 q0 = lds16(da), q1 = lds16(da + 16), q2 = lds16(da + 32), q3 = lds16(da + 48), q4 = lds16(da + 64),
-                    q5 = lds16(da + 80);
+        const uint4 q0 = lds16(da), q1 = lds16(da + 16), q2 = lds16(da + 32);
         const uint32_t flags = q0.z;
         tc_fence_after();
         if (!(g.skip & 2)) {
           const uint32_t row_lo = q0.x, b_lo = q0.y;
           const int nk16 = (int)(flags & 15u);
-          const bool first = (flags & DF_FIRST) != 0;
-          const Run R0 = {q2.x, q2.y, q2.z, 1u}, R1 = {q2.w, q3.x, q3.y, 1u};
-          if (first) {
-            // F0 always exists; a guarded MMA costs its issue time even when it is predicated off, so the
-            // rare third one gets a branch of its own
-            mma1(q3.z, row_lo, b_lo + q3.w, q4.x, (flags >> 11) & 1u);
-            if (flags & DF_F1) mma1(q4.y, row_lo, b_lo + q4.z, q4.w, (flags >> 12) & 1u);
-            if (__builtin_expect((flags & DF_F2) != 0, 0)) {
-              mma1(q5.x, row_lo, b_lo + q5.y, q5.z, (flags >> 13) & 1u);
-              asm volatile("" ::: "memory");
-            }
-          }
+          const Run R0 = {q1.x, q1.y, q1.z, 1u}, R1 = {q1.w, q2.x, q2.y, 1u};
           bool done = false;
           if (!g.loop_issue)
-            done = (flags & DF_NR2) ? st_issue_nk<2>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1, first)
-                                    : st_issue_nk<1>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0, first);
+            done = (flags & DF_NR2) ? st_issue_nk<2>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1)
+                                    : st_issue_nk<1>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0);
           if (!done) {
             // more K steps than the straight line forms cover
             for (int dx = 0; dx < 3; ++dx)
-              for (int kc = (first && dx == 0) ? 1 : 0; kc < nk16; ++kc) {
+              for (int kc = 0; kc < nk16; ++kc) {
                 const uint32_t a = row_lo + (uint32_t)dx + (uint32_t)kc * kstep_a;
                 const uint32_t b = b_lo + (uint32_t)dx * (wdx_bytes >> 4) + (uint32_t)kc * kstep_b;
                 mma1(R0.col, a, b + R0.boff, R0.idesc, 1u);
@@ -1211,7 +1215,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         }
         if (tr) trace(g, 0, pos, 2);
         tc_commit(bar(ST_BAR_EMPTY + bofs + slot));
-        if (q1.y) tc_commit(q1.y);
+        if (q0.w) tc_commit(q0.w);
         if (tr) trace(g, 0, pos, 3);
         if (flags & DF_LAST) break;
         ++pos;
@@ -1241,6 +1245,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     int item = 0;
     int blk = 0;
     uint32_t tphase = 0;  // parity of tfull[blk] for the current round of the ring
+    // Every MMA accumulates, so a block is zero when the MMA thread gets it: all of them once here (this
+    // completes the first phase of the block barriers), and each one again when it has been read out.
+    for (int b = 0; b < NB; ++b) tc_zero_cols(lane_addr + (uint32_t)(b * N), N);
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0)
+      for (int b = 0; b < NB; ++b) mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b));
     for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
       const StUnit t = st_unit_of(g, u);
       const int x = t.x0 + m;
@@ -1280,7 +1291,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
               for (; c0 + 32 <= N; c0 += 32) stage_cols<32, EPI>(g, tr_addr, c0, tile + mine);
               if (c0 < N) stage_cols<16, EPI>(g, tr_addr, c0, tile + mine);
               if (r == nrows - 1) {
-                // last TMEM read of the item done: give the blocks back
+                // last TMEM read of the item done: give the blocks back, zeroed (every MMA accumulates)
+                tc_zero_cols(t0, N);
+                if (nrows == 2) tc_zero_cols(t1, N);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
@@ -1308,6 +1321,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
               __syncwarp();
             }
           } else {
+            tc_zero_cols(t0, N);
+            if (nrows == 2) tc_zero_cols(t1, N);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -1329,6 +1344,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           if (c0 < N) epi_fast<16, 1, EPI>(g, t0, t1, c0, x, y, xin, lane);
         }
         if (tr) trace(g, 1, item >> 1, 2);
+        tc_zero_cols(t0, N);
+        if (nrows == 2) tc_zero_cols(t1, N);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
@@ -1527,7 +1544,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     int slot = 0;
     uint32_t ephase = 1;  // parity to wait for on the empty barrier: first round passes
     int blkC = 0;
-    uint32_t cphase = 1;  // parity to wait for on tempty[blkC]: the first round passes
+    uint32_t cphase = 0;  // parity to wait for on tempty[blkC]: the epilogue's first zeroing completes phase 0
     bool ok = true;
     for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
       const StUnit t = st_unit_of(g, u);
@@ -1545,14 +1562,10 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           r.acc = acc;
           return r;
         };
-        // runs of neighbouring blocks one MMA can cover: R* for every MMA of the row but the
-        // first, F* for the first one (the fresh block C on its own, overwriting); acc == 2: unused
-        Run R0 = {0, 0, 0, 2}, R1 = R0, R2 = R0, F0 = R0, F1 = R0, F2 = R0;
-        if (vA && vB && vC && blkB != 0 && blkC != 0 && three) {  // the common case
-          R0 = mk(0, 3, 1);
-          F0 = mk(0, 2, 1);
-          F1 = mk(2, 1, 0);
-        } else {
+        // runs of neighbouring blocks one MMA can cover (every block starts zeroed, so all MMAs accumulate);
+        // acc == 2: unused
+        Run R0 = {0, 0, 0, 2}, R1 = R0, R2 = R0;
+        {
           const bool mAB = vA && vB && blkB != 0 && two;
           const bool mBC = vB && vC && blkC != 0 && two && (!mAB || three);
           if (mAB && mBC) {
@@ -1567,14 +1580,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
             if (vB) { if (vA) R1 = mk(1, 1, 1); else R0 = mk(1, 1, 1); }
             if (vC) { if (vA && vB) R2 = mk(2, 1, 1); else if (vA || vB) R1 = mk(2, 1, 1); else R0 = mk(2, 1, 1); }
           }
-          if (mAB) {
-            F0 = mk(0, 2, 1);
-            if (vC) F1 = mk(2, 1, 0);
-          } else {
-            if (vA) F0 = mk(0, 1, 1);
-            if (vB) { if (vA) F1 = mk(1, 1, 1); else F0 = mk(1, 1, 1); }
-            if (vC) { if (vA && vB) F2 = mk(2, 1, 0); else if (vA || vB) F1 = mk(2, 1, 0); else F0 = mk(2, 1, 0); }
-          }
         }
         if (R2.acc != 2) {
           // three separate runs need a block ring shorter than the plan ever makes: refuse instead of computing wrong
@@ -1583,29 +1588,21 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           ok = false;
           break;
         }
-        uint32_t rowflags = 0;
-        if (R1.acc != 2) rowflags |= DF_NR2;
-        if (F0.acc != 2) rowflags |= DF_F0 | (F0.acc << 11);
-        if (F1.acc != 2) rowflags |= DF_F1 | (F1.acc << 12);
-        if (F2.acc != 2) rowflags |= DF_F2 | (F2.acc << 13);
+        const uint32_t rowflags = R1.acc != 2 ? DF_NR2 : 0u;
         for (int gi = 0; ok && gi < g.G; ++gi) {
           ok = mbar_wait<32>(bar(ST_BAR_EMPTY + bofs + slot), ephase, abort_flag, g.status, 7);
           if (!ok) break;
           uint32_t flags = rowflags | (uint32_t)(g.gch[gi] >> 1);
-          if (gi == 0) flags |= DF_FIRST;
           if (last_unit && jj == rows_in - 1 && gi == g.G - 1) flags |= DF_LAST;
           const uint32_t row_lo = (((slots_addr + (uint32_t)slot * slot_bytes) & 0x3FFFFu) >> 4) | a_lo0;
           const uint32_t wgrp = (uint32_t)g.gc0[gi] * 3u * N16;  // group's first chunk, in 16 byte units
           const uint32_t b_lo = (((w_addr & 0x3FFFFu) >> 4) + wgrp) | b_lo0;
           const uint32_t tfbar = (gi == g.G - 1 && vA) ? bar(ST_BAR_TFULL + bofs + blkA) : 0u;
           const uint32_t da = sbase + ST_OFF_DESC + (uint32_t)(bofs + slot) * ST_DESC_BYTES;
-          sts16(da, make_uint4(row_lo, b_lo, flags, bar(ST_BAR_TEMPTY + bofs + blkC)));
-          sts16(da + 16, make_uint4(cphase, tfbar, 0u, 0u));
-          sts16(da + 32, make_uint4(R0.col, R0.boff, R0.idesc, R1.col));
-          sts16(da + 48, make_uint4(R1.boff, R1.idesc, F0.col, F0.boff));
-          sts16(da + 64, make_uint4(F0.idesc, F1.col, F1.boff, F1.idesc));
-          sts16(da + 80, make_uint4(F2.col, F2.boff, F2.idesc, 0u));
-          // the row's fresh TMEM block must have been drained before the MMA thread may start the row
+          sts16(da, make_uint4(row_lo, b_lo, flags, tfbar));
+          sts16(da + 16, make_uint4(R0.col, R0.boff, R0.idesc, R1.col));
+          sts16(da + 32, make_uint4(R1.boff, R1.idesc, 0u, 0u));
+          // the row's fresh TMEM block must have been read out and zeroed before the MMA thread may start the row
           if (gi == 0 && vC) {
             ok = mbar_wait<32>(bar(ST_BAR_TEMPTY + bofs + blkC), cphase, abort_flag, g.status, 3);
             if (!ok) break;
