@@ -61,7 +61,7 @@ def time_dispatch(d, iters, warmup=3):
     return float(np.median([e[i].elapsed_time(e[i + 1]) for i in range(iters)]))
 
 
-def run(variants="best", iters=20, h=H, w=W, only=None):
+def run(variants="best", iters=20, h=H, w=W, only=None, config=None):
     hbm, tc, src = peaks()
     rows = []
     conv_variants = [v for v in lib.variants() if v["op"] == lib.OP_CONV3X3 and v["needs_tcgen05"]]
@@ -78,6 +78,8 @@ def run(variants="best", iters=20, h=H, w=W, only=None):
         outp = torch.empty((h // 2, w // 2, k), dtype=torch.float16, device="cuda")
         best = None
         for v in conv_variants:
+            if config and v["config"] != config:
+                continue
             d = lib.Dispatch()
             d.variant, d.flags, d.c_a, d.c_b, d.c_out = v["id"], flags, ca, cb, k
             d.pc[0], d.pc[1] = w, h
@@ -115,9 +117,10 @@ def main():
     ap.add_argument("--variants", default="best", choices=["best", "all"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", default=None)
-    ap.add_argument("--only", default=None)
+    ap.add_argument("--only", default=None, help="run only the cases whose name contains this text")
+    ap.add_argument("--config", default=None, help="run only the variant with exactly this config string")
     args = ap.parse_args()
-    res = run(args.variants, args.iters, only=args.only)
+    res = run(args.variants, args.iters, only=args.only, config=args.config)
     for r in res["rows"]:
         print(f"{r['case']:40s} {r['variant']:22s} {r['ms']:8.4f} ms  {r['tflops']:7.1f} TF/s  {r['gbs']:7.1f} GB/s  "
               f"{r['bound']:6s} roof {r['roof_ms']:.4f} ms  frac {r['frac']:.3f}")
