@@ -156,7 +156,13 @@ typedef struct dnxcu_dispatch {
    * border (zeros).  Order: a_top, a_bottom, b_top, b_bottom. */
   const void *halo[4];
   int32_t *device_status; /* optional device int: a kernel stores a non-zero code
-                             here when one of its bounded waits ran out */
+                             here when one of its bounded waits ran out
+                             (1 weights, 2 input row, 3 accumulator block free,
+                             4/5 streamed weights, 6 accumulators complete,
+                             7 input slot free, 8 raw row of the upsampled
+                             operand) or when it met a state it refuses to
+                             compute in (9); the launch returns normally and
+                             the output is then undefined */
 } dnxcu_dispatch;
 
 /* Checks the dispatch against the variant's rules without launching. */
