@@ -95,6 +95,10 @@ static const Variant kVariants[] = {
     {{18, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=2#W=resident#NSPLIT=2", CONV_ALL, 1, 1, 16, 256, 0}, VK_CONV_TC, 0, 2, 0, 2},
     {{19, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=4#W=resident#NSPLIT=2", CONV_ALL, 1, 1, 16, 256, 0}, VK_CONV_TC, 0, 4, 0, 2},
     {{20, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=4#W=resident#NSPLIT=3", CONV_ALL, 1, 1, 16, 256, 0}, VK_CONV_TC, 0, 4, 0, 3},
+    {{21, DNXCU_OP_PAD_EDGE, "memory-pad", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_PAD_EDGE, 8, 0, 0, 0},
+    {{22, DNXCU_OP_PAD_EDGE, "memory-pad", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_PAD_EDGE, 1, 0, 0, 0},
+    {{23, DNXCU_OP_SLICE, "memory-slice", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_SLICE, 8, 0, 0, 0},
+    {{24, DNXCU_OP_SLICE, "memory-slice", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_SLICE, 1, 0, 0, 0},
 };
 static const int kVariantCount = (int)(sizeof(kVariants) / sizeof(kVariants[0]));
 
@@ -175,6 +179,14 @@ int dnxcu_validate(const dnxcu_dispatch *d) {
     default:
       if (!d->in_a || !d->out || d->c_a <= 0 || !d->pc[0] || !d->pc[1]) return DNXCU_E_BAD_ARG;
       if (v->kind == VK_CONCAT && (!d->in_b || d->c_b <= 0)) return DNXCU_E_BAD_ARG;
+      if (v->kind == VK_PAD_EDGE || v->kind == VK_SLICE) {
+        const bool pad = v->kind == VK_PAD_EDGE;
+        const long long iw = pad ? (long long)d->pc[0] - d->pc_ext[0] - d->pc_ext[1] : d->pc_ext[2];
+        const long long ih = pad ? (long long)d->pc[1] - d->pc_ext[2] - d->pc_ext[3] : d->pc_ext[3];
+        if (iw <= 0 || ih <= 0) return DNXCU_E_BAD_ARG;
+        if (!pad && ((long long)d->pc_ext[0] + d->pc[0] > iw || (long long)d->pc_ext[1] + d->pc[1] > ih))
+          return DNXCU_E_BAD_ARG;
+      }
       if (v->kind == VK_PADC) {
         if (d->c_out < d->c_a || d->c_out % 8) return DNXCU_E_BAD_ARG;
         if (((uintptr_t)d->out & 15) || ((uintptr_t)d->in_a & 1)) return DNXCU_E_MISALIGNED;
@@ -242,6 +254,11 @@ int dnxcu_cost(const dnxcu_dispatch *d, uint64_t *rd, uint64_t *wr, uint64_t *fl
     case DNXCU_OP_CONCAT: r = 2 * P * ((uint64_t)d->c_a + d->c_b); w = r; break;
     case DNXCU_OP_RELU: r = 2 * P * d->c_a; w = r; break;
     case DNXCU_OP_PAD_CHANNELS: r = 2 * P * d->c_a; w = 2 * P * d->c_out; break;
+    case DNXCU_OP_PAD_EDGE:
+      r = 2 * (uint64_t)(W - d->pc_ext[0] - d->pc_ext[1]) * (H - d->pc_ext[2] - d->pc_ext[3]) * d->c_a;
+      w = 2 * P * d->c_a;
+      break;
+    case DNXCU_OP_SLICE: r = 2 * P * d->c_a; w = r; break;
     default: return DNXCU_E_BAD_ARG;
   }
   if (rd) *rd = r;

@@ -26,6 +26,8 @@ enum VariantKind {
   VK_CONCAT,
   VK_RELU,
   VK_PADC,
+  VK_PAD_EDGE,
+  VK_SLICE,
 };
 
 struct Variant {

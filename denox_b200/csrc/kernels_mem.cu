@@ -127,6 +127,31 @@ __global__ void pad_channels(const unsigned short *__restrict__ in, uint4 *__res
   }
 }
 
+// Spatial pad by edge replication and spatial slice: one thread per output pixel and piece (16 bytes
+// or one channel) of it.  T = uint4 (C % 8 == 0) or unsigned short.
+//   pad:   out[ho][wo] = in[clamp(ho - top, 0, IH - 1)][clamp(wo - left, 0, IW - 1)]   (memory_pad.comp:71-72)
+//   slice: out[h][w]   = in[h + top][w + left]                                         (memory_slice.comp:59-66)
+template <class T, bool PAD>
+__global__ void pad_or_slice(const T *__restrict__ in, T *__restrict__ out, int OH, int OW, int IH, int IW, int CT,
+                             int left, int top) {
+  const long long n = (long long)OH * OW * CT;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % CT);
+    const long long p = i / CT;
+    const int wo = (int)(p % OW), ho = (int)(p / OW);
+    int hi, wi;
+    if (PAD) {
+      hi = min(max(ho - top, 0), IH - 1);
+      wi = min(max(wo - left, 0), IW - 1);
+    } else {
+      hi = ho + top;
+      wi = wo + left;
+    }
+    out[i] = in[((long long)hi * IW + wi) * CT + c];
+  }
+}
+
 constexpr int kThreads = 256;
 
 // Number of 16-byte (or 2-byte) items the dispatch writes.
@@ -139,6 +164,8 @@ long long item_count(const Variant &v, const dnxcu_dispatch &d) {
     case VK_CONCAT: return H * W * ((d.c_a + d.c_b) / vec);
     case VK_RELU: return H * W * d.c_a / vec;
     case VK_PADC: return H * W * (d.c_out / 8);
+    case VK_PAD_EDGE:
+    case VK_SLICE: return H * W * (d.c_a / vec);
     default: return 0;
   }
 }
@@ -181,6 +208,26 @@ int mem_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
     if (((uintptr_t)d.in_a | (uintptr_t)d.out | (uintptr_t)d.in_b) & 1) return DNXCU_E_MISALIGNED;
   }
   if (v.kind == VK_POOL && (H < 2 || W < 2)) return DNXCU_E_BAD_ARG;
+  if (v.kind == VK_PAD_EDGE || v.kind == VK_SLICE) {
+    // W, H are the output extent here
+    const bool pad = v.kind == VK_PAD_EDGE;
+    const long long IW = pad ? (long long)W - d.pc_ext[0] - d.pc_ext[1] : d.pc_ext[2];
+    const long long IH = pad ? (long long)H - d.pc_ext[2] - d.pc_ext[3] : d.pc_ext[3];
+    if (IW <= 0 || IH <= 0) return DNXCU_E_BAD_ARG;
+    if (!pad && ((long long)d.pc_ext[0] + W > IW || (long long)d.pc_ext[1] + H > IH)) return DNXCU_E_BAD_ARG;
+    const int left = (int)d.pc_ext[0], top = pad ? (int)d.pc_ext[2] : (int)d.pc_ext[1];
+    uint32_t gp[3];
+    mem_grid(v, d, gp);
+    if (vec == 8) {
+      if (pad) pad_or_slice<uint4, true><<<gp[0], kThreads, 0, s>>>((const uint4 *)d.in_a, (uint4 *)d.out, H, W, (int)IH, (int)IW, d.c_a / 8, left, top);
+      else pad_or_slice<uint4, false><<<gp[0], kThreads, 0, s>>>((const uint4 *)d.in_a, (uint4 *)d.out, H, W, (int)IH, (int)IW, d.c_a / 8, left, top);
+    } else {
+      if (pad) pad_or_slice<unsigned short, true><<<gp[0], kThreads, 0, s>>>((const unsigned short *)d.in_a, (unsigned short *)d.out, H, W, (int)IH, (int)IW, d.c_a, left, top);
+      else pad_or_slice<unsigned short, false><<<gp[0], kThreads, 0, s>>>((const unsigned short *)d.in_a, (unsigned short *)d.out, H, W, (int)IH, (int)IW, d.c_a, left, top);
+    }
+    DNXCU_CUDA(cudaGetLastError());
+    return DNXCU_OK;
+  }
   if (v.kind == VK_PADC) {
     if (d.c_out < d.c_a || d.c_out % 8) return DNXCU_E_BAD_ARG;
     if (((uintptr_t)d.out & 15) || ((uintptr_t)d.in_a & 1)) return DNXCU_E_MISALIGNED;

@@ -244,7 +244,13 @@ void candidate_variants(const FusedOp &op, bool allow_tc, std::vector<int> &out)
 
 struct dnxcu_instance {
   const dnxcu_model *model = nullptr;
-  int H = 0, W = 0;  // band extent at level 0
+  int H = 0, W = 0;  // band extent at level 0 (what the schedule runs at)
+  // Frames whose extent is not a multiple of the network's alignment: the caller's extent, the two
+  // extra dispatches (edge pad in front, slice behind) and the caller-extent device buffers.
+  int user_H = 0, user_W = 0;
+  bool padded = false;
+  dnxcu_dispatch pre = {}, post = {};
+  void *user_in = nullptr, *user_out = nullptr;
   dnxcu_band band = {0, 0, 0};
   bool banded = false;
   std::vector<void *> tensor_ptr;    // per tensor device pointer (nullptr if not materialized)
@@ -330,6 +336,16 @@ int dnxcu_instance_create(const dnxcu_model *m, int height, int width, const dnx
   std::unique_ptr<dnxcu_instance> inst(new (std::nothrow) dnxcu_instance());
   if (!inst) return DNXCU_E_NO_MEMORY;
   inst->model = m;
+  inst->user_W = width;
+  inst->user_H = height;
+  if (!band && ((height % align) || (width % align))) {
+    // the reference's exported models wrap the net in pad (replicate, right and bottom) -> net -> slice
+    // (oidn_model.py:334-347); here the instance does it
+    if (m->tensors[m->output_tensor].level != 0) return DNXCU_E_UNSUPPORTED;
+    inst->padded = true;
+    height = (height + align - 1) / align * align;
+    width = (width + align - 1) / align * align;
+  }
   inst->W = width;
   inst->H = height;
   inst->band = {height, 0, height};
@@ -462,6 +478,32 @@ int dnxcu_instance_create(const dnxcu_model *m, int height, int width, const dnx
     }
     inst->disp[i] = d;
   }
+  if (inst->padded) {
+    const TensorInfo &ti = m->tensors[m->input_tensor], &to = m->tensors[m->output_tensor];
+    st = dev_alloc(*inst, (size_t)inst->user_H * inst->user_W * ti.channels * 2, &inst->user_in);
+    if (st) return st;
+    st = dev_alloc(*inst, (size_t)inst->user_H * inst->user_W * to.channels * 2, &inst->user_out);
+    if (st) return st;
+    dnxcu_dispatch &p = inst->pre, &q = inst->post;
+    p.variant = dnxcu_find_variant("memory-pad", ti.channels % 8 ? "VEC=1" : "VEC=8");
+    p.pc[0] = (uint32_t)inst->W;
+    p.pc[1] = (uint32_t)inst->H;
+    p.c_a = ti.channels;
+    p.pc_ext[1] = (uint32_t)(inst->W - inst->user_W);
+    p.pc_ext[3] = (uint32_t)(inst->H - inst->user_H);
+    p.in_a = inst->user_in;
+    p.out = inst->tensor_ptr[m->input_tensor];
+    q.variant = dnxcu_find_variant("memory-slice", to.channels % 8 ? "VEC=1" : "VEC=8");
+    q.pc[0] = (uint32_t)inst->user_W;
+    q.pc[1] = (uint32_t)inst->user_H;
+    q.c_a = to.channels;
+    q.pc_ext[2] = (uint32_t)inst->W;
+    q.pc_ext[3] = (uint32_t)inst->H;
+    q.in_a = inst->tensor_ptr[m->output_tensor];
+    q.out = inst->user_out;
+    if (p.variant < 0 || q.variant < 0 || !p.out || !q.in_a) return DNXCU_E_STATE;
+    if ((st = dnxcu_validate(&p)) || (st = dnxcu_validate(&q))) return st;
+  }
   inst->events.resize(inst->disp.size() + 1);
   for (cudaEvent_t &e : inst->events) DNXCU_CUDA(cudaEventCreate(&e));
   *out = inst.release();
@@ -493,16 +535,32 @@ int dnxcu_instance_enqueue(dnxcu_instance *inst, const void *dev_in, void *dev_o
       cudaGraphExecDestroy(inst->graph);
       inst->graph = nullptr;
     }
+    // caller-extent frames: pad into the model's own input tensor first, slice out of its own output tensor last
+    auto whole = [&]() -> int {
+      int st = DNXCU_OK;
+      if (inst->padded) {
+        dnxcu_dispatch p = inst->pre;
+        p.in_a = dev_in;
+        st = dnxcu_launch(&p, inst->stream);
+      }
+      for (size_t i = 0; i < inst->disp.size() && !st; ++i)
+        st = launch_one(*inst, (int)i, inst->padded ? nullptr : dev_in, inst->padded ? nullptr : dev_out, inst->stream);
+      if (inst->padded && !st) {
+        dnxcu_dispatch q = inst->post;
+        q.out = dev_out;
+        st = dnxcu_launch(&q, inst->stream);
+      }
+      return st;
+    };
     // a first plain pass makes every kernel's one-time function attribute set-up happen outside the capture
-    for (size_t i = 0; i < inst->disp.size(); ++i) {
-      int st = launch_one(*inst, (int)i, dev_in, dev_out, inst->stream);
+    {
+      int st = whole();
       if (st) return st;
     }
     DNXCU_CUDA(cudaStreamSynchronize(inst->stream));
     cudaGraph_t gr = nullptr;
     DNXCU_CUDA(cudaStreamBeginCapture(inst->stream, cudaStreamCaptureModeThreadLocal));
-    int st = DNXCU_OK;
-    for (size_t i = 0; i < inst->disp.size() && !st; ++i) st = launch_one(*inst, (int)i, dev_in, dev_out, inst->stream);
+    int st = whole();
     cudaError_t e = cudaStreamEndCapture(inst->stream, &gr);
     if (st) {
       if (gr) cudaGraphDestroy(gr);
@@ -526,11 +584,13 @@ int dnxcu_instance_infer_async(dnxcu_instance *inst, const void *host_in, void *
   if (!inst || !host_in || !host_out) return DNXCU_E_BAD_ARG;
   const dnxcu_model *m = inst->model;
   DNXCU_CUDA(cudaSetDevice(m->device));
-  void *din = inst->tensor_ptr[m->input_tensor], *dout = inst->tensor_ptr[m->output_tensor];
+  void *din = inst->padded ? inst->user_in : inst->tensor_ptr[m->input_tensor];
+  void *dout = inst->padded ? inst->user_out : inst->tensor_ptr[m->output_tensor];
   if (!din || !dout) return DNXCU_E_STATE;
   const TensorInfo &ti = m->tensors[m->input_tensor], &to = m->tensors[m->output_tensor];
-  const size_t in_bytes = (size_t)inst->H * inst->W * ti.channels * 2;
-  const size_t out_bytes = (size_t)(inst->H >> to.level) * (inst->W >> to.level) * to.channels * 2;
+  const int fh = inst->padded ? inst->user_H : inst->H, fw = inst->padded ? inst->user_W : inst->W;
+  const size_t in_bytes = (size_t)fh * fw * ti.channels * 2;
+  const size_t out_bytes = (size_t)(fh >> to.level) * (fw >> to.level) * to.channels * 2;
   DNXCU_CUDA(cudaMemcpyAsync(din, host_in, in_bytes, cudaMemcpyHostToDevice, inst->stream));
   int st = dnxcu_instance_enqueue(inst, din, dout, inst->stream);
   if (st) return st;
@@ -551,11 +611,13 @@ int dnxcu_instance_infer(dnxcu_instance *inst, const void *host_in, void *host_o
   if (!inst || !host_in || !host_out) return DNXCU_E_BAD_ARG;
   const dnxcu_model *m = inst->model;
   DNXCU_CUDA(cudaSetDevice(m->device));
-  void *din = inst->tensor_ptr[m->input_tensor], *dout = inst->tensor_ptr[m->output_tensor];
+  void *din = inst->padded ? inst->user_in : inst->tensor_ptr[m->input_tensor];
+  void *dout = inst->padded ? inst->user_out : inst->tensor_ptr[m->output_tensor];
   if (!din || !dout) return DNXCU_E_STATE;
   const TensorInfo &ti = m->tensors[m->input_tensor], &to = m->tensors[m->output_tensor];
-  const size_t in_bytes = (size_t)inst->H * inst->W * ti.channels * 2;
-  const size_t out_bytes = (size_t)(inst->H >> to.level) * (inst->W >> to.level) * to.channels * 2;
+  const int fh = inst->padded ? inst->user_H : inst->H, fw = inst->padded ? inst->user_W : inst->W;
+  const size_t in_bytes = (size_t)fh * fw * ti.channels * 2;
+  const size_t out_bytes = (size_t)(fh >> to.level) * (fw >> to.level) * to.channels * 2;
   DNXCU_CUDA(cudaMemcpyAsync(din, host_in, in_bytes, cudaMemcpyHostToDevice, inst->stream));
   int st = dnxcu_instance_enqueue(inst, din, dout, inst->stream);
   if (st) return st;
@@ -578,8 +640,17 @@ int dnxcu_instance_tensor(const dnxcu_instance *inst, int t, void **ptr, int *h,
 
 int dnxcu_instance_io(const dnxcu_instance *inst, void **dev_in, void **dev_out) {
   if (!inst) return DNXCU_E_BAD_ARG;
-  if (dev_in) *dev_in = inst->tensor_ptr[inst->model->input_tensor];
-  if (dev_out) *dev_out = inst->tensor_ptr[inst->model->output_tensor];
+  if (dev_in) *dev_in = inst->padded ? inst->user_in : inst->tensor_ptr[inst->model->input_tensor];
+  if (dev_out) *dev_out = inst->padded ? inst->user_out : inst->tensor_ptr[inst->model->output_tensor];
+  return DNXCU_OK;
+}
+
+int dnxcu_instance_extent(const dnxcu_instance *inst, int *h, int *w, int *h_run, int *w_run) {
+  if (!inst) return DNXCU_E_BAD_ARG;
+  if (h) *h = inst->padded ? inst->user_H : inst->H;
+  if (w) *w = inst->padded ? inst->user_W : inst->W;
+  if (h_run) *h_run = inst->H;
+  if (w_run) *w_run = inst->W;
   return DNXCU_OK;
 }
 

@@ -23,7 +23,7 @@ L = C.CDLL(LIB_PATH)
 OK = 0
 E_BAD_ARG, E_UNSUPPORTED, E_MISALIGNED, E_CUDA, E_DEVICE, E_NO_MEMORY, E_STATE, E_IO, E_LIMIT = range(-1, -10, -1)
 
-OP_CONV3X3, OP_MAXPOOL2X2, OP_UPSAMPLE2X, OP_CONCAT, OP_RELU, OP_PAD_CHANNELS = 1, 2, 3, 4, 5, 6
+OP_CONV3X3, OP_MAXPOOL2X2, OP_UPSAMPLE2X, OP_CONCAT, OP_RELU, OP_PAD_CHANNELS, OP_PAD_EDGE, OP_SLICE = 1, 2, 3, 4, 5, 6, 7, 8
 F_RELU, F_BIAS, F_UP2X_A, F_POOL_OUT, F_NO_FULL_OUT = 0x01, 0x02, 0x04, 0x08, 0x10
 OPT_NO_FUSE_ACTIVATION, OPT_NO_FUSE_POOL, OPT_NO_FUSE_UPSAMPLE, OPT_NO_FUSE_CONCAT, OPT_NO_TCGEN05 = 1, 2, 4, 8, 16
 OPT_NO_PAD_INPUT = 32
@@ -61,7 +61,8 @@ class Dispatch(C.Structure):
     _fields_ = [("variant", C.c_int32), ("flags", C.c_uint32), ("pc", C.c_uint32 * 2), ("c_a", C.c_int32),
                 ("c_b", C.c_int32), ("c_out", C.c_int32), ("reserved", C.c_int32), ("in_a", C.c_void_p),
                 ("in_b", C.c_void_p), ("out", C.c_void_p), ("out_pool", C.c_void_p), ("weights", C.c_void_p),
-                ("bias", C.c_void_p), ("halo", C.c_void_p * 4), ("device_status", C.c_void_p)]
+                ("bias", C.c_void_p), ("halo", C.c_void_p * 4), ("device_status", C.c_void_p),
+                ("pc_ext", C.c_uint32 * 4)]
 
 
 class NodeC(C.Structure):
@@ -130,6 +131,8 @@ SIGNATURES = {
     "dnxcu_instance_halo": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(HaloPoint)]),
     "dnxcu_instance_enqueue_range": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "dnxcu_instance_io": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
+    "dnxcu_instance_extent": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                        C.POINTER(C.c_int)]),
     "dnxcu_db_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "dnxcu_db_close": (None, [C.c_void_p]),
     "dnxcu_db_size": (C.c_int, [C.c_void_p]),
@@ -277,6 +280,9 @@ class Instance:
         x = np.ascontiguousarray(x, dtype=np.float16)
         assert x.shape == (self.rows, self.w, net.in_channels), x.shape
         _, h, w, c = self.tensor(net.output_tensor)
+        fh, fw, rh, rw = self.extent()
+        if (fh, fw) != (rh, rw):  # the instance pads the frame and slices the output back
+            h, w = fh, fw
         y = np.empty((h, w, c), dtype=np.float16)
         check(L.dnxcu_instance_infer(self._h, x.ctypes.data, y.ctypes.data), "dnxcu_instance_infer")
         return y
@@ -298,6 +304,12 @@ class Instance:
         a, b = C.c_void_p(), C.c_void_p()
         check(L.dnxcu_instance_io(self._h, C.byref(a), C.byref(b)))
         return a.value, b.value
+
+    def extent(self):
+        """(h, w) of the caller's frames and (h_run, w_run) the schedule runs at."""
+        v = [C.c_int() for _ in range(4)]
+        check(L.dnxcu_instance_extent(self._h, *[C.byref(x) for x in v]))
+        return tuple(x.value for x in v)
 
     def tensor(self, tid):
         p, h, w, c = C.c_void_p(), C.c_int(), C.c_int(), C.c_int()

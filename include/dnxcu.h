@@ -87,10 +87,15 @@ typedef enum dnxcu_op {
   DNXCU_OP_UPSAMPLE2X = 3, /* basic_upsample.comp  */
   DNXCU_OP_CONCAT = 4,     /* copy_transform.comp  */
   DNXCU_OP_RELU = 5,       /* basic_activation.comp */
-  DNXCU_OP_PAD_CHANNELS = 6 /* copy_transform.comp used as a layout change: HWC with C channels ->
-                               HWC with c_out >= C channels, the new ones zero (what the reference's
-                               HWC -> HWC8 / CHWC8 layout specialisation does,
-                               specialization/specialization.cpp:183-340) */
+  DNXCU_OP_PAD_CHANNELS = 6, /* copy_transform.comp used as a layout change: HWC with C channels ->
+                                HWC with c_out >= C channels, the new ones zero (what the reference's
+                                HWC -> HWC8 / CHWC8 layout specialisation does,
+                                specialization/specialization.cpp:183-340) */
+  DNXCU_OP_PAD_EDGE = 7,     /* memory_pad.comp: spatial pad, source coordinate clamped to the input
+                                (edge replication); pc = {OUT_W, OUT_H},
+                                pc_ext = {PAD_LEFT, PAD_RIGHT, PAD_TOP, PAD_BOTTOM} */
+  DNXCU_OP_SLICE = 8         /* memory_slice.comp: out[h][w] = in[h + IN_TOP][w + IN_LEFT];
+                                pc = {OUT_W, OUT_H}, pc_ext = {IN_LEFT, IN_TOP, IN_W, IN_H} */
 } dnxcu_op;
 
 /* dispatch flags (conv only unless noted) */
@@ -163,6 +168,7 @@ typedef struct dnxcu_dispatch {
                              operand) or when it met a state it refuses to
                              compute in (9); the launch returns normally and
                              the output is then undefined */
+  uint32_t pc_ext[4];     /* further push constants of pad / slice dispatches (see dnxcu_op) */
 } dnxcu_dispatch;
 
 /* Checks the dispatch against the variant's rules without launching. */
@@ -354,6 +360,13 @@ DNXCU_API int dnxcu_instance_halo(const dnxcu_instance *inst, int e, dnxcu_halo_
 DNXCU_API int dnxcu_instance_enqueue_range(dnxcu_instance *inst, int first, int last, void *stream);
 /* Copies the band's input into the instance's input tensor / the output out. */
 DNXCU_API int dnxcu_instance_io(const dnxcu_instance *inst, void **dev_in, void **dev_out);
+/* The extent the caller's frames have (h, w) and the extent the schedule runs at
+ * (h_run, w_run).  They differ when the instance was created with an extent that is not
+ * a multiple of the network's alignment: the instance then pads the frame by edge
+ * replication at the right and the bottom before the first dispatch and slices the
+ * output back after the last one, as the reference's exported models do
+ * (oidn_model.py:334-347: UNetAlignment; memory_pad.comp, memory_slice.comp). */
+DNXCU_API int dnxcu_instance_extent(const dnxcu_instance *inst, int *h, int *w, int *h_run, int *w_run);
 
 /* ------------------------------------------------------------------------
  * Benchmark database.

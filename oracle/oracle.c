@@ -233,6 +233,34 @@ ORC_API int orc_relu(const uint16_t *in, int64_t n, uint16_t *out) {
   return 0;
 }
 
+/* Spatial pad with edge replication (memory_pad.comp:71-72: the source coordinate is the
+ * output coordinate minus the pad, clamped to the input extent).  out is
+ * (H + top + bottom) x (W + left + right) x C. */
+ORC_API int orc_pad_edge(const uint16_t *in, int H, int W, int C, int left, int right, int top,
+                         int bottom, uint16_t *out) {
+  const int OH = H + top + bottom, OW = W + left + right;
+  if (H <= 0 || W <= 0 || left < 0 || right < 0 || top < 0 || bottom < 0) return -1;
+#pragma omp parallel for
+  for (int ho = 0; ho < OH; ++ho)
+    for (int wo = 0; wo < OW; ++wo) {
+      int hi = ho - top, wi = wo - left;
+      hi = hi < 0 ? 0 : (hi > H - 1 ? H - 1 : hi);
+      wi = wi < 0 ? 0 : (wi > W - 1 ? W - 1 : wi);
+      memcpy(out + ((int64_t)ho * OW + wo) * C, in + ((int64_t)hi * W + wi) * C, (size_t)C * 2);
+    }
+  return 0;
+}
+
+/* Spatial slice: out[h][w] = in[h + top][w + left] (memory_slice.comp:59-66). */
+ORC_API int orc_slice(const uint16_t *in, int H, int W, int C, int left, int top, int OH, int OW,
+                      uint16_t *out) {
+  if (left < 0 || top < 0 || left + OW > W || top + OH > H) return -1;
+#pragma omp parallel for
+  for (int h = 0; h < OH; ++h)
+    memcpy(out + (int64_t)h * OW * C, in + ((int64_t)(h + top) * W + left) * C, (size_t)OW * C * 2);
+  return 0;
+}
+
 ORC_API int orc_num_threads(void) {
   int n = 1;
 #pragma omp parallel

@@ -38,6 +38,10 @@ def lib():
         _lib.orc_upsample2x.argtypes = [vp, i, i, i, vp]
         _lib.orc_concat.argtypes = [vp, i, vp, i, i, i, vp]
         _lib.orc_relu.argtypes = [vp, C.c_int64, vp]
+        _lib.orc_pad_edge.restype = i
+        _lib.orc_pad_edge.argtypes = [vp, i, i, i, i, i, i, i, vp]
+        _lib.orc_slice.restype = i
+        _lib.orc_slice.argtypes = [vp, i, i, i, i, i, i, i, vp]
         _lib.orc_f32_to_f16_trunc.argtypes = [vp, vp, C.c_int64]
         _lib.orc_num_threads.restype = i
     return _lib
@@ -98,6 +102,33 @@ def relu(x):
     out = np.empty_like(x)
     lib().orc_relu(_p(x), x.size, _p(out))
     return out
+
+
+def pad_edge(x, left=0, right=0, top=0, bottom=0):
+    """Edge replicating spatial pad (memory_pad.comp)."""
+    x = _f16(x)
+    h, w, c = x.shape
+    out = np.empty((h + top + bottom, w + left + right, c), dtype=np.float16)
+    assert lib().orc_pad_edge(_p(x), h, w, c, left, right, top, bottom, _p(out)) == 0
+    return out
+
+
+def slice_hw(x, left, top, oh, ow):
+    """Spatial slice (memory_slice.comp)."""
+    x = _f16(x)
+    h, w, c = x.shape
+    out = np.empty((oh, ow, c), dtype=np.float16)
+    assert lib().orc_slice(_p(x), h, w, c, left, top, oh, ow, _p(out)) == 0
+    return out
+
+
+def run_network_aligned(net, x, alignment=16, mode=ACC_F32):
+    """The network behind the reference's alignment wrapper (oidn_model.py:334-347): pad right and bottom
+    to a multiple of `alignment` by edge replication, run, slice the output back.  Returns the output."""
+    h, w = x.shape[:2]
+    ph, pw = (-h) % alignment, (-w) % alignment
+    y = run_network(net, pad_edge(x, 0, pw, 0, ph), mode)[net.output_tensor]
+    return slice_hw(y, 0, 0, h, w)
 
 
 def f32_to_f16_trunc(x):

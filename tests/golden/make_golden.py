@@ -92,6 +92,28 @@ def conv_case_torch(case):
     return t_out(y)
 
 
+# (name, H, W, C, left, right, top, bottom): spatial pads (torch: F.pad(mode="replicate")) and the slices that undo them
+PAD_CASES = [
+    ("c3", 5, 7, 3, 0, 9, 0, 11),
+    ("c9", 13, 10, 9, 0, 6, 0, 3),
+    ("c8", 6, 20, 8, 2, 1, 3, 0),
+    ("c32", 17, 33, 32, 0, 15, 0, 15),
+]
+
+
+def pad_case_input(case):
+    name, h, w, c = case[:4]
+    return rng.to_f16(rng.uniform(8000 + sum(name.encode()), h * w * c, -4.0, 4.0)).reshape(h, w, c)
+
+
+def run_torch_aligned(net, x, alignment=16):
+    """The reference's alignment wrapper (oidn_model.py:334-347): replicate pad right / bottom, net, slice."""
+    h, w = x.shape[:2]
+    ph, pw = (-h) % alignment, (-w) % alignment
+    xp = t_out(F.pad(t_in(x), (0, pw, 0, ph), mode="replicate"))
+    return run_torch(net, xp)[net.output_tensor][:h, :w].copy()
+
+
 def main():
     torch.set_num_threads(4)
     out = {}
@@ -109,6 +131,10 @@ def main():
     for name in ("enc_conv1", "enc_conv4", "dec_conv4a", "dec_conv1a"):
         nd = next(n for n in oidn.nodes if n.name == name + ".relu")
         out[f"oidn_32x48/{name}"] = res[nd.out]
+    for case in PAD_CASES:
+        name, h, w, c, l, r, t, b = case
+        out["pad/" + name] = t_out(F.pad(t_in(pad_case_input(case)), (l, r, t, b), mode="replicate"))
+    out["oidn_40x52_aligned/out"] = run_torch_aligned(oidn, nets.oidn_input(1002, 40, 52))
     path = os.path.join(HERE, "golden.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes", len(out), "arrays")

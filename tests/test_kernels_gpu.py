@@ -140,3 +140,44 @@ def test_launch_rejects_bad_dispatches_without_touching_the_device():
 def test_device_caps():
     caps = lib.device_caps(0)
     assert caps.sm_count > 0 and caps.cc_major == 10 and caps.tcgen05 == 1 and caps.tmem_columns == 512
+
+
+@pytest.mark.parametrize("case", mg.PAD_CASES + [("c16_big", 270, 481, 16, 0, 15, 0, 2)], ids=lambda c: c[0])
+def test_pad_edge_and_slice_bit_exact(case):
+    """memory-pad / memory-slice against the oracle, both vector widths where the channel count allows."""
+    import ctypes as C
+    import torch
+    from gpu_util import Guarded, dev
+    name, h, w, c, l, r, t, b = case
+    x = mg.pad_case_input(case)
+    ref = oracle.pad_edge(x, l, r, t, b)
+    if "pad/" + name in GOLD.files:
+        assert (ref.view(np.uint16) == GOLD["pad/" + name].view(np.uint16)).all()
+    oh, ow = h + t + b, w + l + r
+    tx = dev(x)
+    for vec in (["VEC=8", "VEC=1"] if c % 8 == 0 else ["VEC=1"]):
+        d = lib.Dispatch()
+        d.variant = lib.L.dnxcu_find_variant(b"memory-pad", vec.encode())
+        d.pc[0], d.pc[1], d.c_a = ow, oh, c
+        d.pc_ext[0], d.pc_ext[1], d.pc_ext[2], d.pc_ext[3] = l, r, t, b
+        out = Guarded((oh, ow, c))
+        d.in_a, d.out = tx.data_ptr(), out.ptr()
+        lib.check(lib.L.dnxcu_launch(C.byref(d), None))
+        y = out.check()
+        assert (y.view(np.uint16) == ref.view(np.uint16)).all(), (name, vec, "pad")
+        q = lib.Dispatch()
+        q.variant = lib.L.dnxcu_find_variant(b"memory-slice", vec.encode())
+        q.pc[0], q.pc[1], q.c_a = w, h, c
+        q.pc_ext[0], q.pc_ext[1], q.pc_ext[2], q.pc_ext[3] = l, t, ow, oh
+        back = Guarded((h, w, c))
+        ty = dev(y)
+        q.in_a, q.out = ty.data_ptr(), back.ptr()
+        lib.check(lib.L.dnxcu_launch(C.byref(q), None))
+        assert (back.check().view(np.uint16) == x.view(np.uint16)).all(), (name, vec, "slice")
+    # a slice that would read outside its input is refused before any launch
+    bad = lib.Dispatch()
+    bad.variant = lib.L.dnxcu_find_variant(b"memory-slice", b"VEC=1")
+    bad.pc[0], bad.pc[1], bad.c_a = w, h, c
+    bad.pc_ext[0], bad.pc_ext[1], bad.pc_ext[2], bad.pc_ext[3] = 1, 0, w, h
+    bad.in_a, bad.out = tx.data_ptr(), tx.data_ptr()
+    assert lib.L.dnxcu_launch(C.byref(bad), None) == lib.E_BAD_ARG

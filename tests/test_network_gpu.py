@@ -81,12 +81,31 @@ def test_oidn_larger_frame_properties():
     model.close()
 
 
-def test_instance_rejects_unaligned_extent():
+def test_unaligned_extent_runs_behind_pad_and_slice():
+    """A frame whose extent is not a multiple of 16 (the reference pads such frames by edge replication and
+    slices the output, oidn_model.py:334-347): the instance does both, results as the oracle's wrapper and
+    PyTorch's."""
     net = nets.oidn_unet()
     model = lib.Model(net)
-    with pytest.raises(lib.DnxcuError) as e:
-        lib.Instance(model, 100, 100)  # not a multiple of 16: the reference pads such images first
-    assert e.value.status == lib.E_UNSUPPORTED
+    inst = lib.Instance(model, 40, 52)
+    assert inst.extent() == (40, 52, 48, 64)
+    x = nets.oidn_input(1002, 40, 52)
+    y = inst.infer(x)
+    assert y.shape == (40, 52, 3)
+    ref = oracle.run_network_aligned(net, x)
+    assert_close(y, ref, "oidn 40x52 behind pad/slice vs oracle")
+    assert_close(y, GOLD["oidn_40x52_aligned/out"], "oidn 40x52 behind pad/slice vs PyTorch golden")
+    # stream ordered form with the same buffers
+    import torch
+    xs = torch.from_numpy(x).pin_memory()
+    ys = torch.empty((40, 52, 3), dtype=torch.float16).pin_memory()
+    inst.infer_async(xs.numpy(), ys.numpy())
+    inst.wait()
+    assert (ys.numpy().view(np.uint16) == y.view(np.uint16)).all()
+    inst.close()
+    # a row band must still be aligned: bands of an unaligned frame are not offered
+    with pytest.raises(lib.DnxcuError):
+        lib.Instance(model, 24, 52, band=(40, 0, 24))
     model.close()
 
 

@@ -111,3 +111,25 @@ def test_oidn_intermediates_match_torch():
     for name in ("enc_conv1", "enc_conv4", "dec_conv4a", "dec_conv1a"):
         nd = next(q for q in n.nodes if q.name == name + ".relu")
         assert ref_allclose(t[nd.out], GOLD[f"oidn_32x48/{name}"]).all(), name
+
+
+@pytest.mark.parametrize("case", mg.PAD_CASES, ids=[c[0] for c in mg.PAD_CASES])
+def test_pad_edge_and_slice_match_torch_bit_exact(case):
+    name, h, w, c, l, r, t, b = case
+    x = mg.pad_case_input(case)
+    y = oracle.pad_edge(x, l, r, t, b)
+    ref = GOLD["pad/" + name]
+    assert y.shape == ref.shape == (h + t + b, w + l + r, c)
+    assert (y.view(np.uint16) == ref.view(np.uint16)).all()
+    back = oracle.slice_hw(y, l, t, h, w)
+    assert (back.view(np.uint16) == x.view(np.uint16)).all()
+
+
+def test_aligned_network_matches_torch():
+    """OIDN-style net on a 40 x 52 frame behind the alignment wrapper (pad to 48 x 64, run, slice)."""
+    net = nets.oidn_unet()
+    x = nets.oidn_input(1002, 40, 52)
+    y = oracle.run_network_aligned(net, x)
+    ref = GOLD["oidn_40x52_aligned/out"]
+    assert y.shape == ref.shape == (40, 52, 3)
+    assert ref_allclose(y, ref).all()
