@@ -143,6 +143,35 @@ def test_validate_rules():
     assert ok(C.byref(p)) == 0
 
 
+def test_pad_and_slice_dispatch_rules():
+    """memory_pad.comp / memory_slice.comp stand-ins: push constants in pc (output extent) and pc_ext."""
+    ok = lib.L.dnxcu_validate
+    p = lib.Dispatch()
+    p.variant, p.c_a = lib.find_variant("memory-pad", "VEC=1"), 9
+    p.pc[0], p.pc[1] = 1920, 1088
+    p.pc_ext[1], p.pc_ext[3] = 0, 8  # bottom pad of 8: a 1080 row frame
+    p.in_a = p.out = 0x1000
+    assert ok(C.byref(p)) == 0
+    rd, wr, fl = C.c_uint64(), C.c_uint64(), C.c_uint64()
+    assert lib.L.dnxcu_cost(C.byref(p), C.byref(rd), C.byref(wr), C.byref(fl)) == 0
+    assert (rd.value, wr.value, fl.value) == (2 * 1920 * 1080 * 9, 2 * 1920 * 1088 * 9, 0)
+    p.pc_ext[3] = 1088  # nothing left of the input
+    assert ok(C.byref(p)) == lib.E_BAD_ARG
+    p.pc_ext[3] = 8
+    p.variant = lib.find_variant("memory-pad", "VEC=8")
+    assert ok(C.byref(p)) == lib.E_UNSUPPORTED  # 128-bit form needs C % 8 == 0
+    q = lib.Dispatch()
+    q.variant, q.c_a = lib.find_variant("memory-slice", "VEC=1"), 3
+    q.pc[0], q.pc[1] = 1920, 1080
+    q.pc_ext[2], q.pc_ext[3] = 1920, 1088
+    q.in_a = q.out = 0x1000
+    assert ok(C.byref(q)) == 0
+    q.pc_ext[1] = 9  # rows 9 .. 1088 of a 1088 row input
+    assert ok(C.byref(q)) == lib.E_BAD_ARG
+    ops = {v["family"]: v["op"] for v in lib.variants()}
+    assert ops["memory-pad"] == lib.OP_PAD_EDGE and ops["memory-slice"] == lib.OP_SLICE
+
+
 def test_grid_is_persistent_and_bounded():
     g = (C.c_uint32 * 3)()
     assert lib.L.dnxcu_grid(C.byref(_conv_dispatch(2)), C.byref(g)) == 0
