@@ -889,12 +889,17 @@ __device__ __forceinline__ void epi_fast(const TcArgs &g, uint32_t t0, uint32_t 
 //   - block ring: output row number ob (counted over the CTA's whole life) uses
 //     TMEM block ob % NB, columns [block * N, block * N + N)
 //   - an output row is complete after input row y+1: commit -> tfull[block]
-//   - the block of output row j+1 is fresh at input row j: its first MMA
-//     (dx = 0, first channel step) is issued on its own with accumulate = 0
+//   - every MMA accumulates: the epilogue zeroes a block (tcgen05.st) after its last
+//     read and hands it back zeroed; all blocks are zeroed once at kernel start
 //   - runs of blocks are split where the ring wraps and where N' would exceed 256
 //   - an input slot is released as soon as its own row's MMAs are committed
-// Two epilogue teams of four warps take alternate row pairs.
-constexpr int ST_THREADS = 512;        // MMA, weights, 8 epilogue warps, 4 producer warps, 2 descriptor warps
+// Warp roles (512 threads): warps 0..P-1 issue the MMAs of pipeline 0..P-1 (one thread
+// each; warp 0 owns the TMEM allocation); warp 1 also moves the weights and, with one
+// pipeline in expand mode, issues the TMA copies; warps 2..2+4P-1 are the epilogue teams
+// (four warps per pipeline, one TMEM lane quarter each); warps 10-13 fill the input
+// slots; warps 14, 15 hold the descriptor threads (one thread per pipeline), which work
+// out, per entry, what the MMA thread needs and write it to shared memory.
+constexpr int ST_THREADS = 512;
 constexpr int ST_MAX_BLOCKS = 16;
 constexpr int ST_BAR_FULL = 0;
 constexpr int ST_BAR_EMPTY = ST_BAR_FULL + MAX_SLOTS;
@@ -930,7 +935,7 @@ struct Run {
   uint32_t col;    // first TMEM column
   uint32_t boff;   // byte offset of the run's first weight row inside a stacked chunk, >> 4
   uint32_t idesc;  // instruction descriptor with this run's N'
-  uint32_t acc;    // 0: overwrite (fresh block), 1: accumulate
+  uint32_t acc;    // 1: in use (accumulates), 2: unused
 };
 
 // The MMAs of one input row (all horizontal taps, NK K steps, NR runs of TMEM blocks) as straight
