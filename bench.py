@@ -145,6 +145,29 @@ def _private_stdout():
     return out
 
 
+def bind_to_gpu_numa_node(torch, device):
+    """Several ranks share the host: run this rank on the CPUs of the NUMA node its GPU hangs off, so that the
+    pinned frame buffers it allocates next are local to that GPU's PCIe root (first touch).  Returns the node
+    or None when the topology cannot be read."""
+    try:
+        bdf = torch.cuda.get_device_properties(device)
+        bus = f"{bdf.pci_domain_id:04x}:{bdf.pci_bus_id:02x}:{bdf.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return node
+    except Exception:
+        return None
+
+
 def main():
     result_out = _private_stdout()
     ap = argparse.ArgumentParser()
@@ -175,6 +198,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: this backend has no CPU path")
     torch.cuda.set_device(local_rank)
+    numa = bind_to_gpu_numa_node(torch, local_rank) if world > 1 else None
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -351,7 +375,8 @@ def main():
                    "dispatches_per_frame": n_disp, "streams": NS, "gflop_per_frame": nets.total_flops(net, H, W) / 1e9,
                    "roofline_bound_ms_per_frame": round(sum_bound_ms, 4)},
         "e2e": {"value": e2e, "unit": "frames/s", "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
-                "api": "dnxcu_instance_infer_async + dnxcu_instance_wait, 3 instances round robin, pinned host buffers"},
+                "api": "dnxcu_instance_infer_async + dnxcu_instance_wait, 3 instances round robin, pinned host buffers",
+                "numa_node": numa},
         "gpu_launches": args.steps * n_disp,
         "clocks": clocks,
         "roofline": roof,
