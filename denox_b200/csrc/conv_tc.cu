@@ -109,6 +109,7 @@ struct TcArgs {
   uint32_t tmem_cols;
   int desc_swap;  // debugging aid: exchange the two descriptor strides
   long long *trace;  // debugging aid: per role time stamps of CTA 0 (nullptr = off)
+  int switch_issue;  // debugging aid: the straight line form is chosen per row even with one K group
   int loop_issue;  // debugging aid: MMAs issued by the generic loops instead of the straight line code
   int skip;       // debugging aid (timing only, results wrong): 1 no input loads, 2 no MMAs, 4 no output stores
 };
@@ -956,6 +957,10 @@ __device__ __forceinline__ void st_issue_row(uint32_t hi, uint32_t row_lo, uint3
     }
   }
 }
+template <int V>
+struct IntC {
+  static constexpr int value = V;
+};
 template <int NR>
 __device__ __forceinline__ bool st_issue_nk(int nk, uint32_t hi, uint32_t row_lo, uint32_t b_lo, uint32_t wdx16,
                                             uint32_t kstep_b, const Run &r0, const Run &r1) {
@@ -1188,7 +1193,10 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     auto mma1 = [&](uint32_t d, uint32_t alo, uint32_t blo, uint32_t idesc, uint32_t acc) {
       tc_mma(d, ((uint64_t)a_hi << 32) | alo, ((uint64_t)b_hi << 32) | blo, idesc, acc);
     };
-    if (lane == 0 && ok && (int)blockIdx.x * P + pipe < g.nunits) {
+    // The loop, instantiated per K step count: when all K groups have the same count, the choice of the
+    // straight line form is made once here and not per row (NKC = 0: per row, by a switch).
+    auto mma_loop = [&](auto NKC) {
+      constexpr int NK = decltype(NKC)::value;
       int slot = 0, pos = 0;
       uint32_t fphase = 0;
       for (;;) {
@@ -1201,21 +1209,26 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         tc_fence_after();
         if (!(g.skip & 2)) {
           const uint32_t row_lo = q0.x, b_lo = q0.y;
-          const int nk16 = (int)(flags & 15u);
           const Run R0 = {q1.x, q1.y, q1.z, 1u}, R1 = {q1.w, q2.x, q2.y, 1u};
-          bool done = false;
-          if (!g.loop_issue)
-            done = (flags & DF_NR2) ? st_issue_nk<2>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1)
-                                    : st_issue_nk<1>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0);
-          if (!done) {
-            // more K steps than the straight line forms cover
-            for (int dx = 0; dx < 3; ++dx)
-              for (int kc = 0; kc < nk16; ++kc) {
-                const uint32_t a = row_lo + (uint32_t)dx + (uint32_t)kc * kstep_a;
-                const uint32_t b = b_lo + (uint32_t)dx * (wdx_bytes >> 4) + (uint32_t)kc * kstep_b;
-                mma1(R0.col, a, b + R0.boff, R0.idesc, 1u);
-                if (flags & DF_NR2) mma1(R1.col, a, b + R1.boff, R1.idesc, 1u);
-              }
+          if constexpr (NK > 0) {
+            if (flags & DF_NR2) st_issue_row<NK, 2>(a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1);
+            else st_issue_row<NK, 1>(a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0);
+          } else {
+            const int nk16 = (int)(flags & 15u);
+            bool done = false;
+            if (!g.loop_issue)
+              done = (flags & DF_NR2) ? st_issue_nk<2>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1)
+                                      : st_issue_nk<1>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0);
+            if (!done) {
+              // more K steps than the straight line forms cover
+              for (int dx = 0; dx < 3; ++dx)
+                for (int kc = 0; kc < nk16; ++kc) {
+                  const uint32_t a = row_lo + (uint32_t)dx + (uint32_t)kc * kstep_a;
+                  const uint32_t b = b_lo + (uint32_t)dx * (wdx_bytes >> 4) + (uint32_t)kc * kstep_b;
+                  mma1(R0.col, a, b + R0.boff, R0.idesc, 1u);
+                  if (flags & DF_NR2) mma1(R1.col, a, b + R1.boff, R1.idesc, 1u);
+                }
+            }
           }
         }
         if (tr) trace(g, 0, pos, 2);
@@ -1228,6 +1241,20 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           slot = 0;
           fphase ^= 1u;
         }
+      }
+    };
+    if (lane == 0 && ok && (int)blockIdx.x * P + pipe < g.nunits) {
+      bool same = !g.loop_issue && !g.switch_issue;
+      for (int gi = 1; gi < g.G; ++gi) same = same && g.gch[gi] == g.gch[0];
+      const int nkfix = same ? (g.gch[0] >> 1) : 0;
+      switch (nkfix) {
+        case 1: mma_loop(IntC<1>{}); break;
+        case 2: mma_loop(IntC<2>{}); break;
+        case 3: mma_loop(IntC<3>{}); break;
+        case 4: mma_loop(IntC<4>{}); break;
+        case 5: mma_loop(IntC<5>{}); break;
+        case 6: mma_loop(IntC<6>{}); break;
+        default: mma_loop(IntC<0>{}); break;
       }
     }
     __syncwarp();
@@ -1883,6 +1910,8 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   g.desc_swap = (sw && sw[0] == '1') ? 1 : 0;
   const char *sk = getenv("DNXCU_TC_SKIP");
   g.skip = sk ? atoi(sk) : 0;
+  const char *si = getenv("DNXCU_TC_SWITCH_ISSUE");
+  g.switch_issue = (si && si[0] == '1') ? 1 : 0;
   const char *li = getenv("DNXCU_TC_LOOP_ISSUE");
   g.loop_issue = (li && li[0] == '1') ? 1 : 0;
   // time line tracing: the caller's status buffer must then hold 8 + 3*64*6 64-bit words
