@@ -1075,22 +1075,31 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   const int unit_stride = (int)gridDim.x * P;
   const int nprod_warps = P == 2 ? 2 : 4;  // producer warps per pipeline
 
-  if (threadIdx.x == 0) {
-    *abort_flag = 0;
+  if (warp == 2) {
+    // barrier set-up by a whole warp (one barrier per lane and round) while warp 0 allocates tensor memory
+    if (lane == 0) *abort_flag = 0;
     // who completes a slot: the TMA bytes alone; or TMA bytes + the producer warps' cp.async part; or, in expand
-    // mode, the producer warps alone after they have expanded the TMA data that landed on the raw barrier
-    const uint32_t full_count = 1u + (g.xp ? (uint32_t)nprod_warps : (g.cpa ? (uint32_t)nprod_warps + 1u : 1u));  // + the descriptor thread
-    for (int i = 0; i < MAX_SLOTS; ++i) {
-      mbar_init(bar(ST_BAR_FULL + i), full_count);
-      mbar_init(bar(ST_BAR_EMPTY + i), 1);
-      mbar_init(bar(ST_BAR_RAW + i), 1);
+    // mode, the producer warps alone after they have expanded the TMA data that landed on the raw barrier;
+    // plus, always, the descriptor thread
+    const uint32_t full_count = 1u + (g.xp ? (uint32_t)nprod_warps : (g.cpa ? (uint32_t)nprod_warps + 1u : 1u));
+    for (int i = lane; i < ST_BAR_COUNT; i += 32) {
+      if (i == ST_BAR_WRES) continue;  // warp 1's own
+      uint32_t count = 1;
+      if (i >= ST_BAR_FULL && i < ST_BAR_FULL + MAX_SLOTS) count = full_count;
+      if (i >= ST_BAR_TEMPTY && i < ST_BAR_TEMPTY + ST_MAX_BLOCKS) count = 4;
+      mbar_init(bar(i), count);
     }
-    for (int i = 0; i < ST_MAX_BLOCKS; ++i) {
-      mbar_init(bar(ST_BAR_TFULL + i), 1);
-      mbar_init(bar(ST_BAR_TEMPTY + i), 4);
-    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1 && lane == 0) {
+    // ---------------- weights (resident), copies of at most 32 KB: started before anything else ----------------
     mbar_init(bar(ST_BAR_WRES), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(g.w);
+    const uint32_t total = wdx_bytes * 3u;
+    mbar_expect_tx(bar(ST_BAR_WRES), total);
+    for (uint32_t off = 0; off < total; off += 32768u)
+      bulk_g2s(w_addr + off, wsrc + off, min(32768u, total - off), bar(ST_BAR_WRES));
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + ST_OFF_TMEM_PTR),
@@ -1162,14 +1171,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     return true;
   };
 
-  if (warp == 1 && lane == 0) {
-    // ---------------- weights (resident), copies of at most 32 KB ----------------
-    const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(g.w);
-    const uint32_t total = wdx_bytes * 3u;
-    mbar_expect_tx(bar(ST_BAR_WRES), total);
-    for (uint32_t off = 0; off < total; off += 32768u)
-      bulk_g2s(w_addr + off, wsrc + off, min(32768u, total - off), bar(ST_BAR_WRES));
-  }
   if (warp == 1 && lane == 0 && g.xp && P == 1) {
     // one pipeline: this thread has nothing else to do and feeds the expand mode's TMA copies
     XpCursor is;
