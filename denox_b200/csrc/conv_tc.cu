@@ -1142,7 +1142,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   auto xp_issue = [&](XpCursor &is, int pipe) -> bool {
     const int bofs = pipe * ST_PIPE_STRIDE;
     const uint32_t slots_addr = slots_addr0 + (uint32_t)(pipe * S) * slot_bytes;
-    const uint32_t src0 = slots_addr0 + (uint32_t)(P * S) * slot_bytes + (uint32_t)(pipe * S) * g.src_bytes;
     const int nca = g.a.nch;
     const int iy = is.t.y0 - 1 + is.jj;
     const bool a_tma = row_by_tma(g, g.a, iy), b_tma = g.b.nch > 0 && row_by_tma(g, g.b, iy);
@@ -1150,7 +1149,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     const int a_lo = min(c_lo, nca), a_hi = min(c_hi, nca);  // operand a's chunks in this group
     if (!mbar_wait<64>(bar(ST_BAR_EMPTY + bofs + is.slot), is.ephase, abort_flag, g.status, 7)) return false;
     const uint32_t slot_addr = slots_addr + (uint32_t)is.slot * slot_bytes;
-    const uint32_t src_addr = src0 + (uint32_t)is.slot * g.src_bytes;
     const uint32_t rb = bar(ST_BAR_RAW + bofs + is.slot);
     uint32_t bytes = 0;
     if (a_tma) bytes += (uint32_t)(a_hi - a_lo) * SRC_PITCH;
@@ -1159,8 +1157,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     if (bytes) {
       mbar_expect_tx(rb, bytes);
       if (a_tma)
-        for (int c = a_lo; c < a_hi; c += g.a.tbox)
-          tma_load_4d(src_addr + (uint32_t)((c - a_lo) * SRC_PITCH), &g.tm_a, 0, (is.t.x0 >> 1) - 1, c, iy >> 1, rb);
+        for (int c = a_lo; c < a_hi; c += 2)  // two chunks of the half resolution row, packed, at the first one's place
+          tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, (is.t.x0 >> 1) - 1, c, iy >> 1, rb);
       if (b_tma)
         for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
           tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, is.t.x0 - 1, c - nca, iy, rb);
@@ -1442,7 +1440,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
       // src = dst / 2).  TMA fetches the half resolution row (66 pixels) into a staging buffer and operand
       // b's row straight into the slot; both land on the slot's raw barrier.  The producer warps then write
       // every source pixel to its two destination pixels inside shared memory and signal the slot.
-      const uint32_t src0 = slots_addr0 + (uint32_t)(P * S) * slot_bytes + (uint32_t)(pipe * S) * g.src_bytes;
       const int nca = g.a.nch;
       // Thread 0 of the producer warps (two pipelines) or lane 0 of the otherwise idle weights warp (one
       // pipeline) starts the TMA copies; it runs ahead of the expansion as far as free slots allow, so the copy
@@ -1454,13 +1451,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
       xp_start(ex, pipe);
       int ahead = 0;  // entries issued but not yet expanded (thread 0, self_issue only)
       int xcount = 0;
-      while (ok && ex.valid) {
+      while (ex.valid) {
         if (self_issue && tid == 0) {
           while (ok && is.valid && ahead < LA) {
             ok = xp_issue(is, pipe);
             ++ahead;
           }
-          if (!ok) break;
         }
         // expand entry `ex`
         {
@@ -1469,10 +1465,25 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           const int c_lo = g.gc0[ex.gi], c_hi = c_lo + g.gch[ex.gi];
           const int a_lo = min(c_lo, nca), a_hi = min(c_hi, nca);
           const uint32_t slot_addr = slots_addr + (uint32_t)ex.slot * slot_bytes;
-          const uint32_t src_addr = src0 + (uint32_t)ex.slot * g.src_bytes;
           const uint32_t rb = bar(ST_BAR_RAW + bofs + ex.slot);
           if (tid == 32 && pipe == 0) trace(g, 2, xcount, 0);
-          ok = mbar_wait<32>(rb, ex.rphase, abort_flag, g.status, 8);
+          if (ok) ok = mbar_wait<32>(rb, ex.rphase, abort_flag, g.status, 8);
+          // The expansion below meets at a named barrier, so the producer threads of a pipeline must leave
+          // this loop together: they vote, and a wait that ran out in one of them takes all of them out.
+          {
+            uint32_t all_ok;
+            asm volatile(
+                "{\n\t"
+                ".reg .pred p, q;\n\t"
+                "setp.ne.u32 p, %1, 0;\n\t"
+                "bar.red.and.pred q, %2, %3, p;\n\t"
+                "selp.u32 %0, 1, 0, q;\n\t"
+                "}"
+                : "=r"(all_ok)
+                : "r"((uint32_t)ok), "r"(1 + pipe), "r"(nprod)
+                : "memory");
+            ok = all_ok != 0;
+          }
           if (!ok) break;
           if (tid == 32 && pipe == 0) trace(g, 2, xcount, 1);
           // rows TMA does not cover (halo rows of a row band) come the old way; the raw barrier has completed,
@@ -1483,24 +1494,30 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
             cp_async_wait<0>();
           }
           if (a_tma && !(g.skip & 1)) {
-            const int n = a_hi - a_lo;
-            for (int px = tid; px < SLOT_PX; px += nprod) {
-              uint32_t sp = src_addr + (uint32_t)(((px + 1) >> 1) * 16);
-              uint32_t dp = slot_addr + (uint32_t)((a_lo - c_lo) * CHUNK_PITCH + px * 16);
-              // four loads in flight, then their four stores
-              for (int ch = 0; ch < n; ch += 4) {
-                uint4 v[4];
+            // In place, one pair of chunks at a time: the copy left the pair's two half resolution rows packed
+            // (2 x 72 pixels) at the start of the pair's 2 x 132 pixel area.  Every thread first loads the
+            // sources of its pixels, then all producer threads of the pipeline meet, then they store.
+            for (int c = a_lo; c < a_hi; c += 2) {
+              const uint32_t pair = slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH);
+              uint4 v[3][2];
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  if (ch + q < n) v[q] = lds16(sp + (uint32_t)(q * SRC_PITCH));
+              for (int i = 0; i < 3; ++i) {
+                const int px = tid + i * nprod;
+                if (px < SLOT_PX) {
+                  const uint32_t sp = pair + (uint32_t)(((px + 1) >> 1) * 16);
+                  v[i][0] = lds16(sp);
+                  v[i][1] = lds16(sp + (uint32_t)SRC_PITCH);
+                }
+              }
+              asm volatile("bar.sync %0, %1;" ::"r"(1 + pipe), "r"(nprod) : "memory");
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  if (ch + q < n)
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dp + (uint32_t)(q * CHUNK_PITCH)), "r"(v[q].x),
-                                 "r"(v[q].y), "r"(v[q].z), "r"(v[q].w)
-                                 : "memory");
-                sp += 4 * SRC_PITCH;
-                dp += 4 * CHUNK_PITCH;
+              for (int i = 0; i < 3; ++i) {
+                const int px = tid + i * nprod;
+                if (px < SLOT_PX) {
+                  const uint32_t dp = pair + (uint32_t)(px * 16);
+                  sts16(dp, v[i][0]);
+                  sts16(dp + (uint32_t)CHUNK_PITCH, v[i][1]);
+                }
               }
             }
           }
@@ -1772,7 +1789,8 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
       const int hi = g.gc0[gi] + g.gch[gi] < g.a.nch ? g.gc0[gi] + g.gch[gi] : g.a.nch;
       if (hi - lo > amax) amax = hi - lo;
     }
-    xp_src_bytes = (uint32_t)amax * SRC_PITCH;
+    xp_src_bytes = 0;  // the half resolution rows land in the slot itself and are expanded in place
+    (void)amax;
   }
   const bool stage_possible = g.K % 8 == 0 && !(nost && nost[0] == '1');
   const size_t stage_pitch = (size_t)g.K * 2 + 16;
@@ -1846,7 +1864,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   memset(&g.tm_b, 0, sizeof(g.tm_b));
   if (encode) {
     if (g.xp) {
-      if (make_tensor_map(&g.tm_a, d.in_a, H / 2, W / 2, d.c_a, g.a.tbox, SRC_PX)) return DNXCU_E_CUDA;
+      if (make_tensor_map(&g.tm_a, d.in_a, H / 2, W / 2, d.c_a, 2, SRC_PX)) return DNXCU_E_CUDA;
     } else if (g.a.tma && make_tensor_map(&g.tm_a, d.in_a, H, W, d.c_a, g.a.tbox)) {
       return DNXCU_E_CUDA;
     }
