@@ -99,6 +99,7 @@ static const Variant kVariants[] = {
     {{22, DNXCU_OP_PAD_EDGE, "memory-pad", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_PAD_EDGE, 1, 0, 0, 0},
     {{23, DNXCU_OP_SLICE, "memory-slice", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_SLICE, 8, 0, 0, 0},
     {{24, DNXCU_OP_SLICE, "memory-slice", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_SLICE, 1, 0, 0, 0},
+    {{25, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=1#W=resident#PIPES=1", CONV_ALL, 1, 1, 1, 128, 0}, VK_CONV_TC, 0, 1, 2, 0},
 };
 static const int kVariantCount = (int)(sizeof(kVariants) / sizeof(kVariants[0]));
 

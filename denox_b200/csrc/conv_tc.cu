@@ -1797,7 +1797,8 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   const size_t stage_per_warp = (g.pool ? 2 : 1) * 32 * stage_pitch;
   const size_t base_bytes = ST_HEADER_BYTES + wregion;
   const size_t plain_slot = (size_t)g.gmax * CHUNK_PITCH;
-  const bool p2_possible = 4 * g.N <= 256 && !(np && np[0] == '1');
+  // v.p2 == 2 ("PIPES=1"): one pipeline with a longer slot ring even where two would fit
+  const bool p2_possible = 4 * g.N <= 256 && !(np && np[0] == '1') && v.p2 != 2;
   // candidate configurations, best first: (pipelines, expand, staging)
   int P = 0;
   size_t slot_bytes = 0, stage_total = 0;
@@ -1873,7 +1874,8 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   return DNXCU_OK;
 }
 
-// v.p0 = R (rows per pass), v.p1 = K groups, v.p2 = weight mode (0 resident, 1 streamed), v.p3 = weight stages
+// v.p0 = R (rows per pass), v.p1 = K groups, v.p2 = weight mode (0 resident, 1 streamed; stacked form: 2 = one
+// pipeline only), v.p3 = weight stages (stacked form: output channel split)
 int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, int os_override = 0) {
   if (!d.in_a || !d.weights || d.c_a <= 0 || d.c_out <= 0 || d.c_b < 0) return DNXCU_E_BAD_ARG;
   if (d.pc[0] == 0 || d.pc[1] == 0) return DNXCU_E_BAD_ARG;
@@ -1922,7 +1924,7 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   g.relu = (d.flags & DNXCU_F_RELU) ? 1 : 0;
   g.pool = pool ? 1 : 0;
   g.full_out = full ? 1 : 0;
-  g.wstream = v.p2;
+  g.wstream = v.p2 == 1 ? 1 : 0;
   g.WST = v.p3 > 0 ? v.p3 : 2;
   if (g.WST > MAX_WST) g.WST = MAX_WST;
   const char *sw = getenv("DNXCU_TC_DESC_SWAP");
