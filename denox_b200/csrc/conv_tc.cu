@@ -110,6 +110,7 @@ struct TcArgs {
   int desc_swap;  // debugging aid: exchange the two descriptor strides
   long long *trace;  // debugging aid: per role time stamps of CTA 0 (nullptr = off)
   int switch_issue;  // debugging aid: the straight line form is chosen per row even with one K group
+  int parts;       // launches of this dispatch that run side by side (output channel split): each plans for 1/parts of the SMs
   int loop_issue;  // debugging aid: MMAs issued by the generic loops instead of the straight line code
   int skip;       // debugging aid (timing only, results wrong): 1 no input loads, 2 no MMAs, 4 no output stores
 };
@@ -1843,7 +1844,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   g.tmem_cols = p2;
   g.D = g.S - 1 < MAX_DEPTH ? g.S - 1 : MAX_DEPTH;
   pl.smem = ST_HEADER_BYTES + wregion + (size_t)P * g.S * slot_bytes + stage_total;
-  const int sms = sm_count();
+  const int sms = g.parts > 1 ? (sm_count() / g.parts > 0 ? sm_count() / g.parts : 1) : sm_count();
   const int lanes = sms * P;
   double best = 1e30;
   int bestRB = 2;
@@ -1876,7 +1877,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
 
 // v.p0 = R (rows per pass), v.p1 = K groups, v.p2 = weight mode (0 resident, 1 streamed; stacked form: 2 = one
 // pipeline only), v.p3 = weight stages (stacked form: output channel split)
-int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, int os_override = 0) {
+int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, int os_override = 0, int parts = 1) {
   if (!d.in_a || !d.weights || d.c_a <= 0 || d.c_out <= 0 || d.c_b < 0) return DNXCU_E_BAD_ARG;
   if (d.pc[0] == 0 || d.pc[1] == 0) return DNXCU_E_BAD_ARG;
   if (d.c_b > 0 && !d.in_b) return DNXCU_E_BAD_ARG;
@@ -1925,6 +1926,7 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   g.pool = pool ? 1 : 0;
   g.full_out = full ? 1 : 0;
   g.wstream = v.p2 == 1 ? 1 : 0;
+  g.parts = parts;
   g.WST = v.p3 > 0 ? v.p3 : 2;
   if (g.WST > MAX_WST) g.WST = MAX_WST;
   const char *sw = getenv("DNXCU_TC_DESC_SWAP");
@@ -2144,7 +2146,7 @@ int conv_tc_validate(const Variant &v, const dnxcu_dispatch &d) {
   for (int p = 0; p < n; ++p) {
     Plan pl;
     const dnxcu_dispatch dp = part_dispatch(d, k0[p], kp[p], woff);
-    const int st = make_plan(v, dp, pl, false, d.c_out);
+    const int st = make_plan(v, dp, pl, false, d.c_out, n);
     if (st) return st;
     woff += (size_t)9 * (nch_of(d.c_a) + nch_of(d.c_b)) * pad16(kp[p]) * 16;
   }
@@ -2157,8 +2159,33 @@ void conv_tc_grid(const Variant &v, const dnxcu_dispatch &d, uint32_t g[3]) {
   Plan pl;
   g[0] = g[1] = g[2] = 1;
   const dnxcu_dispatch dp = n == 1 ? d : part_dispatch(d, k0[0], kp[0], 0);
-  if (make_plan(v, dp, pl, false, n == 1 ? 0 : d.c_out) == DNXCU_OK) g[0] = (uint32_t)pl.grid;
+  if (make_plan(v, dp, pl, false, n == 1 ? 0 : d.c_out, n) == DNXCU_OK) g[0] = (uint32_t)pl.grid;
   g[2] = (uint32_t)n;  // launches
+}
+
+// Side streams for the launches of an output channel split: the parts are independent, each plans for its share
+// of the SMs, and they run side by side between a fork and a join on the caller's stream (inside a stream
+// capture this becomes parallel branches of the graph).  Created on first use, per device.
+struct SideStreams {
+  cudaStream_t stream[8] = {};
+  cudaEvent_t fork = nullptr, join[8] = {};
+  bool ready = false;
+};
+static SideStreams g_side[16];
+
+static int side_streams(int dev, SideStreams **out) {
+  if (dev < 0 || dev >= 16) return DNXCU_E_UNSUPPORTED;
+  SideStreams &ss = g_side[dev];
+  if (!ss.ready) {
+    DNXCU_CUDA(cudaEventCreateWithFlags(&ss.fork, cudaEventDisableTiming));
+    for (int i = 1; i < 8; ++i) {
+      DNXCU_CUDA(cudaStreamCreateWithFlags(&ss.stream[i], cudaStreamNonBlocking));
+      DNXCU_CUDA(cudaEventCreateWithFlags(&ss.join[i], cudaEventDisableTiming));
+    }
+    ss.ready = true;
+  }
+  *out = &ss;
+  return DNXCU_OK;
 }
 
 int conv_tc_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
@@ -2166,23 +2193,53 @@ int conv_tc_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
   int k0[8], kp[8];
   const int n = split_parts(v, d.c_out, k0, kp);
   if (n > 1 && d.c_out % 16) return DNXCU_E_UNSUPPORTED;
+  SideStreams *ss = nullptr;
+  if (n > 1) {
+    int dev = 0;
+    DNXCU_CUDA(cudaGetDevice(&dev));
+    int st = side_streams(dev, &ss);
+    if (st) return st;
+    // plans first: nothing may fail between the fork and the join
+    size_t woff = 0;
+    for (int p = 0; p < n; ++p) {
+      Plan pl;
+      const dnxcu_dispatch dp = part_dispatch(d, k0[p], kp[p], woff);
+      st = make_plan(v, dp, pl, false, d.c_out, n);
+      if (st) return st;
+      if (pl.R != 0) return DNXCU_E_UNSUPPORTED;
+      woff += (size_t)9 * (nch_of(d.c_a) + nch_of(d.c_b)) * pad16(kp[p]) * 16;
+    }
+    DNXCU_CUDA(cudaEventRecord(ss->fork, s));
+    for (int p = 1; p < n; ++p) DNXCU_CUDA(cudaStreamWaitEvent(ss->stream[p], ss->fork, 0));
+  }
   size_t woff = 0;
+  int result = DNXCU_OK;
   for (int p = 0; p < n; ++p) {
     Plan pl;
     const dnxcu_dispatch dp = n == 1 ? d : part_dispatch(d, k0[p], kp[p], woff);
-    int st = make_plan(v, dp, pl, true, n == 1 ? 0 : d.c_out);
-    if (st) return st;
-    switch (pl.R) {
-      case 0: st = launch_stack(pl, s); break;
-      case 1: st = launch_r<1>(pl, s); break;
-      case 2: st = launch_r<2>(pl, s); break;
-      case 4: st = launch_r<4>(pl, s); break;
-      default: st = DNXCU_E_UNSUPPORTED; break;
+    cudaStream_t sp = (n > 1 && p > 0) ? ss->stream[p] : s;
+    int st = make_plan(v, dp, pl, true, n == 1 ? 0 : d.c_out, n);
+    if (!st) {
+      switch (pl.R) {
+        case 0: st = launch_stack(pl, sp); break;
+        case 1: st = launch_r<1>(pl, sp); break;
+        case 2: st = launch_r<2>(pl, sp); break;
+        case 4: st = launch_r<4>(pl, sp); break;
+        default: st = DNXCU_E_UNSUPPORTED; break;
+      }
     }
-    if (st) return st;
+    if (st && !result) result = st;
+    if (st && n == 1) return st;
     woff += (size_t)9 * (nch_of(d.c_a) + nch_of(d.c_b)) * pad16(kp[p]) * 16;
   }
-  return DNXCU_OK;
+  if (n > 1) {
+    // the join is made even after a failed launch, so that the side streams never stay forked
+    for (int p = 1; p < n; ++p) {
+      cudaEventRecord(ss->join[p], ss->stream[p]);
+      cudaStreamWaitEvent(s, ss->join[p], 0);
+    }
+  }
+  return result;
 }
 
 }  // namespace dnxcu
