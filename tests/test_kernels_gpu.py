@@ -181,3 +181,24 @@ def test_pad_edge_and_slice_bit_exact(case):
     bad.pc_ext[0], bad.pc_ext[1], bad.pc_ext[2], bad.pc_ext[3] = 1, 0, w, h
     bad.in_a, bad.out = tx.data_ptr(), tx.data_ptr()
     assert lib.L.dnxcu_launch(C.byref(bad), None) == lib.E_BAD_ARG
+
+
+@pytest.mark.parametrize("shape", [(7, 37, 9, 16), (16, 16, 3, 8), (33, 129, 9, 16), (5, 11, 67, 72), (3, 700, 12, 16)])
+def test_pad_channels_bit_exact(shape):
+    """copy-transform PAD=8 (HWC with C channels -> HWC with c_out channels, new ones zero), both kernel forms
+    (tiled through shared memory for C <= 48, direct otherwise), pixel counts that are not a multiple of a tile."""
+    import ctypes as C
+    from gpu_util import Guarded, dev
+    h, w, c, co = shape
+    x = rng.to_f16(rng.uniform(9100 + c, h * w * c, -3.0, 3.0)).reshape(h, w, c)
+    ref = np.zeros((h, w, co), dtype=np.float16)
+    ref[:, :, :c] = x
+    d = lib.Dispatch()
+    d.variant = lib.L.dnxcu_find_variant(b"copy-transform", b"PAD=8")
+    d.pc[0], d.pc[1], d.c_a, d.c_out = w, h, c, co
+    tx = dev(x)
+    out = Guarded((h, w, co))
+    d.in_a, d.out = tx.data_ptr(), out.ptr()
+    lib.check(lib.L.dnxcu_launch(C.byref(d), None))
+    y = out.check()
+    assert (y.view(np.uint16) == ref.view(np.uint16)).all()
