@@ -127,35 +127,6 @@ __global__ void pad_channels(const unsigned short *__restrict__ in, uint4 *__res
   }
 }
 
-// The same through shared memory: a block takes 256 consecutive pixels, whose C*512 bytes are contiguous and
-// start on a 16 byte boundary, with 16 byte loads; each thread then builds the 8 channel pieces of its pixel
-// from shared memory.  (The direct form above issues eight scattered 2 byte loads per stored piece.)
-constexpr int kPadTile = 256;
-__global__ void pad_channels_tiled(const unsigned short *__restrict__ in, uint4 *__restrict__ out, long long P, int C,
-                                   int Cp8) {
-  extern __shared__ __align__(16) unsigned short tile[];
-  const long long ntiles = (P + kPadTile - 1) / kPadTile;
-  for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
-    const long long p0 = t * kPadTile;
-    const int npx = (int)min((long long)kPadTile, P - p0);
-    const int nvec = npx * C / 8, ntail = npx * C - nvec * 8;  // whole 16 byte pieces, then single halves
-    const uint4 *src = reinterpret_cast<const uint4 *>(in + p0 * C);
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) reinterpret_cast<uint4 *>(tile)[i] = __ldg(src + i);
-    for (int i = threadIdx.x; i < ntail; i += blockDim.x) tile[nvec * 8 + i] = __ldg(in + p0 * C + nvec * 8 + i);
-    __syncthreads();
-    for (int i = threadIdx.x; i < npx * Cp8; i += blockDim.x) {
-      const int px = i / Cp8, c8 = i - px * Cp8;
-      const unsigned short *sp = tile + px * C + c8 * 8;
-      unsigned int w[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-      for (int e = 0; e < 8; ++e)
-        if (c8 * 8 + e < C) w[e >> 1] |= (unsigned int)sp[e] << ((e & 1) * 16);
-      out[(p0 + px) * Cp8 + c8] = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-    __syncthreads();
-  }
-}
-
 // Spatial pad by edge replication and spatial slice: one thread per output pixel and piece (16 bytes
 // or one channel) of it.  T = uint4 (C % 8 == 0) or unsigned short.
 //   pad:   out[ho][wo] = in[clamp(ho - top, 0, IH - 1)][clamp(wo - left, 0, IW - 1)]   (memory_pad.comp:71-72)
@@ -262,15 +233,8 @@ int mem_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
     if (((uintptr_t)d.out & 15) || ((uintptr_t)d.in_a & 1)) return DNXCU_E_MISALIGNED;
     uint32_t gp[3];
     mem_grid(v, d, gp);
-    const long long P = (long long)H * W;
-    if (d.c_a <= 48 && !((uintptr_t)d.in_a & 15)) {
-      const long long ntiles = (P + kPadTile - 1) / kPadTile;
-      const long long cap = (long long)sm_count_cached() * 4;
-      pad_channels_tiled<<<(unsigned)(ntiles < cap ? ntiles : cap), kThreads, (size_t)kPadTile * d.c_a * 2, s>>>(
-          (const unsigned short *)d.in_a, (uint4 *)d.out, P, d.c_a, d.c_out / 8);
-    } else {
-      pad_channels<<<gp[0], kThreads, 0, s>>>((const unsigned short *)d.in_a, (uint4 *)d.out, P, d.c_a, d.c_out / 8);
-    }
+    pad_channels<<<gp[0], kThreads, 0, s>>>((const unsigned short *)d.in_a, (uint4 *)d.out, (long long)H * W, d.c_a,
+                                            d.c_out / 8);
     DNXCU_CUDA(cudaGetLastError());
     return DNXCU_OK;
   }

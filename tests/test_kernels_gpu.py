@@ -185,8 +185,7 @@ def test_pad_edge_and_slice_bit_exact(case):
 
 @pytest.mark.parametrize("shape", [(7, 37, 9, 16), (16, 16, 3, 8), (33, 129, 9, 16), (5, 11, 67, 72), (3, 700, 12, 16)])
 def test_pad_channels_bit_exact(shape):
-    """copy-transform PAD=8 (HWC with C channels -> HWC with c_out channels, new ones zero), both kernel forms
-    (tiled through shared memory for C <= 48, direct otherwise), pixel counts that are not a multiple of a tile."""
+    """copy-transform PAD=8: HWC with C channels -> HWC with c_out channels, the new ones zero."""
     import ctypes as C
     from gpu_util import Guarded, dev
     h, w, c, co = shape
