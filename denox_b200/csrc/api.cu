@@ -100,6 +100,8 @@ static const Variant kVariants[] = {
     {{23, DNXCU_OP_SLICE, "memory-slice", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_SLICE, 8, 0, 0, 0},
     {{24, DNXCU_OP_SLICE, "memory-slice", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_SLICE, 1, 0, 0, 0},
     {{25, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=1#W=resident#PIPES=1", CONV_ALL, 1, 1, 1, 128, 0}, VK_CONV_TC, 0, 1, 2, 0},
+    {{26, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=2#W=resident#NSPLIT=3", CONV_ALL, 1, 1, 16, 256, 0}, VK_CONV_TC, 0, 2, 0, 3},
+    {{27, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=2#W=resident#NSPLIT=4", CONV_ALL, 1, 1, 16, 256, 0}, VK_CONV_TC, 0, 2, 0, 4},
 };
 static const int kVariantCount = (int)(sizeof(kVariants) / sizeof(kVariants[0]));
 

@@ -222,7 +222,7 @@ void candidate_variants(const FusedOp &op, bool allow_tc, std::vector<int> &out)
   out.clear();
   // preference when no benchmark data exists: tensor core variants first,
   // resident weights before streamed, then the CUDA core fallback; 128-bit before 2-byte.
-  static const int conv_pref[] = {6, 7, 17, 18, 19, 20, 25, 2, 3, 1, 4, 5, 0};
+  static const int conv_pref[] = {6, 7, 17, 18, 19, 26, 20, 27, 25, 2, 3, 1, 4, 5, 0};
   if (op.op == DNXCU_OP_CONV3X3) {
     for (int id : conv_pref) {
       const Variant *v = get_variant(id);
