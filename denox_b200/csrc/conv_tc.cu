@@ -35,6 +35,7 @@
 // and every role leaves its loop; TMEM is freed on that path too.
 #include "internal.h"
 #include <cuda.h>
+#include <mutex>
 #include <stdlib.h>
 #include <string.h>
 
@@ -2175,6 +2176,8 @@ static SideStreams g_side[16];
 
 static int side_streams(int dev, SideStreams **out) {
   if (dev < 0 || dev >= 16) return DNXCU_E_UNSUPPORTED;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
   SideStreams &ss = g_side[dev];
   if (!ss.ready) {
     DNXCU_CUDA(cudaEventCreateWithFlags(&ss.fork, cudaEventDisableTiming));
