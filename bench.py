@@ -357,7 +357,7 @@ def main():
     # DRAM bytes per launch of that kernel from the ncu capture summarised in
     # profiles/conv3x3_tc_stack_upconcat_64_16_to_64_1080p.md (dram__bytes_read.sum + dram__bytes_write.sum); only
     # valid while the dominant dispatch is that shape
-    traffic = 356.4e6 if (dt.c_a, dt.c_b, dt.c_out, dt.h, dt.w) == (64, 16, 64, 1088, 1920) else None
+    traffic = 352.7e6 if (dt.c_a, dt.c_b, dt.c_out, dt.h, dt.w) == (64, 16, 64, 1088, 1920) else None
     roof.update(traffic=traffic, kernel=f"conv3x3_tc {tt['name']} {dt.c_a}+{dt.c_b}->{dt.c_out} @{dt.h}x{dt.w}",
                 peak_source=pk["src"], duration_ms=round(dt.ms, 5), share_of_frame=tt["share"])
     sum_bound_ms = sum(r["roof_ms"] for r in table)
