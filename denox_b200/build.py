@@ -30,7 +30,19 @@ def needs_build():
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False):
+def source_digest():
+    """SHA-256 over the kernel sources and the public header, in a fixed order: becomes part of every variant's
+    identity (dnxcu_variant_sha256), so that a benchmark database never serves timings of other kernel code."""
+    import hashlib
+    h = hashlib.sha256()
+    files = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".h")))
+    for path in files + [os.path.join(ROOT, "include", "dnxcu.h")]:
+        h.update(os.path.basename(path).encode() + b"\0")
+        h.update(open(path, "rb").read())
+    return h.hexdigest()
+
+
+def build(force=False, verbose=False, debug_aids=False):
     if not force and not needs_build():
         return OUT
     objs = []
@@ -41,7 +53,10 @@ def build(force=False, verbose=False):
         "-gencode", "arch=compute_100a,code=sm_100a",
         "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall",
         "-I", os.path.join(ROOT, "include"), "-I", CSRC,
+        f'-DDNXCU_SOURCE_DIGEST="{source_digest()}"',
     ]
+    if debug_aids:  # development only: time line tracing and load / MMA / store switches in the conv kernels
+        common += ["-DDNXCU_DEBUG_AIDS"]
     if verbose:
         common += ["-Xptxas", "-v"]
     procs = []
@@ -66,4 +81,4 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, debug_aids="--debug-aids" in sys.argv))

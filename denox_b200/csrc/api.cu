@@ -3,6 +3,8 @@
 #include "internal.h"
 #include <string.h>
 #include <stdio.h>
+#include <atomic>
+#include <new>
 
 namespace dnxcu {
 
@@ -65,11 +67,23 @@ void sha256_hex(const void *data, size_t n, char out_hex[65]) {
   out_hex[64] = 0;
 }
 
-// ---- variant table ------------------------------------------------------------
-// Bump when a kernel's code changes in a way that invalidates stored timings.
-static const char *kSourceRevision = "dnxcu-kernels-1";
+// ---- bounded waits ------------------------------------------------------------
+namespace {
+constexpr unsigned long long kDefaultWaitCycles = 3000000000ull;  // about 1.5 s
+std::atomic<unsigned long long> g_wait_limit_cycles{kDefaultWaitCycles};
+}  // namespace
+unsigned long long wait_limit_cycles() { return g_wait_limit_cycles.load(std::memory_order_relaxed); }
 
-static const uint32_t CONV_BASE = DNXCU_F_RELU | DNXCU_F_BIAS | DNXCU_F_UP2X_A;
+// ---- variant table ------------------------------------------------------------
+// Digest of the kernel sources this library was built from (the build passes the SHA-256 of csrc/*.cu,
+// csrc/*.h and the public header): part of every variant's identity, so a changed kernel invalidates the
+// timings a benchmark database holds for it.
+#ifndef DNXCU_SOURCE_DIGEST
+#define DNXCU_SOURCE_DIGEST "unversioned-build"
+#endif
+static const char *kSourceRevision = DNXCU_SOURCE_DIGEST;
+
+static const uint32_t CONV_BASE = DNXCU_F_RELU | DNXCU_F_BIAS | DNXCU_F_UP2X_A | DNXCU_F_LEAKY;
 static const uint32_t CONV_ALL = CONV_BASE | DNXCU_F_POOL_OUT | DNXCU_F_NO_FULL_OUT;
 
 static const Variant kVariants[] = {
@@ -88,8 +102,8 @@ static const Variant kVariants[] = {
     {{11, DNXCU_OP_UPSAMPLE2X, "basic-upsample", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_UPSAMPLE, 1, 0, 0, 0},
     {{12, DNXCU_OP_CONCAT, "copy-transform", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_CONCAT, 8, 0, 0, 0},
     {{13, DNXCU_OP_CONCAT, "copy-transform", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_CONCAT, 1, 0, 0, 0},
-    {{14, DNXCU_OP_RELU, "basic-activation", "VEC=8", 0, 0, 8, 1, 0, 0}, VK_RELU, 8, 0, 0, 0},
-    {{15, DNXCU_OP_RELU, "basic-activation", "VEC=1", 0, 0, 1, 1, 0, 0}, VK_RELU, 1, 0, 0, 0},
+    {{14, DNXCU_OP_RELU, "basic-activation", "VEC=8", DNXCU_F_LEAKY, 0, 8, 1, 0, 0}, VK_RELU, 8, 0, 0, 0},
+    {{15, DNXCU_OP_RELU, "basic-activation", "VEC=1", DNXCU_F_LEAKY, 0, 1, 1, 0, 0}, VK_RELU, 1, 0, 0, 0},
     {{16, DNXCU_OP_PAD_CHANNELS, "copy-transform", "PAD=8", 0, 0, 1, 8, 65536, 0}, VK_PADC, 1, 0, 0, 0},
     {{17, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=4#W=resident", CONV_ALL, 1, 1, 1, 128, 0}, VK_CONV_TC, 0, 4, 0, 0},
     {{18, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=2#W=resident#NSPLIT=2", CONV_ALL, 1, 1, 16, 256, 0}, VK_CONV_TC, 0, 2, 0, 2},
@@ -176,6 +190,7 @@ int dnxcu_validate(const dnxcu_dispatch *d) {
   const Variant *v = get_variant(d->variant);
   if (!v) return DNXCU_E_BAD_ARG;
   if (d->flags & ~v->desc.allowed_flags) return DNXCU_E_UNSUPPORTED;
+  if ((d->flags & DNXCU_F_RELU) && (d->flags & DNXCU_F_LEAKY)) return DNXCU_E_BAD_ARG;
   switch (v->kind) {
     case VK_CONV_DIRECT: return conv_direct_validate(*v, *d);
     case VK_CONV_TC: return conv_tc_validate(*v, *d);
@@ -212,12 +227,72 @@ int dnxcu_launch(const dnxcu_dispatch *d, void *stream) {
   const Variant *v = get_variant(d->variant);
   if (!v) return DNXCU_E_BAD_ARG;
   if (d->flags & ~v->desc.allowed_flags) return DNXCU_E_UNSUPPORTED;
+  if ((d->flags & DNXCU_F_RELU) && (d->flags & DNXCU_F_LEAKY)) return DNXCU_E_BAD_ARG;
   cudaStream_t s = (cudaStream_t)stream;
   switch (v->kind) {
     case VK_CONV_DIRECT: return conv_direct_launch(*v, *d, s);
     case VK_CONV_TC: return conv_tc_launch(*v, *d, s);
     default: return mem_launch(*v, *d, s);
   }
+}
+
+int dnxcu_set_wait_limit_us(uint32_t us) {
+  if (us == 0) {
+    g_wait_limit_cycles.store(kDefaultWaitCycles, std::memory_order_relaxed);
+    return DNXCU_OK;
+  }
+  int dev = 0, khz = 0;
+  DNXCU_CUDA(cudaGetDevice(&dev));
+  if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev) != cudaSuccess || khz <= 0) khz = 1965000;
+  g_wait_limit_cycles.store((unsigned long long)us * (unsigned long long)khz / 1000ull, std::memory_order_relaxed);
+  return DNXCU_OK;
+}
+
+}  // extern "C"
+
+// A planned dispatch.  Tensor core convs keep their launch parameters and encoded tensor maps; every other
+// kernel family derives its launch from the dispatch record alone, which is kept as it is.
+struct dnxcu_plan {
+  dnxcu_dispatch d;
+  const Variant *v = nullptr;
+  ConvTcPlan *tc = nullptr;
+};
+
+extern "C" {
+
+int dnxcu_plan_create(const dnxcu_dispatch *d, dnxcu_plan **out) {
+  if (!d || !out) return DNXCU_E_BAD_ARG;
+  int st = dnxcu_validate(d);
+  if (st) return st;
+  dnxcu_plan *p = new (std::nothrow) dnxcu_plan();
+  if (!p) return DNXCU_E_NO_MEMORY;
+  p->d = *d;
+  p->v = get_variant(d->variant);
+  if (p->v->kind == VK_CONV_TC) {
+    st = conv_tc_plan(*p->v, *d, &p->tc);
+    if (st) {
+      delete p;
+      return st;
+    }
+  }
+  *out = p;
+  return DNXCU_OK;
+}
+
+int dnxcu_plan_launch(const dnxcu_plan *p, void *stream) {
+  if (!p || !p->v) return DNXCU_E_BAD_ARG;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (p->v->kind) {
+    case VK_CONV_DIRECT: return conv_direct_launch(*p->v, p->d, s);
+    case VK_CONV_TC: return conv_tc_launch_plan(*p->tc, s);
+    default: return mem_launch(*p->v, p->d, s);
+  }
+}
+
+void dnxcu_plan_destroy(dnxcu_plan *p) {
+  if (!p) return;
+  if (p->tc) conv_tc_plan_free(p->tc);
+  delete p;
 }
 
 int dnxcu_grid(const dnxcu_dispatch *d, uint32_t grid[3]) {

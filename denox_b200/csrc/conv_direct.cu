@@ -32,7 +32,8 @@ struct DirectArgs {
   const __half *bias;
   __half *out;
   int H, W, K, Kp;
-  int relu;
+  int relu;      // 0 none, 1 max(x, 0), 2 max(x, alpha * x) in binary16 on the rounded sum
+  __half alpha;
 };
 
 __global__ void __launch_bounds__(TW *TH) conv3x3_direct(DirectArgs g) {
@@ -109,8 +110,10 @@ __global__ void __launch_bounds__(TW *TH) conv3x3_direct(DirectArgs g) {
   for (int k = 0; k < KT; ++k) {
     if (k0 + k < g.K) {
       float v = acc[k];
-      if (g.relu) v = fmaxf(v, 0.0f);
-      o[k] = __float2half_rn(v);
+      if (g.relu == 1) v = fmaxf(v, 0.0f);
+      __half h = __float2half_rn(v);
+      if (g.relu == 2) h = __hmax(h, __hmul(g.alpha, h));
+      o[k] = h;
     }
   }
 }
@@ -171,7 +174,8 @@ int conv_direct_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s
   g.H = (int)d.pc[1];
   g.K = d.c_out;
   g.Kp = kpad(d.c_out);
-  g.relu = (d.flags & DNXCU_F_RELU) ? 1 : 0;
+  g.relu = (d.flags & DNXCU_F_LEAKY) ? 2 : ((d.flags & DNXCU_F_RELU) ? 1 : 0);
+  g.alpha = __float2half_rn(d.leaky_alpha);
   uint32_t grid[3];
   conv_direct_grid(v, d, grid);
   conv3x3_direct<<<dim3(grid[0], grid[1], grid[2]), TW * TH, 0, s>>>(g);

@@ -35,6 +35,7 @@
 // and every role leaves its loop; TMEM is freed on that path too.
 #include "internal.h"
 #include <cuda.h>
+#include <atomic>
 #include <mutex>
 #include <stdlib.h>
 #include <string.h>
@@ -53,7 +54,6 @@ constexpr int MAX_DEPTH = 8;      // input rows a producer thread keeps in fligh
 constexpr int MAX_WST = 4;
 constexpr int N_PRODUCER = 128;
 constexpr int THREADS = 320;
-constexpr unsigned long long WAIT_LIMIT_CYCLES = 3000000000ull;  // about 1.5 s
 
 // barrier indices inside the header
 constexpr int BAR_FULL = 0;                   // [MAX_SLOTS] slot filled (4 producer warps arrive)
@@ -66,7 +66,7 @@ constexpr int BAR_WRES = BAR_WEMPTY + MAX_WST;    // resident weights landed
 constexpr int BAR_COUNT = BAR_WRES + 1;
 static_assert(BAR_COUNT * 8 + 16 <= HEADER_BYTES, "header too small");
 constexpr int OFF_TMEM_PTR = BAR_COUNT * 8;
-constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
+constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;  // int abort flag, then the 64-bit wait limit
 
 struct Seg {
   const __half *ptr;  // H x W x C (or (H/2) x (W/2) x C when up)
@@ -92,7 +92,9 @@ struct TcArgs {
   int *status;
   int H, W, K, N, Ns;
   int os;  // halves between consecutive pixels of the outputs (= K unless the output channels are split over launches)
-  int relu, pool, full_out;
+  int relu, pool, full_out;  // relu: an activation follows the sum (ReLU, or LeakyReLU when leaky is set)
+  int leaky;                 // the activation is max(x, alpha * x) in binary16
+  uint32_t alpha_h2;         // alpha as a binary16 pair
   int RB, S, nstrips, nunits;
   int wstream, WST;
   int G;                 // K groups: 1 = rolling row window; > 1 = every pass loads its rows once per group
@@ -108,13 +110,33 @@ struct TcArgs {
   int stage_pitch;       // stacked form: bytes per pixel row of an epilogue warp's staging tile, 0 = direct stores
   uint32_t stage_warp_bytes;  // staging bytes per epilogue warp
   uint32_t tmem_cols;
-  int desc_swap;  // debugging aid: exchange the two descriptor strides
-  long long *trace;  // debugging aid: per role time stamps of CTA 0 (nullptr = off)
-  int switch_issue;  // debugging aid: the straight line form is chosen per row even with one K group
   int parts;       // launches of this dispatch that run side by side (output channel split): each plans for 1/parts of the SMs
-  int loop_issue;  // debugging aid: MMAs issued by the generic loops instead of the straight line code
-  int skip;       // debugging aid (timing only, results wrong): 1 no input loads, 2 no MMAs, 4 no output stores
+  unsigned long long wait_limit;  // clock64 ticks after which a barrier wait gives up (see mbar_wait)
+#ifdef DNXCU_DEBUG_AIDS
+  int desc_swap;     // exchange the two descriptor strides
+  long long *trace;  // per role time stamps of CTA 0 (nullptr = off)
+  int switch_issue;  // the straight line form is chosen per row even with one K group
+  int loop_issue;    // MMAs issued by the generic loops instead of the straight line code
+  int skip;          // timing only, results wrong: 1 no input loads, 2 no MMAs, 4 no output stores
+#endif
 };
+
+// Development aids (time line tracing, switching loads / MMAs / stores off for timing experiments) exist only in
+// builds made with -DDNXCU_DEBUG_AIDS.  A normal build compiles them out: the macros below are constants, so no
+// kernel carries the fields or the tests, and nothing reads the environment.
+#ifdef DNXCU_DEBUG_AIDS
+#define DBG_SKIP(g) ((g).skip)
+#define DBG_DESC_SWAP(g) ((g).desc_swap)
+#define DBG_SWITCH_ISSUE(g) ((g).switch_issue)
+#define DBG_LOOP_ISSUE(g) ((g).loop_issue)
+#define DBG_TRACE_ON(g) ((g).trace != nullptr)
+#else
+#define DBG_SKIP(g) 0
+#define DBG_DESC_SWAP(g) 0
+#define DBG_SWITCH_ISSUE(g) 0
+#define DBG_LOOP_ISSUE(g) 0
+#define DBG_TRACE_ON(g) false
+#endif
 
 // ---- PTX wrappers ---------------------------------------------------------
 
@@ -169,7 +191,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 0) {
       if (*abort_flag) return false;
-      if ((unsigned long long)clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      // the limit (clock64 ticks) sits in the header right behind the abort flag, written once at kernel start
+      const unsigned long long limit = *reinterpret_cast<const volatile unsigned long long *>(abort_flag + 1);
+      if ((unsigned long long)clock64() - t0 > limit) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;
@@ -271,10 +295,37 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   return *reinterpret_cast<uint32_t *>(&h);
 }
 
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t hmax2_u32(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+// The activation on a pair of finished, rounded sums: max(x, 0), or max(x, alpha * x) with the product rounded
+// to binary16 (direct_conv_cm.comp:1061-1076).
+__device__ __forceinline__ uint32_t activate_h2(uint32_t p, int leaky, uint32_t alpha_h2) {
+  return leaky ? hmax2_u32(p, hmul2_u32(alpha_h2, p)) : hmax2_u32(p, 0u);
+}
+// The same on one fp32 sum; the result is the binary16 value as a float.
+__device__ __forceinline__ float activate_f(float v, int leaky, uint32_t alpha_h2) {
+  if (!leaky) return fmaxf(v, 0.0f);
+  const __half h = __float2half_rn(v);
+  const __half a = __ushort_as_half((unsigned short)(alpha_h2 & 0xffffu));
+  return __half2float(__hmax(h, __hmul(a, h)));
+}
+
 // Debug time line: role `role` of CTA 0 stores clock64() at event `ev` of its n-th iteration.
 constexpr int TRACE_ITERS = 64, TRACE_EVENTS = 6;
 __device__ __forceinline__ void trace(const TcArgs &g, int role, int n, int ev) {
+#ifdef DNXCU_DEBUG_AIDS
   if (g.trace && blockIdx.x == 0 && n < TRACE_ITERS) g.trace[(role * TRACE_ITERS + n) * TRACE_EVENTS + ev] = clock64();
+#else
+  (void)g; (void)role; (void)n; (void)ev;
+#endif
 }
 
 struct Unit {
@@ -421,7 +472,7 @@ __device__ __forceinline__ void epilogue_block(const TcArgs &g, uint32_t t0, uin
   __half *o0 = g.out + ((long long)y * g.W + x) * g.K + c0;
   __half *o1 = o0 + (long long)g.W * g.K;
   __half *op = g.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (x >> 1)) * g.K + c0;
-  const bool st_full = g.full_out && xin && !(g.skip & 4);
+  const bool st_full = g.full_out && xin && !(DBG_SKIP(g) & 4);
   const bool st_pool = do_pool && xin && !(lane & 1) && row1;
 #pragma unroll
   for (int j8 = 0; j8 < NC; j8 += 8) {
@@ -431,10 +482,10 @@ __device__ __forceinline__ void epilogue_block(const TcArgs &g, uint32_t t0, uin
       float bj = 0.0f;
       if (g.bias && c0 + j8 + j < g.K) bj = __half2float(__ldg(g.bias + c0 + j8 + j));
       f0[j] = __uint_as_float(v0[j8 + j]) + bj;
-      if (g.relu) f0[j] = fmaxf(f0[j], 0.0f);
+      if (g.relu) f0[j] = activate_f(f0[j], g.leaky, g.alpha_h2);
       if constexpr (RSTEP == 2) {
         f1[j] = __uint_as_float(v1[j8 + j]) + bj;
-        if (g.relu) f1[j] = fmaxf(f1[j], 0.0f);
+        if (g.relu) f1[j] = activate_f(f1[j], g.leaky, g.alpha_h2);
       } else {
         f1[j] = 0.0f;
       }
@@ -497,6 +548,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    *reinterpret_cast<volatile unsigned long long *>(abort_flag + 1) = g.wait_limit;
     // a slot is full when the TMA bytes have landed (one arrival with the byte count by the
     // issuing thread) and, when producer warps copy part of the rows, those four warps arrived
     const uint32_t full_count = g.cpa ? 5u : 1u;
@@ -538,10 +590,10 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
     // uniform registers); lane 0 alone issues the tcgen05 instructions.
     const bool issuer = lane == 0;
     const uint32_t idesc = (1u << 4) | ((uint32_t)(g.N >> 3) << 17) | ((uint32_t)(STRIP >> 4) << 24);
-    const uint32_t a_lbo = g.desc_swap ? 128u : (uint32_t)CHUNK_PITCH;
-    const uint32_t a_sbo = g.desc_swap ? (uint32_t)CHUNK_PITCH : 128u;
-    const uint32_t b_lbo = g.desc_swap ? 128u : (uint32_t)g.N * 16u;
-    const uint32_t b_sbo = g.desc_swap ? (uint32_t)g.N * 16u : 128u;
+    const uint32_t a_lbo = DBG_DESC_SWAP(g) ? 128u : (uint32_t)CHUNK_PITCH;
+    const uint32_t a_sbo = DBG_DESC_SWAP(g) ? (uint32_t)CHUNK_PITCH : 128u;
+    const uint32_t b_lbo = DBG_DESC_SWAP(g) ? 128u : (uint32_t)g.N * 16u;
+    const uint32_t b_sbo = DBG_DESC_SWAP(g) ? (uint32_t)g.N * 16u : 128u;
     // descriptor = hi word (stride offset + version, constant) : lo word (start address + leading offset)
     const uint32_t a_hi = (a_sbo >> 4) | (1u << 14), b_hi = (b_sbo >> 4) | (1u << 14);
     const uint32_t a_lo0 = (a_lbo >> 4) << 16, b_lo0 = (b_lbo >> 4) << 16;
@@ -607,7 +659,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
             uint32_t acc = (gi | tap) == 0 ? 0u : 1u;
 #pragma unroll 1
             for (int kc = 0; kc < nk16; ++kc) {
-              if (issuer && !(g.skip & 2)) {
+              if (issuer && !(DBG_SKIP(g) & 2)) {
                 const uint64_t bdesc = ((uint64_t)b_hi << 32) | b_lo;
 #pragma unroll
                 for (int r = 0; r < R; ++r)
@@ -738,7 +790,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
       if (tid == 0) {
         const uint32_t fb = bar(BAR_FULL + slot);
         // announce the byte count first, then start the copies
-        const uint32_t bytes = (g.skip & 1) ? 0u : tma_row<false>(g, slot_addr, iy, x0, c_lo, c_hi, fb);
+        const uint32_t bytes = (DBG_SKIP(g) & 1) ? 0u : tma_row<false>(g, slot_addr, iy, x0, c_lo, c_hi, fb);
         if (bytes) {
           mbar_expect_tx(fb, bytes);
           tma_row<true>(g, slot_addr, iy, x0, c_lo, c_hi, fb);
@@ -747,7 +799,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
         }
       }
       if (g.cpa) {
-        if (!(g.skip & 1)) load_row(g, slot_addr, iy, x0, tid, N_PRODUCER, c_lo, c_hi);
+        if (!(DBG_SKIP(g) & 1)) load_row(g, slot_addr, iy, x0, tid, N_PRODUCER, c_lo, c_hi);
         cp_async_commit();
         if (tid == 0) trace(g, 2, pos, 2);
         ++pos;
@@ -803,12 +855,6 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
 // ReLU and the 2x2 max then work on packed pairs (max commutes with the rounding).
 constexpr int EPI_BIAS = 1, EPI_RELU = 2, EPI_POOL = 4, EPI_FULL = 8;
 
-__device__ __forceinline__ uint32_t hmax2_u32(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-
 template <int NC, int EPI>
 __device__ __forceinline__ void round_row(const TcArgs &g, const uint32_t (&v)[NC], int c0, uint32_t (&h)[NC / 2]) {
 #pragma unroll
@@ -819,7 +865,7 @@ __device__ __forceinline__ void round_row(const TcArgs &g, const uint32_t (&v)[N
       hi += (c0 + j + 1 < g.K) ? __half2float(__ldg(g.bias + c0 + j + 1)) : 0.0f;
     }
     uint32_t p = pack_h2(lo, hi);
-    if (EPI & EPI_RELU) p = hmax2_u32(p, 0u);
+    if (EPI & EPI_RELU) p = activate_h2(p, g.leaky, g.alpha_h2);
     h[j / 2] = p;
   }
 }
@@ -854,8 +900,8 @@ __device__ __forceinline__ void epi_fast(const TcArgs &g, uint32_t t0, uint32_t 
     if constexpr (RSTEP == 2) tc_ld16(t1 + (uint32_t)c0, v1);
   }
   tc_wait_ld();
-  if (g.skip & 16) return;
-  if (g.skip & 4) xin = false;
+  if (DBG_SKIP(g) & 16) return;
+  if (DBG_SKIP(g) & 4) xin = false;
   uint32_t h0[NC / 2], h1[RSTEP == 2 ? NC / 2 : 1];
   round_row<NC, EPI>(g, v0, c0, h0);
   if constexpr (RSTEP == 2) round_row<NC, EPI>(g, v1, c0, h1);
@@ -1079,7 +1125,10 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
 
   if (warp == 2) {
     // barrier set-up by a whole warp (one barrier per lane and round) while warp 0 allocates tensor memory
-    if (lane == 0) *abort_flag = 0;
+    if (lane == 0) {
+      *abort_flag = 0;
+      *reinterpret_cast<volatile unsigned long long *>(abort_flag + 1) = g.wait_limit;
+    }
     // who completes a slot: the TMA bytes alone; or TMA bytes + the producer warps' cp.async part; or, in expand
     // mode, the producer warps alone after they have expanded the TMA data that landed on the raw barrier;
     // plus, always, the descriptor thread
@@ -1155,7 +1204,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     uint32_t bytes = 0;
     if (a_tma) bytes += (uint32_t)(a_hi - a_lo) * SRC_PITCH;
     if (b_tma) bytes += (uint32_t)max(0, c_hi - max(c_lo, nca)) * CHUNK_PITCH;
-    if (g.skip & 1) bytes = 0;
+    if (DBG_SKIP(g) & 1) bytes = 0;
     if (bytes) {
       mbar_expect_tx(rb, bytes);
       if (a_tma)
@@ -1190,7 +1239,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     const uint32_t a_hi = (128u >> 4) | (1u << 14), b_hi = a_hi;
     const uint32_t kstep_a = (2u * CHUNK_PITCH) >> 4, kstep_b = 2u * 3u * N;
     bool ok = mbar_wait(bar(ST_BAR_WRES), 0, abort_flag, g.status, 1);
-    const bool tr = g.trace != nullptr && blockIdx.x == 0 && lane == 0 && pipe == 0;
+    const bool tr = DBG_TRACE_ON(g) && blockIdx.x == 0 && lane == 0 && pipe == 0;
     auto mma1 = [&](uint32_t d, uint32_t alo, uint32_t blo, uint32_t idesc, uint32_t acc) {
       tc_mma(d, ((uint64_t)a_hi << 32) | alo, ((uint64_t)b_hi << 32) | blo, idesc, acc);
     };
@@ -1208,7 +1257,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         const uint4 q0 = lds16(da), q1 = lds16(da + 16), q2 = lds16(da + 32);
         const uint32_t flags = q0.z;
         tc_fence_after();
-        if (!(g.skip & 2)) {
+        if (!(DBG_SKIP(g) & 2)) {
           const uint32_t row_lo = q0.x, b_lo = q0.y;
           const Run R0 = {q1.x, q1.y, q1.z, 1u}, R1 = {q1.w, q2.x, q2.y, 1u};
           if constexpr (NK > 0) {
@@ -1217,7 +1266,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           } else {
             const int nk16 = (int)(flags & 15u);
             bool done = false;
-            if (!g.loop_issue)
+            if (!DBG_LOOP_ISSUE(g))
               done = (flags & DF_NR2) ? st_issue_nk<2>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1)
                                       : st_issue_nk<1>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0);
             if (!done) {
@@ -1245,7 +1294,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
       }
     };
     if (lane == 0 && ok && (int)blockIdx.x * P + pipe < g.nunits) {
-      bool same = !g.loop_issue && !g.switch_issue;
+      bool same = !DBG_LOOP_ISSUE(g) && !DBG_SWITCH_ISSUE(g);
       for (int gi = 1; gi < g.G; ++gi) same = same && g.gch[gi] == g.gch[0];
       const int nkfix = same ? (g.gch[0] >> 1) : 0;
       switch (nkfix) {
@@ -1269,7 +1318,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     const int q = warp & 3;
     const int m = q * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    const bool tr = g.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64;
+    const bool tr = DBG_TRACE_ON(g) && blockIdx.x == 0 && threadIdx.x == 64;
     const int pitch = g.stage_pitch;  // 0: no staging tile, direct stores
     const int nck = g.K >> 3;
     const int os8 = g.os >> 3;  // output pixel stride in 16 byte units (= nck unless the output channels are split)
@@ -1315,7 +1364,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           const int xw = t.x0 + q * 32;                      // first pixel of this warp
           const int npx = max(0, min(32, g.W - xw));        // pixels of this warp inside the image
           const bool pool2 = (EPI & EPI_POOL) && nrows == 2;
-          if (!(g.skip & 8)) {
+          if (!(DBG_SKIP(g) & 8)) {
             for (int r = 0; r < nrows; ++r) {
               const uint32_t tr_addr = r ? t1 : t0;
               const uint32_t tile = (pool2 && r) ? tile1 : tile0;
@@ -1337,13 +1386,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
                 __syncwarp();
               }
               if (!pool2) {
-                if ((EPI & EPI_FULL) && !(g.skip & 4))
+                if ((EPI & EPI_FULL) && !(DBG_SKIP(g) & 4))
                   copy_out(tile, pitch, nck, os8, npx, g.out + ((long long)(y + r) * g.W + xw) * g.os, lane);
                 __syncwarp();
               }
             }
             if (pool2) {
-              if (!(g.skip & 4)) {
+              if (!(DBG_SKIP(g) & 4)) {
                 if (EPI & EPI_FULL) {
                   copy_out(tile0, pitch, nck, os8, npx, g.out + ((long long)y * g.W + xw) * g.os, lane);
                   copy_out(tile1, pitch, nck, os8, npx, g.out + ((long long)(y + 1) * g.W + xw) * g.os, lane);
@@ -1366,7 +1415,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           if (tr) trace(g, 1, item >> 1, 2);
           continue;
         }
-        int c0 = (g.skip & 8) ? N : 0;
+        int c0 = (DBG_SKIP(g) & 8) ? N : 0;
         if (nrows == 2) {
 #pragma unroll 1
           for (; c0 + 32 <= N; c0 += 32) epi_fast<32, 2, EPI>(g, t0, t1, c0, x, y, xin, lane);
@@ -1402,7 +1451,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         int slot = 0, pcount = 0;
         uint32_t phase = 1;  // parity to wait for on the empty barrier: first round passes
         const int nca = g.a.nch;
-        const bool tr = g.trace != nullptr && blockIdx.x == 0 && pipe == 0;
+        const bool tr = DBG_TRACE_ON(g) && blockIdx.x == 0 && pipe == 0;
         for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
           const StUnit t = st_unit_of(g, u);
           for (int jj = 0; ok && jj < t.rows_out + 2; ++jj) {
@@ -1416,7 +1465,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
               const uint32_t fb = bar(ST_BAR_FULL + bofs + slot);
               const int c_lo = g.gc0[gi], c_hi = c_lo + g.gch[gi];
               mbar_expect_tx(fb, (uint32_t)g.gch[gi] * CHUNK_PITCH);
-              if (!(g.skip & 1)) {
+              if (!(DBG_SKIP(g) & 1)) {
                 for (int c = c_lo; c < min(c_hi, nca); c += g.a.tbox)
                   tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, t.x0 - 1, c, iy, fb);
                 for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
@@ -1490,12 +1539,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           if (tid == 32 && pipe == 0) trace(g, 2, xcount, 1);
           // rows TMA does not cover (halo rows of a row band) come the old way; the raw barrier has completed,
           // so the slot is free (thread 0 waited for that before it armed the barrier)
-          if (!(g.skip & 1) && (!a_tma || (g.b.nch > 0 && !b_tma))) {
+          if (!(DBG_SKIP(g) & 1) && (!a_tma || (g.b.nch > 0 && !b_tma))) {
             load_row(g, slot_addr, iy, ex.t.x0, tid, nprod, c_lo, c_hi);
             cp_async_commit();
             cp_async_wait<0>();
           }
-          if (a_tma && !(g.skip & 1)) {
+          if (a_tma && !(DBG_SKIP(g) & 1)) {
             // In place, one pair of chunks at a time: the copy left the pair's two half resolution rows packed
             // (2 x 72 pixels) at the start of the pair's 2 x 132 pixel area.  Every thread first loads the
             // sources of its pixels, then all producer threads of the pipeline meet, then they store.
@@ -1550,7 +1599,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
             const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes;
             if (tid == 0) {
               const uint32_t fb = bar(ST_BAR_FULL + bofs + slot);
-              const uint32_t bytes = (g.skip & 1) ? 0u : tma_row<false>(g, slot_addr, iy, t.x0, c_lo, c_hi, fb);
+              const uint32_t bytes = (DBG_SKIP(g) & 1) ? 0u : tma_row<false>(g, slot_addr, iy, t.x0, c_lo, c_hi, fb);
               if (bytes) {
                 mbar_expect_tx(fb, bytes);
                 tma_row<true>(g, slot_addr, iy, t.x0, c_lo, c_hi, fb);
@@ -1558,7 +1607,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
                 mbar_arrive(fb);
               }
             }
-            if (!(g.skip & 1)) load_row(g, slot_addr, iy, t.x0, tid, nprod, c_lo, c_hi);
+            if (!(DBG_SKIP(g) & 1)) load_row(g, slot_addr, iy, t.x0, tid, nprod, c_lo, c_hi);
             cp_async_commit();
             ++pos;
             if (pos - signalled >= D) {
@@ -1688,6 +1737,16 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
 
 // ---- host side --------------------------------------------------------------
 
+#ifdef DNXCU_DEBUG_AIDS
+long long *g_trace_buffer = nullptr;
+inline bool dbg_env(const char *name) {
+  const char *v = getenv(name);
+  return v && v[0] == '1';
+}
+#else
+inline bool dbg_env(const char *) { return false; }
+#endif
+
 inline int pad16(int c) { return (c + 15) / 16 * 16; }
 inline int nch_of(int c) { return c > 0 ? pad16(c) / 8 : 0; }
 
@@ -1700,12 +1759,17 @@ struct Plan {
 
 constexpr size_t SMEM_LIMIT = 232448;  // 227 KB opt-in per block on sm_100
 
+// SM count of the current device (cached per device; the first query of each device may race with another
+// thread's, both then store the same value).
 int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const bool cacheable = dev >= 0 && dev < 64;
+  int n = cacheable ? cache[dev].load(std::memory_order_relaxed) : 0;
+  if (n <= 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    if (cacheable) cache[dev].store(n, std::memory_order_relaxed);
   }
   return n;
 }
@@ -1715,16 +1779,15 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn encode_fn() {
+  static std::once_flag once;
   static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  std::call_once(once, [] {
     void *p = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
         q == cudaDriverEntryPointSuccess)
       fn = (EncodeTiledFn)p;
-  }
+  });
   return fn;
 }
 
@@ -1777,12 +1840,8 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   // Shared memory budget.  Wanted, in this order of importance: four input slots; the epilogue staging tiles
   // (4 warps per pipeline x 32 pixels x (K*2 + 16) bytes, two rows when pooling); expand mode for an upsampled
   // operand a (TMA at half resolution + one staging buffer per slot); a second pipeline (eight slots).
-  const char *noxp = getenv("DNXCU_TC_NO_EXPAND");
-  const char *notma = getenv("DNXCU_TC_NO_TMA");
-  const char *nost = getenv("DNXCU_TC_NO_STAGE");
-  const char *np = getenv("DNXCU_TC_PIPES");
-  const bool xp_possible = g.a.up && (g.a.C % 8) == 0 && (g.b.nch == 0 || g.b.tma) && !(noxp && noxp[0] == '1') &&
-                           !(notma && notma[0] == '1');
+  const bool xp_possible = g.a.up && (g.a.C % 8) == 0 && (g.b.nch == 0 || g.b.tma) && !dbg_env("DNXCU_TC_NO_EXPAND") &&
+                           !dbg_env("DNXCU_TC_NO_TMA");
   uint32_t xp_src_bytes = 0;
   if (xp_possible) {
     int amax = 0;
@@ -1794,13 +1853,13 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
     xp_src_bytes = 0;  // the half resolution rows land in the slot itself and are expanded in place
     (void)amax;
   }
-  const bool stage_possible = g.K % 8 == 0 && !(nost && nost[0] == '1');
+  const bool stage_possible = g.K % 8 == 0 && !dbg_env("DNXCU_TC_NO_STAGE");
   const size_t stage_pitch = (size_t)g.K * 2 + 16;
   const size_t stage_per_warp = (g.pool ? 2 : 1) * 32 * stage_pitch;
   const size_t base_bytes = ST_HEADER_BYTES + wregion;
   const size_t plain_slot = (size_t)g.gmax * CHUNK_PITCH;
   // v.p2 == 2 ("PIPES=1"): one pipeline with a longer slot ring even where two would fit
-  const bool p2_possible = 4 * g.N <= 256 && !(np && np[0] == '1') && v.p2 != 2;
+  const bool p2_possible = 4 * g.N <= 256 && !dbg_env("DNXCU_TC_PIPES") && v.p2 != 2;
   // candidate configurations, best first: (pipelines, expand, staging)
   int P = 0;
   size_t slot_bytes = 0, stage_total = 0;
@@ -1907,8 +1966,7 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   g.a = {(const __half *)d.in_a, (const __half *)d.halo[0], (const __half *)d.halo[1], d.c_a, nch_of(d.c_a), up ? 1 : 0, 0, 2};
   g.b = {(const __half *)d.in_b, (const __half *)d.halo[2], (const __half *)d.halo[3], d.c_b, nch_of(d.c_b), 0, 0, 2};
   // TMA takes the operands whose pixels are whole 16 byte chunks at full resolution
-  const char *notma = getenv("DNXCU_TC_NO_TMA");
-  const bool allow_tma = !(notma && notma[0] == '1');
+  const bool allow_tma = !dbg_env("DNXCU_TC_NO_TMA");
   g.a.tma = allow_tma && !up && (d.c_a % 8 == 0);
   g.b.tma = allow_tma && d.c_b > 0 && (d.c_b % 8 == 0);
   g.cpa = (!g.a.tma || (d.c_b > 0 && !g.b.tma) || d.halo[0] || d.halo[1] || d.halo[2] || d.halo[3]) ? 1 : 0;
@@ -1923,24 +1981,28 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   g.os = os_override ? os_override : d.c_out;
   g.N = pad16(d.c_out);
   g.Ns = (g.N + 31) / 32 * 32;
-  g.relu = (d.flags & DNXCU_F_RELU) ? 1 : 0;
+  g.relu = (d.flags & (DNXCU_F_RELU | DNXCU_F_LEAKY)) ? 1 : 0;
+  g.leaky = (d.flags & DNXCU_F_LEAKY) ? 1 : 0;
+  {
+    const uint32_t ah = __half_as_ushort(__float2half_rn(d.leaky_alpha));
+    g.alpha_h2 = ah | (ah << 16);
+  }
   g.pool = pool ? 1 : 0;
   g.full_out = full ? 1 : 0;
   g.wstream = v.p2 == 1 ? 1 : 0;
   g.parts = parts;
   g.WST = v.p3 > 0 ? v.p3 : 2;
   if (g.WST > MAX_WST) g.WST = MAX_WST;
-  const char *sw = getenv("DNXCU_TC_DESC_SWAP");
-  g.desc_swap = (sw && sw[0] == '1') ? 1 : 0;
+  g.wait_limit = wait_limit_cycles();
+#ifdef DNXCU_DEBUG_AIDS
+  g.desc_swap = dbg_env("DNXCU_TC_DESC_SWAP") ? 1 : 0;
   const char *sk = getenv("DNXCU_TC_SKIP");
   g.skip = sk ? atoi(sk) : 0;
-  const char *si = getenv("DNXCU_TC_SWITCH_ISSUE");
-  g.switch_issue = (si && si[0] == '1') ? 1 : 0;
-  const char *li = getenv("DNXCU_TC_LOOP_ISSUE");
-  g.loop_issue = (li && li[0] == '1') ? 1 : 0;
-  // time line tracing: the caller's status buffer must then hold 8 + 3*64*6 64-bit words
-  const char *tr = getenv("DNXCU_TC_TRACE");
-  g.trace = (tr && tr[0] == '1' && d.device_status) ? reinterpret_cast<long long *>(d.device_status) + 8 : nullptr;
+  g.switch_issue = dbg_env("DNXCU_TC_SWITCH_ISSUE") ? 1 : 0;
+  g.loop_issue = dbg_env("DNXCU_TC_LOOP_ISSUE") ? 1 : 0;
+  // time line tracing writes to a buffer of its own, handed over by dnxcu_debug_trace_buffer (size checked there)
+  g.trace = dbg_env("DNXCU_TC_TRACE") ? g_trace_buffer : nullptr;
+#endif
 
   if (R == 0) return make_plan_stack(v, d, pl, encode);
   uint32_t cols = 2u * R * g.Ns;
@@ -2014,31 +2076,34 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   return DNXCU_OK;
 }
 
-template <int R>
-int launch_r(const Plan &pl, cudaStream_t s) {
-  static bool attr_done[16] = {};
+// Raises the kernel's dynamic shared memory limit once per device (under a lock: callers on several threads).
+template <class K>
+int ensure_smem_attr(K kernel, std::atomic<bool> (&done)[64]) {
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 16 && !attr_done[dev]) {
-    DNXCU_CUDA(cudaFuncSetAttribute(conv3x3_tc<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
-    attr_done[dev] = true;
-  } else if (dev >= 16) {
-    DNXCU_CUDA(cudaFuncSetAttribute(conv3x3_tc<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
-  }
+  DNXCU_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && done[dev].load(std::memory_order_acquire)) return DNXCU_OK;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  DNXCU_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
+  if (dev >= 0 && dev < 64) done[dev].store(true, std::memory_order_release);
+  return DNXCU_OK;
+}
+
+template <int R>
+int launch_r(const Plan &pl, cudaStream_t s, bool attr_only = false) {
+  static std::atomic<bool> done[64];
+  int st = ensure_smem_attr(conv3x3_tc<R>, done);
+  if (st || attr_only) return st;
   conv3x3_tc<R><<<pl.grid, THREADS, pl.smem, s>>>(pl.args);
   DNXCU_CUDA(cudaGetLastError());
   return DNXCU_OK;
 }
 
 template <int EPI>
-int launch_stack_epi(const Plan &pl, cudaStream_t s) {
-  static bool attr_done[16] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 16 || !attr_done[dev]) {
-    DNXCU_CUDA(cudaFuncSetAttribute(conv3x3_tc_stack<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
-    if (dev < 16) attr_done[dev] = true;
-  }
+int launch_stack_epi(const Plan &pl, cudaStream_t s, bool attr_only = false) {
+  static std::atomic<bool> done[64];
+  int st = ensure_smem_attr(conv3x3_tc_stack<EPI>, done);
+  if (st || attr_only) return st;
   conv3x3_tc_stack<EPI><<<pl.grid, ST_THREADS, pl.smem, s>>>(pl.args);
   DNXCU_CUDA(cudaGetLastError());
   return DNXCU_OK;
@@ -2164,21 +2229,76 @@ void conv_tc_grid(const Variant &v, const dnxcu_dispatch &d, uint32_t g[3]) {
   g[2] = (uint32_t)n;  // launches
 }
 
+// A dispatch planned once: launch parameters and encoded tensor maps of every part (one part unless the
+// output channels are split).  Valid for the pointers and the shape it was made from.
+struct ConvTcPlan {
+  int n = 0;
+  Plan part[8];
+};
+
+int conv_tc_plan(const Variant &v, const dnxcu_dispatch &d, ConvTcPlan **out) {
+  if (d.c_out <= 0 || !out) return DNXCU_E_BAD_ARG;
+  int k0[8], kp[8];
+  const int n = split_parts(v, d.c_out, k0, kp);
+  if (n > 1 && d.c_out % 16) return DNXCU_E_UNSUPPORTED;
+  ConvTcPlan *cp = new (std::nothrow) ConvTcPlan();
+  if (!cp) return DNXCU_E_NO_MEMORY;
+  cp->n = n;
+  size_t woff = 0;
+  for (int p = 0; p < n; ++p) {
+    const dnxcu_dispatch dp = n == 1 ? d : part_dispatch(d, k0[p], kp[p], woff);
+    int st = make_plan(v, dp, cp->part[p], true, n == 1 ? 0 : d.c_out, n);
+    if (!st && n > 1 && cp->part[p].R != 0) st = DNXCU_E_UNSUPPORTED;
+    if (st) {
+      delete cp;
+      return st;
+    }
+    woff += (size_t)9 * (nch_of(d.c_a) + nch_of(d.c_b)) * pad16(kp[p]) * 16;
+  }
+  *out = cp;
+  return DNXCU_OK;
+}
+
+void conv_tc_plan_free(ConvTcPlan *p) { delete p; }
+
+namespace {
+
+int launch_part(const Plan &pl, cudaStream_t s) {
+  switch (pl.R) {
+    case 0: return launch_stack(pl, s);
+    case 1: return launch_r<1>(pl, s);
+    case 2: return launch_r<2>(pl, s);
+    case 4: return launch_r<4>(pl, s);
+    default: return DNXCU_E_UNSUPPORTED;
+  }
+}
+
 // Side streams for the launches of an output channel split: the parts are independent, each plans for its share
 // of the SMs, and they run side by side between a fork and a join on the caller's stream (inside a stream
-// capture this becomes parallel branches of the graph).  Created on first use, per device.
+// capture this becomes parallel branches of the graph).  Every host thread has its own set per device, created
+// on first use: two threads that launch split dispatches at the same time, or one that captures while another
+// launches, never share a fork event or a side stream.
 struct SideStreams {
   cudaStream_t stream[8] = {};
   cudaEvent_t fork = nullptr, join[8] = {};
   bool ready = false;
+  ~SideStreams() {
+    if (!ready) return;
+    // at thread exit; errors (the context may be gone already) are of no interest here
+    for (int i = 1; i < 8; ++i) {
+      if (stream[i]) cudaStreamDestroy(stream[i]);
+      if (join[i]) cudaEventDestroy(join[i]);
+    }
+    if (fork) cudaEventDestroy(fork);
+    cudaGetLastError();
+  }
 };
-static SideStreams g_side[16];
+constexpr int kSideDevices = 16;
 
-static int side_streams(int dev, SideStreams **out) {
-  if (dev < 0 || dev >= 16) return DNXCU_E_UNSUPPORTED;
-  static std::mutex mu;
-  std::lock_guard<std::mutex> lock(mu);
-  SideStreams &ss = g_side[dev];
+int side_streams(int dev, SideStreams **out) {
+  static thread_local SideStreams t_side[kSideDevices];
+  if (dev < 0 || dev >= kSideDevices) return DNXCU_E_UNSUPPORTED;
+  SideStreams &ss = t_side[dev];
   if (!ss.ready) {
     DNXCU_CUDA(cudaEventCreateWithFlags(&ss.fork, cudaEventDisableTiming));
     for (int i = 1; i < 8; ++i) {
@@ -2191,58 +2311,64 @@ static int side_streams(int dev, SideStreams **out) {
   return DNXCU_OK;
 }
 
-int conv_tc_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
-  if (d.c_out <= 0) return DNXCU_E_BAD_ARG;
-  int k0[8], kp[8];
-  const int n = split_parts(v, d.c_out, k0, kp);
-  if (n > 1 && d.c_out % 16) return DNXCU_E_UNSUPPORTED;
+}  // namespace
+
+int conv_tc_launch_plan(const ConvTcPlan &cp, cudaStream_t s) {
+  const int n = cp.n;
+  if (n == 1) return launch_part(cp.part[0], s);
   SideStreams *ss = nullptr;
-  if (n > 1) {
-    int dev = 0;
-    DNXCU_CUDA(cudaGetDevice(&dev));
-    int st = side_streams(dev, &ss);
-    if (st) return st;
-    // plans first: nothing may fail between the fork and the join
-    size_t woff = 0;
-    for (int p = 0; p < n; ++p) {
-      Plan pl;
-      const dnxcu_dispatch dp = part_dispatch(d, k0[p], kp[p], woff);
-      st = make_plan(v, dp, pl, false, d.c_out, n);
-      if (st) return st;
-      if (pl.R != 0) return DNXCU_E_UNSUPPORTED;
-      woff += (size_t)9 * (nch_of(d.c_a) + nch_of(d.c_b)) * pad16(kp[p]) * 16;
-    }
-    DNXCU_CUDA(cudaEventRecord(ss->fork, s));
-    for (int p = 1; p < n; ++p) DNXCU_CUDA(cudaStreamWaitEvent(ss->stream[p], ss->fork, 0));
-  }
-  size_t woff = 0;
+  int dev = 0;
+  DNXCU_CUDA(cudaGetDevice(&dev));
+  int st = side_streams(dev, &ss);
+  if (st) return st;
+  // nothing below may fail between the fork and the join except the launches themselves
+  DNXCU_CUDA(cudaEventRecord(ss->fork, s));
+  for (int p = 1; p < n; ++p) DNXCU_CUDA(cudaStreamWaitEvent(ss->stream[p], ss->fork, 0));
   int result = DNXCU_OK;
   for (int p = 0; p < n; ++p) {
-    Plan pl;
-    const dnxcu_dispatch dp = n == 1 ? d : part_dispatch(d, k0[p], kp[p], woff);
-    cudaStream_t sp = (n > 1 && p > 0) ? ss->stream[p] : s;
-    int st = make_plan(v, dp, pl, true, n == 1 ? 0 : d.c_out, n);
-    if (!st) {
-      switch (pl.R) {
-        case 0: st = launch_stack(pl, sp); break;
-        case 1: st = launch_r<1>(pl, sp); break;
-        case 2: st = launch_r<2>(pl, sp); break;
-        case 4: st = launch_r<4>(pl, sp); break;
-        default: st = DNXCU_E_UNSUPPORTED; break;
-      }
-    }
+    st = launch_part(cp.part[p], p > 0 ? ss->stream[p] : s);
     if (st && !result) result = st;
-    if (st && n == 1) return st;
-    woff += (size_t)9 * (nch_of(d.c_a) + nch_of(d.c_b)) * pad16(kp[p]) * 16;
   }
-  if (n > 1) {
-    // the join is made even after a failed launch, so that the side streams never stay forked
-    for (int p = 1; p < n; ++p) {
-      cudaEventRecord(ss->join[p], ss->stream[p]);
-      cudaStreamWaitEvent(s, ss->join[p], 0);
-    }
+  // the join is made even after a failed launch, so that the side streams never stay forked
+  for (int p = 1; p < n; ++p) {
+    cudaEventRecord(ss->join[p], ss->stream[p]);
+    cudaStreamWaitEvent(s, ss->join[p], 0);
   }
   return result;
 }
+
+int conv_tc_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
+  ConvTcPlan *cp = nullptr;
+  int st = conv_tc_plan(v, d, &cp);
+  if (st) return st;
+  st = conv_tc_launch_plan(*cp, s);
+  conv_tc_plan_free(cp);
+  return st;
+}
+
+// One-time set-up of every kernel of this file on the current device (the dynamic shared memory limits), so that
+// no launch has to do it later, e.g. inside a stream capture.
+int conv_tc_init_device() {
+  Plan none;
+  memset(&none, 0, sizeof(none));
+  int st = launch_r<1>(none, nullptr, true);
+  if (!st) st = launch_r<2>(none, nullptr, true);
+  if (!st) st = launch_r<4>(none, nullptr, true);
+#define DNXCU_EPI_INIT(E) if (!st) st = launch_stack_epi<E>(none, nullptr, true);
+  DNXCU_EPI_INIT(4) DNXCU_EPI_INIT(5) DNXCU_EPI_INIT(6) DNXCU_EPI_INIT(7)
+  DNXCU_EPI_INIT(8) DNXCU_EPI_INIT(9) DNXCU_EPI_INIT(10) DNXCU_EPI_INIT(11)
+  DNXCU_EPI_INIT(12) DNXCU_EPI_INIT(13) DNXCU_EPI_INIT(14) DNXCU_EPI_INIT(15)
+#undef DNXCU_EPI_INIT
+  return st;
+}
+
+#ifdef DNXCU_DEBUG_AIDS
+int conv_tc_debug_trace_buffer(void *device_buffer, size_t bytes) {
+  const size_t need = (size_t)3 * TRACE_ITERS * TRACE_EVENTS * sizeof(long long);
+  if (device_buffer && bytes < need) return DNXCU_E_BAD_ARG;
+  g_trace_buffer = (long long *)device_buffer;
+  return DNXCU_OK;
+}
+#endif
 
 }  // namespace dnxcu

@@ -223,9 +223,17 @@ int dnxcu_db_atomic_writeback(dnxcu_db *db) {
 
 int dnxcu_db_populate(dnxcu_db *db, const dnxcu_model_desc *desc, int height, int width, int device) {
   if (!db || !desc || height <= 0 || width <= 0) return DNXCU_E_BAD_ARG;
-  (void)device;
   dnxcu_model m;
-  const bool allow_tc = !(desc->options & DNXCU_OPT_NO_TCGEN05);
+  // the candidates are those the device can run (the reference prunes its configuration space with the
+  // device info the same way, DirectConvShaderCM.cpp:19-28); device < 0: no device at hand, every variant counts
+  bool allow_tc = !(desc->options & DNXCU_OPT_NO_TCGEN05);
+  if (device >= 0) {
+    dnxcu_caps caps;
+    int cst = dnxcu_get_device_caps(device, &caps);
+    if (cst) return cst;
+    allow_tc = allow_tc && caps.tcgen05;
+    cudaSetDevice(device);  // launch geometry (part of an entry's key) follows this device's SM count
+  }
   int st = build_fused_ops(*desc, allow_tc, m);
   if (st) return st;
   int added = 0;
@@ -240,6 +248,7 @@ int dnxcu_db_populate(dnxcu_db *db, const dnxcu_model_desc *desc, int height, in
     d.c_a = op.c_a;
     d.c_b = op.c_b;
     d.c_out = op.c_out;
+    d.leaky_alpha = op.alpha;
     // aligned placeholders: validation never dereferences
     d.in_a = (const void *)0x1000;
     d.in_b = op.c_b ? (const void *)0x1000 : nullptr;
@@ -285,6 +294,12 @@ int dnxcu_db_bench(dnxcu_db *db, int device, int min_samples, double max_relativ
   cudaEvent_t e0, e1;
   DNXCU_CUDA(cudaEventCreate(&e0));
   DNXCU_CUDA(cudaEventCreate(&e1));
+  int *dstatus = nullptr;
+  DNXCU_CUDA(cudaMalloc(&dstatus, 256));
+  DNXCU_CUDA(cudaMemset(dstatus, 0, 256));
+  // one sample = kReps launches back to back between one event pair: launch latency and event resolution
+  // weigh less than with single launches, so the variant picks are stable from run to run
+  constexpr int kReps = 5;
   int status = DNXCU_OK;
   for (int round = 0; round < max_rounds && status == DNXCU_OK; ++round) {
     // un-converged entries, never sampled first, then by largest relative standard error (db.cpp:88-175)
@@ -308,24 +323,39 @@ int dnxcu_db_bench(dnxcu_db *db, int device, int min_samples, double max_relativ
       int st = materialise(e, bufs, d);
       if (st == DNXCU_E_NO_MEMORY) continue;
       if (st) { status = st; break; }
-      st = dnxcu_launch(&d, s);  // untimed first launch
+      d.device_status = dstatus;
+      dnxcu_plan *plan = nullptr;
+      st = dnxcu_plan_create(&d, &plan);
+      if (st == DNXCU_E_UNSUPPORTED) continue;  // an entry of another device's database
       if (st) { status = st; break; }
+      st = dnxcu_plan_launch(plan, s);  // untimed first launch
       const int want = e.n == 0 ? min_samples : std::max(2, min_samples / 2);
-      for (int k = 0; k < want; ++k) {
+      for (int k = 0; k < want && !st; ++k) {
         cudaEventRecord(e0, s);
-        st = dnxcu_launch(&d, s);
+        for (int r = 0; r < kReps && !st; ++r) st = dnxcu_plan_launch(plan, s);
         cudaEventRecord(e1, s);
         if (st) break;
         if (cudaEventSynchronize(e1) != cudaSuccess) { st = DNXCU_E_CUDA; break; }
+        int hstatus = 0;
+        if (cudaMemcpy(&hstatus, dstatus, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) { st = DNXCU_E_CUDA; break; }
+        if (hstatus) {
+          // a bounded wait ran out inside the kernel: this is a failure, not a latency
+          cudaMemset(dstatus, 0, sizeof(int));
+          st = DNXCU_E_DEVICE;
+          break;
+        }
         float ms = 0;
         cudaEventElapsedTime(&ms, e0, e1);
+        ms /= (float)kReps;
         if (ms > 0 && ms < 100000.0f) add_sample(e, ms);  // the reference drops ts1 <= ts0 and > 100 s (db.cpp:498-540)
       }
-      if (st) { status = st; break; }
       cudaStreamSynchronize(s);
+      dnxcu_plan_destroy(plan);
+      if (st) { status = st; break; }
     }
     if (status == DNXCU_OK) status = dnxcu_db_atomic_writeback(db);
   }
+  cudaFree(dstatus);
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
   cudaStreamDestroy(s);

@@ -49,12 +49,22 @@ void conv_direct_prepare(const Variant &v, const uint16_t *kcrs, int k, int ca, 
 
 int conv_tc_validate(const Variant &v, const dnxcu_dispatch &d);
 int conv_tc_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s);
+// A tensor core conv dispatch planned once (launch parameters + encoded tensor maps), launched many times.
+struct ConvTcPlan;
+int conv_tc_plan(const Variant &v, const dnxcu_dispatch &d, ConvTcPlan **out);
+int conv_tc_launch_plan(const ConvTcPlan &p, cudaStream_t s);
+void conv_tc_plan_free(ConvTcPlan *p);
+// Sets the per-kernel attributes of every tensor core kernel on the current device (idempotent).
+int conv_tc_init_device();
 void conv_tc_grid(const Variant &v, const dnxcu_dispatch &d, uint32_t g[3]);
 size_t conv_tc_weight_bytes(const Variant &v, int k, int ca, int cb);
 void conv_tc_prepare(const Variant &v, const uint16_t *kcrs, int k, int ca, int cb, uint16_t *out);
 
 int mem_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s);
 void mem_grid(const Variant &v, const dnxcu_dispatch &d, uint32_t g[3]);
+
+// Limit of every bounded device-side wait in clock64 ticks (dnxcu_set_wait_limit_us).
+unsigned long long wait_limit_cycles();
 
 // SHA-256 (hex) of a byte string; used for variant identities and database keys.
 void sha256_hex(const void *data, size_t n, char out_hex[65]);

@@ -95,18 +95,27 @@ __global__ void concat_s(const __half *__restrict__ a, const __half *__restrict_
   }
 }
 
-// max(v, 0) (basic_activation.comp:26-34)
-__global__ void relu_v8(const uint4 *__restrict__ in, uint4 *__restrict__ out, long long n8) {
+// max(v, 0), or with LEAKY max(v, alpha * v) in binary16 (basic_activation.comp:26-34)
+__device__ __forceinline__ uint32_t leaky2u(uint32_t a, __half2 alpha) {
+  const __half2 v = *reinterpret_cast<__half2 *>(&a);
+  __half2 r = __hmax2(v, __hmul2(alpha, v));
+  return *reinterpret_cast<uint32_t *>(&r);
+}
+template <bool LEAKY>
+__global__ void relu_v8(const uint4 *__restrict__ in, uint4 *__restrict__ out, long long n8, __half alpha) {
+  const __half2 a2 = __half2half2(alpha);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8;
        i += (long long)gridDim.x * blockDim.x) {
-    const uint4 z = make_uint4(0, 0, 0, 0);
-    out[i] = hmax8(ldg16(in + i), z);
+    const uint4 v = ldg16(in + i);
+    if (LEAKY) out[i] = make_uint4(leaky2u(v.x, a2), leaky2u(v.y, a2), leaky2u(v.z, a2), leaky2u(v.w, a2));
+    else out[i] = hmax8(v, make_uint4(0, 0, 0, 0));
   }
 }
-__global__ void relu_s(const __half *__restrict__ in, __half *__restrict__ out, long long n) {
+template <bool LEAKY>
+__global__ void relu_s(const __half *__restrict__ in, __half *__restrict__ out, long long n, __half alpha) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x)
-    out[i] = __hmax(in[i], __float2half(0.0f));
+    out[i] = LEAKY ? __hmax(in[i], __hmul(alpha, in[i])) : __hmax(in[i], __float2half(0.0f));
 }
 
 // out[p][0:C] = in[p][0:C], out[p][C:Cp] = 0: one thread per pixel and 8 channel piece of the output
@@ -258,10 +267,18 @@ int mem_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
         concat_s<<<g[0], kThreads, 0, s>>>((const __half *)d.in_a, (const __half *)d.in_b, (__half *)d.out, P,
                                            d.c_a, d.c_b);
       break;
-    case VK_RELU:
-      if (vec == 8) relu_v8<<<g[0], kThreads, 0, s>>>((const uint4 *)d.in_a, (uint4 *)d.out, P * d.c_a / 8);
-      else relu_s<<<g[0], kThreads, 0, s>>>((const __half *)d.in_a, (__half *)d.out, P * d.c_a);
+    case VK_RELU: {
+      const __half alpha = __float2half_rn(d.leaky_alpha);
+      const bool leaky = d.flags & DNXCU_F_LEAKY;
+      if (vec == 8) {
+        if (leaky) relu_v8<true><<<g[0], kThreads, 0, s>>>((const uint4 *)d.in_a, (uint4 *)d.out, P * d.c_a / 8, alpha);
+        else relu_v8<false><<<g[0], kThreads, 0, s>>>((const uint4 *)d.in_a, (uint4 *)d.out, P * d.c_a / 8, alpha);
+      } else {
+        if (leaky) relu_s<true><<<g[0], kThreads, 0, s>>>((const __half *)d.in_a, (__half *)d.out, P * d.c_a, alpha);
+        else relu_s<false><<<g[0], kThreads, 0, s>>>((const __half *)d.in_a, (__half *)d.out, P * d.c_a, alpha);
+      }
       break;
+    }
     default: return DNXCU_E_BAD_ARG;
   }
   DNXCU_CUDA(cudaGetLastError());

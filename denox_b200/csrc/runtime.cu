@@ -17,6 +17,32 @@ namespace dnxcu {
 //   concat(a, b) -> conv                 ConcatConvCMShader.cpp:301-359
 //   conv(+relu) -> maxpool 2x2           pool in the conv epilogue
 //   upsample 2x -> [concat ->] conv      upsample as the conv's operand address map
+// True when some variant that writes the pooled output from its epilogue accepts a conv with these channel
+// counts and flags.  Acceptance depends on channels and weight size only, so a nominal extent is probed.
+static bool fused_pool_variant_exists(int c_a, int c_b, int c_out, uint32_t flags) {
+  dnxcu_dispatch d;
+  memset(&d, 0, sizeof(d));
+  d.flags = flags;
+  d.pc[0] = d.pc[1] = 64;
+  d.c_a = c_a;
+  d.c_b = c_b;
+  d.c_out = c_out;
+  void *const probe = (void *)0x1000;  // passes the alignment rules, never dereferenced by validation
+  d.in_a = probe;
+  d.in_b = c_b > 0 ? probe : nullptr;
+  d.out = (flags & DNXCU_F_NO_FULL_OUT) ? nullptr : probe;
+  d.out_pool = probe;
+  d.weights = probe;
+  d.bias = (flags & DNXCU_F_BIAS) ? probe : nullptr;
+  for (int id = 0; id < variant_count(); ++id) {
+    const Variant *v = get_variant(id);
+    if (v->desc.op != DNXCU_OP_CONV3X3 || !(v->desc.allowed_flags & DNXCU_F_POOL_OUT)) continue;
+    d.variant = id;
+    if (dnxcu_validate(&d) == DNXCU_OK) return true;
+  }
+  return false;
+}
+
 int build_fused_ops(const dnxcu_model_desc &desc, bool allow_tc, dnxcu_model &m) {
   if (desc.n_nodes <= 0 || desc.n_tensors <= 0 || !desc.nodes) return DNXCU_E_BAD_ARG;
   if (desc.input_tensor < 0 || desc.input_tensor >= desc.n_tensors || desc.output_tensor < 0 ||
@@ -47,7 +73,8 @@ int build_fused_ops(const dnxcu_model_desc &desc, bool allow_tc, dnxcu_model &m)
         to.channels = n.c_out;
         to.level = t0.level;
         break;
-      case DNXCU_NODE_RELU: to = t0; break;
+      case DNXCU_NODE_RELU:
+      case DNXCU_NODE_LEAKY_RELU: to = t0; break;
       case DNXCU_NODE_MAXPOOL:
         to.channels = t0.channels;
         to.level = t0.level + 1;
@@ -107,8 +134,10 @@ int build_fused_ops(const dnxcu_model_desc &desc, bool allow_tc, dnxcu_model &m)
       p.a = desc.nodes[pc].in0;
       p.up = 1;
     }
+    // conv -> ReLU | LeakyReLU (DirectConvShaderCM.cpp:201-244: both activations are fused)
     if (f_act && sole(p.out, consumers[p.out].empty() ? -1 : consumers[p.out][0]) &&
-        desc.nodes[consumers[p.out][0]].kind == DNXCU_NODE_RELU) {
+        (desc.nodes[consumers[p.out][0]].kind == DNXCU_NODE_RELU ||
+         desc.nodes[consumers[p.out][0]].kind == DNXCU_NODE_LEAKY_RELU)) {
       p.relu_node = consumers[p.out][0];
       absorbed[p.relu_node] = true;
       p.out = desc.nodes[p.relu_node].out;
@@ -117,9 +146,21 @@ int build_fused_ops(const dnxcu_model_desc &desc, bool allow_tc, dnxcu_model &m)
       for (int c : consumers[p.out])
         if (desc.nodes[c].kind == DNXCU_NODE_MAXPOOL && p.pool_node < 0) p.pool_node = c;
       if (p.pool_node >= 0) {
-        absorbed[p.pool_node] = true;
-        p.out_pool = desc.nodes[p.pool_node].out;
-        p.no_full = sole(p.out, p.pool_node);
+        // The pool moves into the conv's epilogue only when a variant with that epilogue takes the conv
+        // (channel counts, weight size): otherwise the conv keeps any variant, the CUDA core one included,
+        // and basic-pool follows as a dispatch of its own, as in the reference's schedule.
+        const int ca = m.tensors[p.a].channels, cb = p.b >= 0 ? m.tensors[p.b].channels : 0;
+        uint32_t fl = DNXCU_F_POOL_OUT | (p.up ? DNXCU_F_UP2X_A : 0u) | (n.bias ? DNXCU_F_BIAS : 0u);
+        if (p.relu_node >= 0)
+          fl |= desc.nodes[p.relu_node].kind == DNXCU_NODE_RELU ? DNXCU_F_RELU : DNXCU_F_LEAKY;
+        if (sole(p.out, p.pool_node)) fl |= DNXCU_F_NO_FULL_OUT;
+        if (fused_pool_variant_exists(ca, cb, n.c_out, fl)) {
+          absorbed[p.pool_node] = true;
+          p.out_pool = desc.nodes[p.pool_node].out;
+          p.no_full = sole(p.out, p.pool_node);
+        } else {
+          p.pool_node = -1;
+        }
       }
     }
     plans[i] = p;
@@ -149,7 +190,16 @@ int build_fused_ops(const dnxcu_model_desc &desc, bool allow_tc, dnxcu_model &m)
         op.name = "direct-conv";
         if (p.b >= 0) op.name = "concat-conv";
         if (p.up) { op.flags |= DNXCU_F_UP2X_A; op.name = "up" + op.name; }
-        if (p.relu_node >= 0) { op.flags |= DNXCU_F_RELU; op.name += "+relu"; }
+        if (p.relu_node >= 0) {
+          if (desc.nodes[p.relu_node].kind == DNXCU_NODE_RELU) {
+            op.flags |= DNXCU_F_RELU;
+            op.name += "+relu";
+          } else {
+            op.flags |= DNXCU_F_LEAKY;
+            op.alpha = desc.nodes[p.relu_node].alpha;
+            op.name += "+leaky";
+          }
+        }
         if (p.pool_node >= 0) { op.flags |= DNXCU_F_POOL_OUT; op.name += "+pool"; }
         if (p.no_full) op.flags |= DNXCU_F_NO_FULL_OUT;
         const size_t nw = (size_t)n.c_out * (op.c_a + op.c_b) * 9;
@@ -161,6 +211,12 @@ int build_fused_ops(const dnxcu_model_desc &desc, bool allow_tc, dnxcu_model &m)
         break;
       }
       case DNXCU_NODE_RELU: op.op = DNXCU_OP_RELU; op.name = "basic-activation"; break;
+      case DNXCU_NODE_LEAKY_RELU:
+        op.op = DNXCU_OP_RELU;
+        op.flags |= DNXCU_F_LEAKY;
+        op.alpha = n.alpha;
+        op.name = "basic-activation(leaky)";
+        break;
       case DNXCU_NODE_MAXPOOL: op.op = DNXCU_OP_MAXPOOL2X2; op.name = "basic-pool"; break;
       case DNXCU_NODE_UPSAMPLE: op.op = DNXCU_OP_UPSAMPLE2X; op.name = "basic-upsample"; break;
       case DNXCU_NODE_CONCAT:
@@ -257,16 +313,21 @@ struct dnxcu_instance {
   std::vector<void *> owned;         // everything to cudaFree
   std::vector<dnxcu_dispatch> disp;  // with the instance's own input / output buffers
   std::vector<dnxcu_halo_point> halos;
+  std::vector<dnxcu_plan *> plans;   // one per dispatch, made from the instance's own buffers
   int *status = nullptr;
   cudaStream_t stream = nullptr;
-  // cached graph of the whole schedule for one (input, output) pointer pair
-  cudaGraphExec_t graph = nullptr;
-  const void *graph_in = nullptr;
-  void *graph_out = nullptr;
+  // cached graphs of the whole schedule, one per (input, output) pointer pair, most recently used first
+  struct Graph {
+    cudaGraphExec_t exec;
+    const void *in;
+    void *out;
+  };
+  std::vector<Graph> graphs;
   std::vector<cudaEvent_t> events;
 
   ~dnxcu_instance() {
-    if (graph) cudaGraphExecDestroy(graph);
+    for (Graph &g : graphs) cudaGraphExecDestroy(g.exec);
+    for (dnxcu_plan *p : plans) dnxcu_plan_destroy(p);
     for (cudaEvent_t e : events) cudaEventDestroy(e);
     if (stream) cudaStreamDestroy(stream);
     for (void *p : owned) cudaFree(p);
@@ -289,17 +350,30 @@ int dev_alloc(dnxcu_instance &inst, size_t bytes, void **out) {
 
 // Enqueues dispatch i, substituting caller pointers for the model's input / output tensors.
 int launch_one(dnxcu_instance &inst, int i, const void *in_override, void *out_override, cudaStream_t s) {
-  dnxcu_dispatch d = inst.disp[i];
   const FusedOp &op = inst.model->ops[i];
-  if (in_override) {
-    if (op.in_a == inst.model->input_tensor) d.in_a = in_override;
-    if (op.in_b == inst.model->input_tensor) d.in_b = in_override;
+  const int tin = inst.model->input_tensor, tout = inst.model->output_tensor;
+  const bool sub_in = in_override && (op.in_a == tin || op.in_b == tin);
+  const bool sub_out = out_override && (op.out == tout || op.out_pool == tout);
+  if (!sub_in && !sub_out) return dnxcu_plan_launch(inst.plans[i], s);  // planned once at creation
+  dnxcu_dispatch d = inst.disp[i];
+  if (sub_in) {
+    if (op.in_a == tin) d.in_a = in_override;
+    if (op.in_b == tin) d.in_b = in_override;
   }
-  if (out_override) {
-    if (op.out == inst.model->output_tensor) d.out = out_override;
-    if (op.out_pool == inst.model->output_tensor) d.out_pool = out_override;
+  if (sub_out) {
+    if (op.out == tout) d.out = out_override;
+    if (op.out_pool == tout) d.out_pool = out_override;
   }
   return dnxcu_launch(&d, s);
+}
+
+// Reads the instance's status word; a kernel's time-out code is reported once and then cleared, so that
+// the frames after it are judged on their own.
+int take_status(dnxcu_instance &inst, int hstatus) {
+  if (!hstatus) return DNXCU_OK;
+  cudaMemsetAsync(inst.status, 0, sizeof(int), inst.stream);
+  cudaStreamSynchronize(inst.stream);
+  return DNXCU_E_DEVICE;
 }
 
 }  // namespace
@@ -382,8 +456,11 @@ int dnxcu_instance_create(const dnxcu_model *m, int height, int width, const dnx
   st = dnxcu_get_device_caps(m->device, &caps);
   if (st) return st;
   const bool allow_tc = caps.tcgen05 && !(m->options & DNXCU_OPT_NO_TCGEN05);
+  // kernel attributes now, so that no launch needs set-up work later (a launch may sit inside a stream capture)
+  if (allow_tc && (st = conv_tc_init_device())) return st;
 
   inst->disp.resize(m->ops.size());
+  inst->plans.assign(m->ops.size(), nullptr);
   for (size_t i = 0; i < m->ops.size(); ++i) {
     const FusedOp &op = m->ops[i];
     dnxcu_dispatch d;
@@ -399,6 +476,7 @@ int dnxcu_instance_create(const dnxcu_model *m, int height, int width, const dnx
     d.out = (op.flags & DNXCU_F_NO_FULL_OUT) ? nullptr : inst->tensor_ptr[op.out];
     d.out_pool = op.out_pool >= 0 ? inst->tensor_ptr[op.out_pool] : nullptr;
     d.device_status = inst->status;
+    d.leaky_alpha = op.alpha;
     if (!d.in_a || (op.in_b >= 0 && !d.in_b)) return DNXCU_E_STATE;
 
     if (op.op == DNXCU_OP_CONV3X3) {
@@ -477,6 +555,8 @@ int dnxcu_instance_create(const dnxcu_model *m, int height, int width, const dnx
       d.weights = dw;
     }
     inst->disp[i] = d;
+    st = dnxcu_plan_create(&d, &inst->plans[i]);
+    if (st) return st;
   }
   if (inst->padded) {
     const TensorInfo &ti = m->tensors[m->input_tensor], &to = m->tensors[m->output_tensor];
@@ -528,13 +608,12 @@ int dnxcu_instance_enqueue_range(dnxcu_instance *inst, int first, int last, void
 int dnxcu_instance_enqueue(dnxcu_instance *inst, const void *dev_in, void *dev_out, void *stream) {
   if (!inst || !dev_in || !dev_out) return DNXCU_E_BAD_ARG;
   cudaStream_t s = (cudaStream_t)stream;
-  // The schedule is a fixed chain of launches: capture it once per (in, out)
-  // pointer pair and replay the graph (one launch instead of one per dispatch).
-  if (!inst->graph || inst->graph_in != dev_in || inst->graph_out != dev_out) {
-    if (inst->graph) {
-      cudaGraphExecDestroy(inst->graph);
-      inst->graph = nullptr;
-    }
+  // The schedule is a fixed chain of launches: capture it once per (in, out) pointer pair and replay the
+  // graph (one launch instead of one per dispatch).  Capturing records the launches on the instance's own
+  // stream without running anything, so nothing here touches the caller's buffers or waits for the device.
+  size_t hit = 0;
+  while (hit < inst->graphs.size() && (inst->graphs[hit].in != dev_in || inst->graphs[hit].out != dev_out)) ++hit;
+  if (hit == inst->graphs.size()) {
     // caller-extent frames: pad into the model's own input tensor first, slice out of its own output tensor last
     auto whole = [&]() -> int {
       int st = DNXCU_OK;
@@ -552,14 +631,9 @@ int dnxcu_instance_enqueue(dnxcu_instance *inst, const void *dev_in, void *dev_o
       }
       return st;
     };
-    // a first plain pass makes every kernel's one-time function attribute set-up happen outside the capture
-    {
-      int st = whole();
-      if (st) return st;
-    }
-    DNXCU_CUDA(cudaStreamSynchronize(inst->stream));
     cudaGraph_t gr = nullptr;
-    DNXCU_CUDA(cudaStreamBeginCapture(inst->stream, cudaStreamCaptureModeThreadLocal));
+    // relaxed mode: only this instance's private stream is captured; other threads' CUDA calls are not its business
+    DNXCU_CUDA(cudaStreamBeginCapture(inst->stream, cudaStreamCaptureModeRelaxed));
     int st = whole();
     cudaError_t e = cudaStreamEndCapture(inst->stream, &gr);
     if (st) {
@@ -567,13 +641,23 @@ int dnxcu_instance_enqueue(dnxcu_instance *inst, const void *dev_in, void *dev_o
       return st;
     }
     if (e != cudaSuccess) return cuda_fail(e);
-    e = cudaGraphInstantiate(&inst->graph, gr, 0);
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, gr, 0);
     cudaGraphDestroy(gr);
     if (e != cudaSuccess) return cuda_fail(e);
-    inst->graph_in = dev_in;
-    inst->graph_out = dev_out;
+    if (inst->graphs.size() >= 4) {  // keep the four most recently used pairs
+      cudaGraphExecDestroy(inst->graphs.back().exec);
+      inst->graphs.pop_back();
+    }
+    inst->graphs.insert(inst->graphs.begin(), dnxcu_instance::Graph{exec, dev_in, dev_out});
+    hit = 0;
+  } else if (hit > 0) {
+    const dnxcu_instance::Graph g = inst->graphs[hit];
+    inst->graphs.erase(inst->graphs.begin() + (long)hit);
+    inst->graphs.insert(inst->graphs.begin(), g);
+    hit = 0;
   }
-  DNXCU_CUDA(cudaGraphLaunch(inst->graph, s));
+  DNXCU_CUDA(cudaGraphLaunch(inst->graphs[0].exec, s));
   return DNXCU_OK;
 }
 
@@ -604,7 +688,7 @@ int dnxcu_instance_wait(dnxcu_instance *inst) {
   DNXCU_CUDA(cudaStreamSynchronize(inst->stream));
   int hstatus = 0;
   DNXCU_CUDA(cudaMemcpy(&hstatus, inst->status, sizeof(int), cudaMemcpyDeviceToHost));
-  return hstatus ? DNXCU_E_DEVICE : DNXCU_OK;
+  return take_status(*inst, hstatus);
 }
 
 int dnxcu_instance_infer(dnxcu_instance *inst, const void *host_in, void *host_out) {
@@ -625,7 +709,7 @@ int dnxcu_instance_infer(dnxcu_instance *inst, const void *host_in, void *host_o
   int hstatus = 0;
   DNXCU_CUDA(cudaMemcpyAsync(&hstatus, inst->status, sizeof(int), cudaMemcpyDeviceToHost, inst->stream));
   DNXCU_CUDA(cudaStreamSynchronize(inst->stream));
-  return hstatus ? DNXCU_E_DEVICE : DNXCU_OK;
+  return take_status(*inst, hstatus);
 }
 
 int dnxcu_instance_tensor(const dnxcu_instance *inst, int t, void **ptr, int *h, int *w, int *c) {
@@ -715,7 +799,7 @@ int dnxcu_instance_bench(dnxcu_instance *inst, int warmup, int iters, dnxcu_disp
   if (total_ms) *total_ms = (float)(total / iters);
   int hstatus = 0;
   DNXCU_CUDA(cudaMemcpy(&hstatus, inst->status, sizeof(int), cudaMemcpyDeviceToHost));
-  return hstatus ? DNXCU_E_DEVICE : DNXCU_OK;
+  return take_status(*inst, hstatus);
 }
 
 int dnxcu_instance_halo_count(const dnxcu_instance *inst) { return inst ? (int)inst->halos.size() : DNXCU_E_BAD_ARG; }

@@ -20,6 +20,7 @@ struct FusedOp {
   int c_a = 0, c_b = 0, c_out = 0;
   int level = 0;  // resolution level of the push constants
   int src_node = -1;
+  float alpha = 0.0f;                  // slope of a (fused or standalone) LeakyReLU
   std::vector<uint16_t> weights_kcrs;  // conv
   std::vector<uint16_t> bias;          // conv, may be empty
   std::string name;

@@ -24,7 +24,7 @@ OK = 0
 E_BAD_ARG, E_UNSUPPORTED, E_MISALIGNED, E_CUDA, E_DEVICE, E_NO_MEMORY, E_STATE, E_IO, E_LIMIT = range(-1, -10, -1)
 
 OP_CONV3X3, OP_MAXPOOL2X2, OP_UPSAMPLE2X, OP_CONCAT, OP_RELU, OP_PAD_CHANNELS, OP_PAD_EDGE, OP_SLICE = 1, 2, 3, 4, 5, 6, 7, 8
-F_RELU, F_BIAS, F_UP2X_A, F_POOL_OUT, F_NO_FULL_OUT = 0x01, 0x02, 0x04, 0x08, 0x10
+F_RELU, F_BIAS, F_UP2X_A, F_POOL_OUT, F_NO_FULL_OUT, F_LEAKY = 0x01, 0x02, 0x04, 0x08, 0x10, 0x20
 OPT_NO_FUSE_ACTIVATION, OPT_NO_FUSE_POOL, OPT_NO_FUSE_UPSAMPLE, OPT_NO_FUSE_CONCAT, OPT_NO_TCGEN05 = 1, 2, 4, 8, 16
 OPT_NO_PAD_INPUT = 32
 
@@ -59,7 +59,7 @@ class VariantDesc(C.Structure):
 
 class Dispatch(C.Structure):
     _fields_ = [("variant", C.c_int32), ("flags", C.c_uint32), ("pc", C.c_uint32 * 2), ("c_a", C.c_int32),
-                ("c_b", C.c_int32), ("c_out", C.c_int32), ("reserved", C.c_int32), ("in_a", C.c_void_p),
+                ("c_b", C.c_int32), ("c_out", C.c_int32), ("leaky_alpha", C.c_float), ("in_a", C.c_void_p),
                 ("in_b", C.c_void_p), ("out", C.c_void_p), ("out_pool", C.c_void_p), ("weights", C.c_void_p),
                 ("bias", C.c_void_p), ("halo", C.c_void_p * 4), ("device_status", C.c_void_p),
                 ("pc_ext", C.c_uint32 * 4)]
@@ -67,7 +67,7 @@ class Dispatch(C.Structure):
 
 class NodeC(C.Structure):
     _fields_ = [("kind", C.c_int32), ("in0", C.c_int32), ("in1", C.c_int32), ("out", C.c_int32),
-                ("c_out", C.c_int32), ("reserved", C.c_int32), ("weights_kcrs", C.c_void_p), ("bias", C.c_void_p)]
+                ("c_out", C.c_int32), ("alpha", C.c_float), ("weights_kcrs", C.c_void_p), ("bias", C.c_void_p)]
 
 
 class ModelDesc(C.Structure):
@@ -104,6 +104,10 @@ SIGNATURES = {
     "dnxcu_variant_sha256": (C.c_int, [C.c_int, C.c_char_p]),
     "dnxcu_validate": (C.c_int, [C.POINTER(Dispatch)]),
     "dnxcu_launch": (C.c_int, [C.POINTER(Dispatch), C.c_void_p]),
+    "dnxcu_plan_create": (C.c_int, [C.POINTER(Dispatch), C.POINTER(C.c_void_p)]),
+    "dnxcu_plan_launch": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "dnxcu_plan_destroy": (None, [C.c_void_p]),
+    "dnxcu_set_wait_limit_us": (C.c_int, [C.c_uint32]),
     "dnxcu_grid": (C.c_int, [C.POINTER(Dispatch), C.POINTER(C.c_uint32 * 3)]),
     "dnxcu_cost": (C.c_int, [C.POINTER(Dispatch), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
                              C.POINTER(C.c_uint64)]),
@@ -193,6 +197,7 @@ def _model_desc(net, options=0):
     keep = [arr]
     for i, nd in enumerate(net.nodes):
         arr[i].kind, arr[i].in0, arr[i].in1, arr[i].out, arr[i].c_out = nd.kind, nd.in0, nd.in1, nd.out, nd.c_out
+        arr[i].alpha = float(getattr(nd, "alpha", 0.0))
         if nd.weights is not None:
             w = np.ascontiguousarray(nd.weights, dtype=np.float16)
             keep.append(w)
@@ -222,6 +227,7 @@ class Db:
         return check(L.dnxcu_db_size(self._h))
 
     def populate(self, net, h, w, device=0, options=0):
+        """device < 0: enumerate for a device with every capability, without touching one."""
         desc, keep = _model_desc(net, options)
         return check(L.dnxcu_db_populate(self._h, C.byref(desc), h, w, device), "dnxcu_db_populate")
 

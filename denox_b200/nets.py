@@ -14,7 +14,7 @@ import numpy as np
 
 from . import rng
 
-CONV, RELU, MAXPOOL, UPSAMPLE, CONCAT = 1, 2, 3, 4, 5
+CONV, RELU, MAXPOOL, UPSAMPLE, CONCAT, LEAKY_RELU = 1, 2, 3, 4, 5, 6
 
 
 @dataclass
@@ -27,6 +27,7 @@ class Node:
     weights: Optional[np.ndarray] = None  # [c_out][c_in][3][3] binary16
     bias: Optional[np.ndarray] = None     # [c_out] binary16
     name: str = ""
+    alpha: float = 0.0                    # slope of a LEAKY_RELU node
 
 
 @dataclass
@@ -45,7 +46,8 @@ class Net:
         self.n_tensors = len(self.channels)
         return self.n_tensors - 1
 
-    def conv(self, x, c_out, relu=True, bias_seed=None, name=""):
+    def conv(self, x, c_out, relu=True, bias_seed=None, name="", leaky=None):
+        """conv3x3 followed by ReLU (relu=True), by LeakyReLU with slope `leaky`, or by nothing."""
         c_in = self.channels[x]
         w = rng.he_normal_weights(self._wseed, c_out, c_in)
         b = None
@@ -54,6 +56,10 @@ class Net:
         self._wseed += 1
         y = self._new(c_out)
         self.nodes.append(Node(CONV, x, y, c_out=c_out, weights=w, bias=b, name=name))
+        if leaky is not None:
+            z = self._new(c_out)
+            self.nodes.append(Node(LEAKY_RELU, y, z, name=name + ".leaky", alpha=float(leaky)))
+            return z
         if relu:
             z = self._new(c_out)
             self.nodes.append(Node(RELU, y, z, name=name + ".relu"))
@@ -83,15 +89,16 @@ def _start(name, c_in):
     return net
 
 
-def tiny_unet(bias=False) -> Net:
+def tiny_unet(bias=False, leaky=None) -> Net:
+    """leaky: slope of a LeakyReLU that takes the place of every ReLU."""
     n = _start("tiny-unet", 3)
     bs = (lambda i: 3000 + i) if bias else (lambda i: None)
-    x = n.conv(0, 16, name="conv0", bias_seed=bs(0))
+    x = n.conv(0, 16, name="conv0", bias_seed=bs(0), leaky=leaky)
     p = n.pool(x, "pool0")
-    y = n.conv(p, 32, name="conv1", bias_seed=bs(1))
+    y = n.conv(p, 32, name="conv1", bias_seed=bs(1), leaky=leaky)
     u = n.upsample(y, "up0")
     c = n.concat(u, x, "cat0")
-    z = n.conv(c, 16, name="conv2", bias_seed=bs(2))
+    z = n.conv(c, 16, name="conv2", bias_seed=bs(2), leaky=leaky)
     o = n.conv(z, 3, relu=False, name="conv3", bias_seed=bs(3))
     n.output_tensor = o
     return n
@@ -123,6 +130,47 @@ def oidn_unet() -> Net:
     x = n.conv(x, 64, name="dec_conv1a")
     x = n.conv(x, 32, name="dec_conv1b")
     x = n.conv(x, 3, relu=False, name="dec_conv0")
+    n.output_tensor = x
+    return n
+
+
+def oidn_unet_reference(in_channels: int = 9, out_channels: int = 3, wseed: int = 2100, bias: bool = True) -> Net:
+    """The U-Net exactly as the reference's own model file builds it (oidn_model.py:206-331, the large
+    configuration): every skip is a pooled tensor or the input, so the first decoder conv takes
+    96 + 64 = 160 channels (pool3 is the level-4 skip), where the benchmark configuration's list says
+    96 + 80 = 176.  Conv names are the module names of that file; its convs carry a bias (nn.Conv2d default)."""
+    n = _start("oidn-unet-reference", in_channels)
+    n._wseed = wseed
+    nb = [0]
+
+    def conv(x, c, name, relu=True):
+        nb[0] += 1
+        return n.conv(x, c, relu=relu, name=name, bias_seed=(4000 + nb[0]) if bias else None)
+
+    x = conv(0, 32, "enc_conv0")
+    x = conv(x, 32, "enc_conv1")
+    pool1 = n.pool(x, "pool1")
+    x = conv(pool1, 48, "enc_conv2")
+    pool2 = n.pool(x, "pool2")
+    x = conv(pool2, 64, "enc_conv3")
+    pool3 = n.pool(x, "pool3")
+    x = conv(pool3, 80, "enc_conv4")
+    x = n.pool(x, "pool4")
+    x = conv(x, 96, "enc_conv5a")
+    x = conv(x, 96, "enc_conv5b")
+    x = n.concat(n.upsample(x, "upsample4"), pool3, "concat4")    # 96 + 64 = 160
+    x = conv(x, 112, "dec_conv4a")
+    x = conv(x, 112, "dec_conv4b")
+    x = n.concat(n.upsample(x, "upsample3"), pool2, "concat3")    # 112 + 48 = 160
+    x = conv(x, 96, "dec_conv3a")
+    x = conv(x, 96, "dec_conv3b")
+    x = n.concat(n.upsample(x, "upsample2"), pool1, "concat2")    # 96 + 32 = 128
+    x = conv(x, 64, "dec_conv2a")
+    x = conv(x, 64, "dec_conv2b")
+    x = n.concat(n.upsample(x, "upsample1"), 0, "concat1")        # 64 + in_channels
+    x = conv(x, 64, "dec_conv1a")
+    x = conv(x, 32, "dec_conv1b")
+    x = conv(x, out_channels, "dec_conv0", relu=False)
     n.output_tensor = x
     return n
 

@@ -104,6 +104,10 @@ typedef enum dnxcu_op {
 #define DNXCU_F_UP2X_A 0x04u      /* operand a is (H/2)x(W/2), read through src = dst/2      */
 #define DNXCU_F_POOL_OUT 0x08u    /* also write the 2x2 max pooled result to out_pool       */
 #define DNXCU_F_NO_FULL_OUT 0x10u /* with POOL_OUT: do not write the full resolution output */
+#define DNXCU_F_LEAKY 0x20u       /* max(x, alpha * x) in binary16 on the finished, rounded sum
+                                     (direct_conv_cm.comp:1071-1076, basic_activation.comp:29-30);
+                                     alpha = dispatch.leaky_alpha; excludes DNXCU_F_RELU; also the
+                                     flag that turns a DNXCU_OP_RELU dispatch into a LeakyReLU */
 
 typedef struct dnxcu_variant_desc {
   int32_t id;          /* index in the table, stable within one build of the library */
@@ -124,9 +128,10 @@ DNXCU_API int dnxcu_variant_count(void);
 DNXCU_API const dnxcu_variant_desc *dnxcu_variant(int id);
 /* First variant whose family and config match exactly, or DNXCU_E_BAD_ARG. */
 DNXCU_API int dnxcu_find_variant(const char *family, const char *config);
-/* SHA-256 of (family, config, kernel source revision) as 64 hex digits plus
- * NUL: the identity a benchmark database keys on.  Stands in for
- * GlslCompilerInstance::fast_sha256 (spirv/src/denox/glsl/GlslCompilerInstance.hpp:73-79). */
+/* SHA-256 of (family, config, digest of the kernel sources the library was built from) as 64 hex digits
+ * plus NUL: the identity a benchmark database keys on; editing a kernel changes it, so stored timings of
+ * an older build are not picked up.  Stands in for GlslCompilerInstance::fast_sha256, the hash of source
+ * text and preamble (spirv/src/denox/glsl/GlslCompilerInstance.hpp:73-79). */
 DNXCU_API int dnxcu_variant_sha256(int id, char out_hex[65]);
 
 /* ------------------------------------------------------------------------
@@ -148,7 +153,8 @@ typedef struct dnxcu_dispatch {
   int32_t c_a;    /* channels of operand a */
   int32_t c_b;    /* channels of operand b (concat second operand), 0 if none */
   int32_t c_out;  /* output channels (conv); ignored otherwise */
-  int32_t reserved;
+  float leaky_alpha; /* slope of DNXCU_F_LEAKY (rounded to binary16 before use, as the reference's
+                        atype(ACTIVATION_LeakyReLU_alpha)); ignored without the flag */
   const void *in_a;
   const void *in_b;
   void *out;
@@ -165,9 +171,10 @@ typedef struct dnxcu_dispatch {
                              (1 weights, 2 input row, 3 accumulator block free,
                              4/5 streamed weights, 6 accumulators complete,
                              7 input slot free, 8 raw row of the upsampled
-                             operand) or when it met a state it refuses to
-                             compute in (9); the launch returns normally and
-                             the output is then undefined */
+                             operand, 10 halo row of a neighbouring band) or
+                             when it met a state it refuses to compute in (9);
+                             the launch returns normally and the output is
+                             then undefined */
   uint32_t pc_ext[4];     /* further push constants of pad / slice dispatches (see dnxcu_op) */
 } dnxcu_dispatch;
 
@@ -176,6 +183,19 @@ DNXCU_API int dnxcu_validate(const dnxcu_dispatch *d);
 /* Enqueues the kernel on `stream`.  Stands in for the vkCmdDispatch recorded in
  * Instance::infer (runtime/src/denox/runtime/instance.cpp:367-396). */
 DNXCU_API int dnxcu_launch(const dnxcu_dispatch *d, void *stream);
+/* A dispatch planned once and launched many times: validation, launch geometry and the TMA tensor maps
+ * (encoded from the dispatch's pointers and shape) are worked out by dnxcu_plan_create, so that
+ * dnxcu_plan_launch only enqueues.  The plan is tied to the pointers, shape and flags it was made from; the
+ * caller owns it and keeps one per stream that may launch concurrently.  Stands in for the pipeline +
+ * descriptor set objects Instance::make builds once per dispatch (runtime/src/denox/runtime/instance.cpp:25-286). */
+typedef struct dnxcu_plan dnxcu_plan;
+DNXCU_API int dnxcu_plan_create(const dnxcu_dispatch *d, dnxcu_plan **out);
+DNXCU_API int dnxcu_plan_launch(const dnxcu_plan *p, void *stream);
+DNXCU_API void dnxcu_plan_destroy(dnxcu_plan *p);
+/* Limit of every bounded wait inside the kernels, in microseconds at the device's nominal SM clock
+ * (process wide, read when a launch is planned); 0 restores the default of about 1.5 s.  A wait that runs
+ * out makes the kernel store its code to dispatch.device_status and return. */
+DNXCU_API int dnxcu_set_wait_limit_us(uint32_t microseconds);
 /* Grid the launch would use (wgX, wgY, wgZ of the reference's dispatch record). */
 DNXCU_API int dnxcu_grid(const dnxcu_dispatch *d, uint32_t grid[3]);
 /* Algorithmic cost of the dispatch, the reference's per dispatch metadata
@@ -245,7 +265,9 @@ typedef enum dnxcu_node_kind {
   DNXCU_NODE_RELU = 2,
   DNXCU_NODE_MAXPOOL = 3,
   DNXCU_NODE_UPSAMPLE = 4,
-  DNXCU_NODE_CONCAT = 5
+  DNXCU_NODE_CONCAT = 5,
+  DNXCU_NODE_LEAKY_RELU = 6 /* slope in dnxcu_node.alpha (onnx LeakyRelu,
+                               frontend/onnx/details/ops/leaky_relu.cpp:9-44) */
 } dnxcu_node_kind;
 
 typedef struct dnxcu_node {
@@ -254,7 +276,7 @@ typedef struct dnxcu_node {
   int32_t in1;      /* tensor id (concat) or -1 */
   int32_t out;      /* tensor id */
   int32_t c_out;    /* conv: output channels */
-  int32_t reserved;
+  float alpha;      /* leaky relu: slope */
   const void *weights_kcrs; /* conv: host binary16 [c_out][c_in][3][3] */
   const void *bias;         /* conv: host binary16 [c_out] or NULL */
 } dnxcu_node;
@@ -309,7 +331,10 @@ DNXCU_API int dnxcu_instance_infer(dnxcu_instance *inst, const void *host_in, vo
 DNXCU_API int dnxcu_instance_infer_async(dnxcu_instance *inst, const void *host_in, void *host_out);
 DNXCU_API int dnxcu_instance_wait(dnxcu_instance *inst);
 /* Device resident form: input/output are device pointers, work is enqueued on
- * `stream`, nothing is synchronised. */
+ * `stream`, nothing is synchronised and nothing else runs on the device.  The
+ * schedule is replayed from a CUDA graph; the first call with a new (dev_in,
+ * dev_out) pair captures one (host work only, no device work outside `stream`)
+ * and the instance keeps the graphs of the last four pairs. */
 DNXCU_API int dnxcu_instance_enqueue(dnxcu_instance *inst, const void *dev_in, void *dev_out,
                                      void *stream);
 /* Device pointer and shape of any tensor of the instance after a run (for per
@@ -380,7 +405,9 @@ DNXCU_API void dnxcu_db_close(dnxcu_db *db);
 DNXCU_API int dnxcu_db_size(const dnxcu_db *db);
 /* Adds every (dispatch, variant) candidate of the model at H x W that is not
  * in the database yet; returns the number added (denox::populate,
- * compiler/src/denox/compiler/populate.cpp:23-256). */
+ * compiler/src/denox/compiler/populate.cpp:23-256).  Candidates are those
+ * `device` can run; device < 0 enumerates for a device with every capability
+ * without touching one. */
 DNXCU_API int dnxcu_db_populate(dnxcu_db *db, const dnxcu_model_desc *desc, int height, int width,
                                 int device);
 /* Samples un-converged entries until n >= min_samples and

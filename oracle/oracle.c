@@ -27,6 +27,9 @@
 #include <stdlib.h>
 #include <string.h>
 #include <math.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 #define ORC_API __attribute__((visibility("default")))
 
@@ -128,6 +131,22 @@ static void conv_phase(float *acc, int K, const uint16_t *in, int C, int up, int
   }
 }
 
+/* The activation on a finished sum, in binary16 as the reference applies it to its binary16 accumulator:
+ * act 1 = max(0, x) (direct_conv.comp:559-590, direct_conv_cm.comp:1061-1070), act 2 = LeakyReLU
+ * max(alpha * x, x) with alpha rounded to binary16 and the product rounded to binary16
+ * (direct_conv_cm.comp:1071-1076, basic_activation.comp:26-34).  Of two zeros the positive one wins,
+ * as in the max of IEEE 754-2019. */
+static inline uint16_t activate_h(uint16_t xh, int act, float alpha) {
+  const float x = h2f(xh);
+  if (act == 1) return f2h(x > 0.0f ? x : 0.0f);
+  if (act == 2) {
+    const float a = rh(rh(alpha) * x); /* exact product of two binary16 values, one rounding */
+    if (x > a || (x == a && !signbit(x))) return xh;
+    return f2h(a);
+  }
+  return xh;
+}
+
 /* conv3x3, stride 1, padding 1, optional bias, optional ReLU, over the channel
  * concatenation [a, b] (a first: torch.cat((upsampled, skip), 1),
  * oidn_model.py:227-228).  Restates direct_conv.comp:82-775 for one operand
@@ -137,11 +156,11 @@ static void conv_phase(float *acc, int K, const uint16_t *in, int C, int up, int
  * sum (direct_conv.comp:559-590).  Cb == 0 / b == NULL selects the one-operand
  * form.  up_a != 0: `a` is H/2 x W/2 and is read through the 2x nearest map.
  * w_kcrs: [K][Ca+Cb][3][3] binary16.  bias: [K] binary16 or NULL. */
-ORC_API int orc_conv3x3(const uint16_t *a, int Ca, int up_a, const uint16_t *b, int Cb, int H,
-                        int W, const uint16_t *w_kcrs, const uint16_t *bias, int K, int relu,
-                        int mode, uint16_t *out, const uint16_t *a_halo_top,
-                        const uint16_t *a_halo_bot, const uint16_t *b_halo_top,
-                        const uint16_t *b_halo_bot) {
+ORC_API int orc_conv3x3_act(const uint16_t *a, int Ca, int up_a, const uint16_t *b, int Cb, int H,
+                            int W, const uint16_t *w_kcrs, const uint16_t *bias, int K, int act,
+                            float alpha, int mode, uint16_t *out, const uint16_t *a_halo_top,
+                            const uint16_t *a_halo_bot, const uint16_t *b_halo_top,
+                            const uint16_t *b_halo_bot) {
   if (!a || !w_kcrs || !out || Ca <= 0 || K <= 0 || H <= 0 || W <= 0) return -1;
   if (up_a && ((H | W) & 1)) return -1;
   const int C = Ca + Cb;
@@ -166,11 +185,7 @@ ORC_API int orc_conv3x3(const uint16_t *a, int Ca, int up_a, const uint16_t *b, 
         conv_phase(acc, K, a, Ca, up_a, H, W, y, x, a_halo_top, a_halo_bot, wa, mode);
         if (Cb) conv_phase(acc, K, b, Cb, 0, H, W, y, x, b_halo_top, b_halo_bot, wb, mode);
         uint16_t *o = out + ((int64_t)y * W + x) * K;
-        for (int k = 0; k < K; ++k) {
-          float v = acc[k];
-          if (relu) v = v > 0.0f ? v : 0.0f;
-          o[k] = f2h(v);
-        }
+        for (int k = 0; k < K; ++k) o[k] = activate_h(f2h(acc[k]), act, alpha);
       }
     }
     free(acc);
@@ -178,6 +193,16 @@ ORC_API int orc_conv3x3(const uint16_t *a, int Ca, int up_a, const uint16_t *b, 
   free(wa);
   free(wb);
   return 0;
+}
+
+/* The form without LeakyReLU: relu != 0 selects max(0, x). */
+ORC_API int orc_conv3x3(const uint16_t *a, int Ca, int up_a, const uint16_t *b, int Cb, int H,
+                        int W, const uint16_t *w_kcrs, const uint16_t *bias, int K, int relu,
+                        int mode, uint16_t *out, const uint16_t *a_halo_top,
+                        const uint16_t *a_halo_bot, const uint16_t *b_halo_top,
+                        const uint16_t *b_halo_bot) {
+  return orc_conv3x3_act(a, Ca, up_a, b, Cb, H, W, w_kcrs, bias, K, relu ? 1 : 0, 0.0f, mode, out,
+                         a_halo_top, a_halo_bot, b_halo_top, b_halo_bot);
 }
 
 /* 2x2 / stride 2 max pool, floor output size, -inf start value
@@ -233,6 +258,13 @@ ORC_API int orc_relu(const uint16_t *in, int64_t n, uint16_t *out) {
   return 0;
 }
 
+/* standalone LeakyReLU (basic_activation.comp:29-30). */
+ORC_API int orc_leaky_relu(const uint16_t *in, int64_t n, float alpha, uint16_t *out) {
+#pragma omp parallel for
+  for (int64_t i = 0; i < n; ++i) out[i] = activate_h(in[i], 2, alpha);
+  return 0;
+}
+
 /* Spatial pad with edge replication (memory_pad.comp:71-72: the source coordinate is the
  * output coordinate minus the pad, clamped to the input extent).  out is
  * (H + top + bottom) x (W + left + right) x C. */
@@ -259,6 +291,15 @@ ORC_API int orc_slice(const uint16_t *in, int H, int W, int C, int left, int top
   for (int h = 0; h < OH; ++h)
     memcpy(out + (int64_t)h * OW * C, in + ((int64_t)(h + top) * W + left) * C, (size_t)OW * C * 2);
   return 0;
+}
+
+/* Number of threads the parallel loops use from now on (n <= 0: leave as it is). */
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
 }
 
 ORC_API int orc_num_threads(void) {

@@ -34,6 +34,10 @@ def lib():
         vp, i = C.c_void_p, C.c_int
         _lib.orc_conv3x3.restype = i
         _lib.orc_conv3x3.argtypes = [vp, i, i, vp, i, i, i, vp, vp, i, i, i, vp, vp, vp, vp, vp]
+        _lib.orc_conv3x3_act.restype = i
+        _lib.orc_conv3x3_act.argtypes = [vp, i, i, vp, i, i, i, vp, vp, i, i, C.c_float, i, vp, vp, vp, vp, vp]
+        _lib.orc_leaky_relu.argtypes = [vp, C.c_int64, C.c_float, vp]
+        _lib.orc_set_num_threads.argtypes = [i]
         _lib.orc_maxpool2x2.argtypes = [vp, i, i, i, vp]
         _lib.orc_upsample2x.argtypes = [vp, i, i, i, vp]
         _lib.orc_concat.argtypes = [vp, i, vp, i, i, i, vp]
@@ -55,8 +59,10 @@ def _f16(a):
     return None if a is None else np.ascontiguousarray(a, dtype=np.float16)
 
 
-def conv3x3(a, w_kcrs, bias=None, relu=False, mode=ACC_F32, b=None, up_a=False, halo=(None, None, None, None)):
-    """a: [H(/2)][W(/2)][Ca], b: [H][W][Cb] or None, w: [K][Ca+Cb][3][3]; returns [H][W][K] binary16."""
+def conv3x3(a, w_kcrs, bias=None, relu=False, mode=ACC_F32, b=None, up_a=False, halo=(None, None, None, None),
+            leaky=None):
+    """a: [H(/2)][W(/2)][Ca], b: [H][W][Cb] or None, w: [K][Ca+Cb][3][3]; returns [H][W][K] binary16.
+    relu: max(0, x) on the finished sum; leaky=alpha: max(alpha * x, x) in binary16 instead."""
     a, b, w, bias = _f16(a), _f16(b), _f16(w_kcrs), _f16(bias)
     halo = [_f16(h) for h in halo]
     ca = a.shape[2]
@@ -67,8 +73,9 @@ def conv3x3(a, w_kcrs, bias=None, relu=False, mode=ACC_F32, b=None, up_a=False, 
     k = w.shape[0]
     assert w.shape == (k, ca + cb, 3, 3), (w.shape, ca, cb)
     out = np.empty((h, wd, k), dtype=np.float16)
-    st = lib().orc_conv3x3(_p(a), ca, int(up_a), _p(b), cb, h, wd, _p(w), _p(bias), k, int(relu), mode, _p(out),
-                           *[_p(x) for x in halo])
+    act = 2 if leaky is not None else (1 if relu else 0)
+    st = lib().orc_conv3x3_act(_p(a), ca, int(up_a), _p(b), cb, h, wd, _p(w), _p(bias), k, act,
+                               float(leaky or 0.0), mode, _p(out), *[_p(x) for x in halo])
     assert st == 0, st
     return out
 
@@ -101,6 +108,13 @@ def relu(x):
     x = _f16(x)
     out = np.empty_like(x)
     lib().orc_relu(_p(x), x.size, _p(out))
+    return out
+
+
+def leaky_relu(x, alpha):
+    x = _f16(x)
+    out = np.empty_like(x)
+    lib().orc_leaky_relu(_p(x), x.size, float(alpha), _p(out))
     return out
 
 
@@ -142,24 +156,26 @@ def num_threads():
     return lib().orc_num_threads()
 
 
+def set_num_threads(n):
+    """Threads of the oracle's parallel loops from now on (OMP_NUM_THREADS=1, which process launchers like to
+    export, would otherwise make a timing of the oracle a one core figure)."""
+    lib().orc_set_num_threads(int(n))
+
+
 def run_network(net, x, mode=ACC_F32):
     """Runs a denox_b200.nets.Net node by node (un-fused, the reference's own
     dispatch granularity).  Returns {tensor id: array} for every tensor."""
-    CONV, RELU, MAXPOOL, UPSAMPLE, CONCAT = 1, 2, 3, 4, 5
+    CONV, RELU, MAXPOOL, UPSAMPLE, CONCAT, LEAKY_RELU = 1, 2, 3, 4, 5, 6
     t = {net.input_tensor: _f16(x)}
-    # a conv directly followed by its relu is evaluated as one fused call, as the
-    # reference does (ReLU on the accumulator, direct_conv.comp:559-590)
-    relu_of = {nd.in0: nd for nd in net.nodes if nd.kind == RELU}
+    # the activation works on the rounded sum in binary16, so a conv followed by its activation gives the same
+    # bits fused (ReLU on the accumulator, direct_conv.comp:559-590) or as two steps
     for nd in net.nodes:
         if nd.kind == CONV:
-            fuse = nd.out in relu_of
-            y = conv3x3(t[nd.in0], nd.weights, nd.bias, relu=False, mode=mode)
-            t[nd.out] = y
-            if fuse:
-                t[relu_of[nd.out].out] = relu(y)
+            t[nd.out] = conv3x3(t[nd.in0], nd.weights, nd.bias, relu=False, mode=mode)
         elif nd.kind == RELU:
-            if nd.out not in t:
-                t[nd.out] = relu(t[nd.in0])
+            t[nd.out] = relu(t[nd.in0])
+        elif nd.kind == LEAKY_RELU:
+            t[nd.out] = leaky_relu(t[nd.in0], nd.alpha)
         elif nd.kind == MAXPOOL:
             t[nd.out] = maxpool2x2(t[nd.in0])
         elif nd.kind == UPSAMPLE:

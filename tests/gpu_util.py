@@ -50,7 +50,8 @@ class Guarded:
         return host(self.view)
 
 
-def run_conv(variant, a, w_kcrs, bias=None, relu=False, b=None, up_a=False, pool=False, full=True, halo=None):
+def run_conv(variant, a, w_kcrs, bias=None, relu=False, b=None, up_a=False, pool=False, full=True, halo=None,
+             leaky=None, planned=False):
     """Launches one conv dispatch through dnxcu_launch; returns (out, out_pool) as numpy (None when not written)."""
     ca = a.shape[2]
     cb = 0 if b is None else b.shape[2]
@@ -59,7 +60,8 @@ def run_conv(variant, a, w_kcrs, bias=None, relu=False, b=None, up_a=False, pool
     d = lib.Dispatch()
     d.variant = variant
     d.flags = (lib.F_RELU if relu else 0) | (lib.F_BIAS if bias is not None else 0) | (lib.F_UP2X_A if up_a else 0) \
-        | (lib.F_POOL_OUT if pool else 0) | (0 if full else lib.F_NO_FULL_OUT)
+        | (lib.F_POOL_OUT if pool else 0) | (0 if full else lib.F_NO_FULL_OUT) | (lib.F_LEAKY if leaky is not None else 0)
+    d.leaky_alpha = float(leaky or 0.0)
     d.pc[0], d.pc[1] = w, h
     d.c_a, d.c_b, d.c_out = ca, cb, k
     keep = []
@@ -82,15 +84,26 @@ def run_conv(variant, a, w_kcrs, bias=None, relu=False, b=None, up_a=False, pool
     if outp is not None:
         d.out_pool = outp.ptr()
     torch.cuda.synchronize()
-    lib.check(lib.L.dnxcu_launch(C.byref(d), None), f"dnxcu_launch variant {variant}")
+    if planned:  # plan once, launch twice: the second launch must give the same bits as the first
+        plan = C.c_void_p()
+        lib.check(lib.L.dnxcu_plan_create(C.byref(d), C.byref(plan)), f"dnxcu_plan_create variant {variant}")
+        lib.check(lib.L.dnxcu_plan_launch(plan, None), "dnxcu_plan_launch")
+        lib.check(lib.L.dnxcu_plan_launch(plan, None), "dnxcu_plan_launch (second)")
+        torch.cuda.synchronize()
+        lib.L.dnxcu_plan_destroy(plan)
+    else:
+        lib.check(lib.L.dnxcu_launch(C.byref(d), None), f"dnxcu_launch variant {variant}")
     torch.cuda.synchronize()
     assert int(status[0].item()) == 0, f"kernel reported a bounded wait that ran out: code {int(status[0].item())}"
     return (out.check() if out else None), (outp.check() if outp else None)
 
 
-def run_mem(variant, a, b=None):
+def run_mem(variant, a, b=None, leaky=None):
     d = lib.Dispatch()
     d.variant = variant
+    if leaky is not None:
+        d.flags = lib.F_LEAKY
+        d.leaky_alpha = float(leaky)
     h, w, ca = a.shape
     d.pc[0], d.pc[1] = w, h
     d.c_a = ca

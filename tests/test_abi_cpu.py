@@ -47,9 +47,12 @@ def test_variant_table():
 
 def test_sha256_known_answer():
     # identity hashing must be real SHA-256: check through the variant hash of known content
+    # the third component is the digest of the kernel sources the library was built from: editing a kernel
+    # changes every variant's identity (GlslCompilerInstance::fast_sha256 hashes the shader source the same way)
     import hashlib
+    from denox_b200 import build
     v = lib.variants()[0]
-    expect = hashlib.sha256(f"{v['family']}\n{v['config']}\ndnxcu-kernels-1\n".encode()).hexdigest()
+    expect = hashlib.sha256(f"{v['family']}\n{v['config']}\n{build.source_digest()}\n".encode()).hexdigest()
     assert lib.variant_sha256(0) == expect
 
 
@@ -185,9 +188,9 @@ def test_db_bookkeeping(tmp_path):
     db = lib.Db(path)
     assert len(db) == 0
     net = nets.oidn_unet()
-    added = db.populate(net, 1088, 1920)
+    added = db.populate(net, 1088, 1920, device=-1)
     assert added > 16 and len(db) == added
-    assert db.populate(net, 1088, 1920) == 0  # populate extends, never duplicates (README.md:120-124 of the reference)
+    assert db.populate(net, 1088, 1920, device=-1) == 0  # populate extends, never duplicates (README.md:120-124 of the reference)
     d = _conv_dispatch(2)
     assert db.query(d) is None  # never sampled
     db.add_result(d, [1.0, 2.0, 3.0])
@@ -233,3 +236,52 @@ def test_prepare_weights_stacked_split_layout():
                 for ch in range(2):
                     want = w[part * 48:(part + 1) * 48, ch * 8:(ch + 1) * 8, r, sx]
                     assert (t[part, sx, ch, 2 - r] == want).all()
+
+
+def test_leaky_relu_flag_rules():
+    ok = lib.L.dnxcu_validate
+    d = _conv_dispatch(2)
+    d.flags = lib.F_LEAKY
+    d.leaky_alpha = 0.1
+    assert ok(C.byref(d)) == 0
+    d.flags = lib.F_LEAKY | lib.F_RELU  # one activation per dispatch
+    assert ok(C.byref(d)) == lib.E_BAD_ARG
+    a = lib.Dispatch()
+    a.variant, a.c_a, a.flags = lib.find_variant("basic-activation", "VEC=1"), 9, lib.F_LEAKY
+    a.pc[0], a.pc[1] = 20, 10
+    a.in_a = a.out = 0x1000
+    assert ok(C.byref(a)) == 0
+    p = lib.Dispatch()
+    p.variant, p.c_a, p.flags = lib.find_variant("basic-pool", "VEC=1"), 9, lib.F_LEAKY
+    p.pc[0], p.pc[1] = 20, 10
+    p.in_a = p.out = 0x1000
+    assert ok(C.byref(p)) == lib.E_UNSUPPORTED
+
+
+def test_pool_fusion_depends_on_a_variant_taking_it(tmp_path):
+    """conv(-> 1024) + relu + maxpool: no variant with a pooling epilogue takes 1024 output channels, so the pool
+    stays a dispatch of its own; with 64 output channels it is fused away."""
+    def net_with(k):
+        n = nets._start("wide", 8)
+        x = n.conv(0, k, name="c0")
+        p = n.pool(x, "pool")
+        n.output_tensor = n.conv(p, 8, relu=False, name="c1")
+        return n
+    pool_ids = {v["id"] for v in lib.variants() if v["op"] == lib.OP_MAXPOOL2X2}
+
+    # populated candidates: with the pool fused there is no basic-pool entry, so adding both pool variants
+    # by hand grows the database by two; un-fused they are there already
+    def grows_by(k):
+        db = lib.Db(tmp_path / f"g{k}.db")
+        n0 = db.populate(net_with(k), 32, 32, device=-1)
+        for vid in pool_ids:
+            d = lib.Dispatch()
+            d.variant, d.c_a = vid, k
+            d.pc[0], d.pc[1] = 32, 32
+            db.add_result(d, [1.0])
+        grown = len(db) - n0
+        db.close()
+        return grown
+
+    assert grows_by(64) == len(pool_ids)
+    assert grows_by(1024) == 0

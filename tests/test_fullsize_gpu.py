@@ -34,7 +34,20 @@ CASES = [
     ("up96_cat32_k64", H // 2, W // 2, 96, 32, 64, True, False, True, False),
     ("c96_k96", H // 4, W // 4, 96, 0, 96, True, False, False, False),
     ("up112_cat48_k96", H // 4, W // 4, 112, 48, 96, True, False, True, False),
+    # the remaining layer shapes of the benchmark net
+    ("c32_k48_pool", H // 2, W // 2, 32, 0, 48, True, False, False, True),
+    ("c48_k64_pool", H // 4, W // 4, 48, 0, 64, True, False, False, True),
+    ("c64_k80_pool_dual", H // 8, W // 8, 64, 0, 80, True, False, False, True),
+    ("c80_k96", H // 16, W // 16, 80, 0, 96, True, False, False, False),
+    ("c96_k96_small", H // 16, W // 16, 96, 0, 96, True, False, False, False),
+    ("up96_cat80_k112", H // 8, W // 8, 96, 80, 112, True, False, True, False),
+    ("c112_k112", H // 8, W // 8, 112, 0, 112, True, False, False, False),
+    ("c64_k64_half", H // 2, W // 2, 64, 0, 64, True, False, False, False),
+    ("c96_k96_leaky", H // 4, W // 4, 96, 0, 96, False, True, False, False),
 ]
+LEAKY = {"c96_k96_leaky": 0.1}
+# variants that must be among those that run a case (the ones the benchmark database picks there)
+MUST_RUN = {"up96_cat80_k112": ["R=2#KG=2#W=stream3"], "c112_k112": ["DY=stack#KG=2#W=resident#NSPLIT=2"]}
 
 
 def _tensor(seed, shape):
@@ -43,18 +56,20 @@ def _tensor(seed, shape):
     return (torch.rand(shape, generator=g, device="cuda", dtype=torch.float32) * 2 - 1).to(torch.float16)
 
 
-def _launch(variant, case, ta, tb, wt, tbias):
+def _launch(variant, case, ta, tb, wt, tbias, full=True):
     name, h, w, ca, cb, k, relu, bias, up, pool = case
     d = lib.Dispatch()
     d.variant = variant
     d.flags = (lib.F_RELU if relu else 0) | (lib.F_BIAS if bias else 0) | (lib.F_UP2X_A if up else 0) | \
-        (lib.F_POOL_OUT if pool else 0)
+        (lib.F_POOL_OUT if pool else 0) | (0 if full else lib.F_NO_FULL_OUT) | (lib.F_LEAKY if name in LEAKY else 0)
+    d.leaky_alpha = LEAKY.get(name, 0.0)
     d.pc[0], d.pc[1] = w, h
     d.c_a, d.c_b, d.c_out = ca, cb, k
     d.in_a = ta.data_ptr()
     d.in_b = tb.data_ptr() if tb is not None else None
     d.bias = tbias.data_ptr() if tbias is not None else None
-    d.weights = d.out = 0x1000
+    d.weights = 0x1000
+    d.out = 0x1000 if full else None
     d.out_pool = 0x1000 if pool else None
     if lib.L.dnxcu_validate(C.byref(d)) != 0:
         return None
@@ -62,9 +77,9 @@ def _launch(variant, case, ta, tb, wt, tbias):
     d.weights = tw.data_ptr()
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     d.device_status = status.data_ptr()
-    out = Guarded((h, w, k))
+    out = Guarded((h, w, k)) if full else None
     outp = Guarded((h // 2, w // 2, k)) if pool else None
-    d.out = out.ptr()
+    d.out = out.ptr() if full else None
     d.out_pool = outp.ptr() if pool else None
     lib.check(lib.L.dnxcu_launch(C.byref(d), None))
     torch.cuda.synchronize()
@@ -73,7 +88,7 @@ def _launch(variant, case, ta, tb, wt, tbias):
         if gbuf is not None:
             b = gbuf.buf
             assert bool((b[:gbuf.pad] == 12345.0).all()) and bool((b[-gbuf.pad:] == 12345.0).all()), "canary damaged"
-    return out.view, (outp.view if pool else None)
+    return (out.view if full else None), (outp.view if pool else None)
 
 
 def _within_ulps(got, ref, n):
@@ -104,7 +119,7 @@ def test_fullsize_conv(case):
         c0, c1 = max(0, r0 - 2), min(h, r1 + 2)  # even: r0, r1 are
         a_np = (ta[c0 // 2:c1 // 2] if up else ta[c0:c1]).cpu().numpy()
         b_np = tb[c0:c1].cpu().numpy() if cb else None
-        o = oracle.conv3x3(a_np, wt, bs, relu=relu, mode=oracle.ACC_F32, b=b_np, up_a=up)
+        o = oracle.conv3x3(a_np, wt, bs, relu=relu, mode=oracle.ACC_F32, b=b_np, up_a=up, leaky=LEAKY.get(name))
         # rows whose window the crop cut are not comparable
         lo = 0 if c0 == 0 else 1
         hi = (c1 - c0) if c1 == h else (c1 - c0 - 1)
@@ -112,14 +127,14 @@ def test_fullsize_conv(case):
         ok = _within_ulps(got, torch.from_numpy(o[lo:hi]).cuda(), 1)
         assert bool(ok.all()), (name, "direct kernel vs oracle rows", c0 + lo, c0 + hi, int((~ok).sum()))
 
-    ran = 0
+    ran = []
     for v in variants:
         if v["op"] != lib.OP_CONV3X3 or not v["needs_tcgen05"]:
             continue
         res = _launch(v["id"], case, ta, tb, wt, tbias)
         if res is None:
             continue
-        ran += 1
+        ran.append(v["config"])
         y, yp = res
         ok = _within_ulps(y, ref, 2)
         nbad = int((~ok).sum())
@@ -128,7 +143,12 @@ def test_fullsize_conv(case):
         if pool:
             want = torch.maximum(torch.maximum(y[0::2, 0::2], y[0::2, 1::2]), torch.maximum(y[1::2, 0::2], y[1::2, 1::2]))
             assert bool((yp == want).all()), (name, v["config"], "pooled output is not the 2x2 max of the full output")
-    assert ran > 0, "no tensor core variant took this dispatch"
+            # pooled output alone (the form the encoder layers run in): the same bits without the full tensor
+            _, yp_only = _launch(v["id"], case, ta, tb, wt, tbias, full=False)
+            assert bool((yp_only == yp).all()), (name, v["config"], "pooled-only output differs from the dual output form")
+    assert ran, "no tensor core variant took this dispatch"
+    for cfg in MUST_RUN.get(name, []):
+        assert cfg in ran, (name, "variant did not take the dispatch", cfg, ran)
 
 
 def test_fullsize_network_tensor_core_against_cuda_core():
@@ -151,3 +171,46 @@ def test_fullsize_network_tensor_core_against_cuda_core():
     assert bad.mean() <= 1e-3, (float(bad.mean()), float(d.max()))
     for o in (i_tc, i_cc, m_tc, m_cc):
         o.close()
+
+
+def test_fullsize_network_against_oracle_with_report():
+    """The whole OIDN-style net at 1088 x 1920 against the CPU oracle itself: end to end (free running) with
+    binary16 accumulation (the reference's arithmetic: at most 0.5 % of the elements outside the acceptance rule)
+    and with fp32 accumulation (none outside), and every layer teacher forced (the oracle recomputes the layer
+    from the GPU's own input tensors).  The table is written out as a report."""
+    import parity_util
+    net = nets.oidn_unet()
+    x = nets.oidn_input(1006, H, W)
+    model = lib.Model(net)
+    inst = lib.Instance(model, H, W)
+    y = inst.infer(x)
+    rep = parity_util.report(net, x, inst, y)
+    parity_util.save(rep, "parity_oidn_1088x1920")
+    print(parity_util.to_markdown(rep, "OIDN-style U-Net 1088 x 1920"))
+    e = rep["end_to_end"]
+    assert e["acc=f32"]["violation_fraction"] == 0.0, e
+    assert e["acc=f16"]["violation_fraction"] <= 5e-3, e
+    for r in rep["layers"]:
+        assert r["acc=f32"]["violation_fraction"] == 0.0, r
+        assert r["acc=f16"]["violation_fraction"] <= 1e-3, r
+        # one rounding apart from the fp32 oracle on identical inputs: a binary16 ulp of the largest activations
+        assert r["acc=f32"]["max"] <= 0.05, r
+    inst.close()
+    model.close()
+
+
+def test_small_network_report():
+    """The same report for the CPU-runnable configuration (tiny U-Net, 128 x 128)."""
+    import parity_util
+    net = nets.tiny_unet()
+    x = nets.tiny_input(1000, 128, 128)
+    model = lib.Model(net)
+    inst = lib.Instance(model, 128, 128)
+    y = inst.infer(x)
+    rep = parity_util.report(net, x, inst, y)
+    parity_util.save(rep, "parity_tiny_128x128")
+    assert rep["end_to_end"]["acc=f32"]["violation_fraction"] == 0.0
+    assert rep["end_to_end"]["acc=f16"]["violation_fraction"] <= 1e-3
+    assert len(rep["layers"]) >= 4
+    inst.close()
+    model.close()

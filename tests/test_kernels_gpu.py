@@ -58,6 +58,45 @@ def test_conv_against_oracle_and_golden(variant, case):
 
 
 @pytest.mark.parametrize("variant", CONV_VARIANTS)
+@pytest.mark.parametrize("case", mg.CONV_CASES2, ids=[c[0] for c in mg.CONV_CASES2])
+def test_conv_more_shapes_and_leaky_relu(variant, case):
+    """The remaining channel pairs of the reference's conv test list (test/system/test_conv.py, up to 256 -> 256,
+    bias on) and LeakyReLU epilogues, launched through a plan that is used twice."""
+    from gpu_util import run_conv
+    name, h, w, ca, cb, k, relu, bias, up, leaky = case
+    flags = (lib.F_RELU if relu else 0) | (lib.F_BIAS if bias else 0) | (lib.F_UP2X_A if up else 0) | \
+        (lib.F_LEAKY if leaky is not None else 0)
+    if not supports(variant, flags, ca, cb, k, h, w):
+        pytest.skip("variant does not take this dispatch")
+    a, b, wt, bs = mg.conv_case_tensors(case)
+    y, _ = run_conv(variant, a, wt, bs, relu=relu, b=b, up_a=up, leaky=leaky, planned=True)
+    ref32 = oracle.conv3x3(a, wt, bs, relu=relu, mode=oracle.ACC_F32, b=b, up_a=up, leaky=leaky)
+    assert one_ulp(y, ref32).all(), (name, np.abs(y.astype(np.float32) - ref32.astype(np.float32)).max())
+    ref16 = oracle.conv3x3(a, wt, bs, relu=relu, mode=oracle.ACC_F16, b=b, up_a=up, leaky=leaky)
+    if ca + cb >= 256:  # the reference's own tests relax to atol = 1e-1 here (test_conv.py:113-123)
+        assert (np.abs(y.astype(np.float32) - ref16.astype(np.float32)) <= 1e-1).all()
+    else:
+        assert_close(y, ref16, f"{name} vs acc=f16 oracle", max_violation_fraction=5e-3)
+    assert_close(y, GOLD["conv/" + name], f"{name} vs PyTorch golden")
+
+
+@pytest.mark.parametrize("c", [8, 24, 9])
+def test_leaky_relu_standalone_bit_exact(c):
+    from gpu_util import run_mem
+    h, w = 12, 20
+    x = rng.to_f16(rng.uniform(9100 if c == 24 else 9200 + c, h * w * c, -8.0, 8.0)).reshape(h, w, c)
+    x[0, 0, :3] = [0.0, -0.0, -6e-8]
+    for v in lib.variants():
+        if v["op"] != lib.OP_RELU or (v["config"] == "VEC=8" and (h * w * c) % 8):
+            continue
+        for alpha in (0.3, 0.01):
+            got = run_mem(v["id"], x, leaky=alpha)
+            assert (got.view(np.uint16) == oracle.leaky_relu(x, alpha).view(np.uint16)).all(), (v["config"], alpha)
+    if c == 24:
+        assert_close(oracle.leaky_relu(x, 0.3)[1:], GOLD["leaky/standalone_c24"][1:], "leaky vs PyTorch golden")
+
+
+@pytest.mark.parametrize("variant", CONV_VARIANTS)
 @pytest.mark.parametrize("shape", [(16, 128, 32, 32), (18, 130, 16, 48), (34, 300, 48, 64), (16, 16, 64, 80),
                                    (2, 2, 16, 16), (6, 1922 // 2 * 2, 32, 32)])
 def test_conv_pool_epilogue(variant, shape):

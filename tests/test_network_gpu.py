@@ -65,6 +65,84 @@ def test_network_matches_oracle_and_golden(which, shape, seed, key, options):
     model.close()
 
 
+@pytest.mark.parametrize("key,seed,shape", [("ref_unet_32x48/out", 1010, (32, 48)), ("ref_unet_40x52/out", 1011, (40, 52))])
+def test_reference_model_file_output(key, seed, shape):
+    """The GPU schedule against the output of the reference's own PyTorch module (oidn_model.py UNet behind
+    UNetAlignment, run when the fixture was made): its channel list (160 = 96 + 64 into the first decoder conv),
+    biases on every conv, an aligned extent and one that runs behind pad and slice."""
+    net = nets.oidn_unet_reference()
+    x = nets.oidn_input(seed, *shape)
+    model = lib.Model(net)
+    inst = lib.Instance(model, *shape)
+    y = inst.infer(x)
+    assert_close(y, GOLD[key], f"{key}: GPU vs the reference's PyTorch module")
+    ref32 = oracle.run_network_aligned(net, x, 16, oracle.ACC_F32)
+    assert_close(y, ref32, f"{key}: GPU vs acc=f32 oracle")
+    inst.close()
+    model.close()
+
+
+def test_tiny_net_with_leaky_relu():
+    net = nets.tiny_unet(leaky=0.1)
+    x = nets.tiny_input(1003, 32, 48)
+    ref = oracle.run_network(net, x, oracle.ACC_F32)
+    for options in (0, lib.OPT_NO_TCGEN05, lib.OPT_NO_FUSE_ACTIVATION):
+        model = lib.Model(net, options=options)
+        inst = lib.Instance(model, 32, 48)
+        y = inst.infer(x)
+        names = [i.name.decode() for i in inst.dispatch_info()]
+        assert_close(y, ref[net.output_tensor], f"tiny leaky, options {options}")
+        assert_close(y, GOLD["tiny_leaky/out"], f"tiny leaky vs PyTorch golden, options {options}")
+        if options == lib.OPT_NO_FUSE_ACTIVATION:
+            assert any("basic-activation(leaky)" in n for n in names), names
+        else:
+            assert any("+leaky" in n for n in names), names
+        inst.close()
+        model.close()
+
+
+def test_wide_conv_before_pool_runs_unfused():
+    """conv(-> 1024) + relu + maxpool: no variant with a pooling epilogue takes 1024 output channels, so the
+    schedule keeps conv (CUDA core variant) and basic-pool apart instead of refusing the model."""
+    n = nets._start("wide", 8)
+    x = n.conv(0, 1024, name="wide_conv")
+    p = n.pool(x, "pool")
+    o = n.conv(p, 8, relu=False, name="out_conv")
+    n.output_tensor = o
+    frame = nets.rng.to_f16(nets.rng.uniform(31, 16 * 24 * 8, -1, 1)).reshape(16, 24, 8)
+    model = lib.Model(n)
+    inst = lib.Instance(model, 16, 24)
+    names = [i.name.decode() for i in inst.dispatch_info()]
+    assert any(nm.startswith("basic-pool") for nm in names), names
+    y = inst.infer(frame)
+    ref = oracle.run_network(n, frame, oracle.ACC_F32)[n.output_tensor]
+    assert_close(y, ref, "conv(->1024)+pool, un-fused")
+    inst.close()
+    model.close()
+
+
+def test_enqueue_caches_graphs_per_pointer_pair_and_clears_nothing():
+    """Device resident enqueue with two alternating (input, output) pairs: both replay from their own graph,
+    results equal the host path's."""
+    import torch
+    net = nets.tiny_unet()
+    model = lib.Model(net)
+    inst = lib.Instance(model, 64, 128)
+    xs = [nets.tiny_input(40 + i, 64, 128) for i in range(2)]
+    want = [inst.infer(x) for x in xs]
+    din = [torch.from_numpy(x).cuda() for x in xs]
+    dout = [torch.empty((64, 128, 3), dtype=torch.float16, device="cuda") for _ in xs]
+    s = torch.cuda.Stream()
+    for rep in range(3):
+        for i in range(2):
+            inst.enqueue(din[i].data_ptr(), dout[i].data_ptr(), s.cuda_stream)
+    s.synchronize()
+    for i in range(2):
+        assert (dout[i].cpu().numpy() == want[i]).all()
+    inst.close()
+    model.close()
+
+
 def test_oidn_larger_frame_properties():
     """At a size the oracle still finishes in seconds: 96 x 256."""
     net = nets.oidn_unet()

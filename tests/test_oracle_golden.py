@@ -48,6 +48,60 @@ def test_conv_f16_accumulation_within_reference_tolerance(case, mode):
     assert ok.mean() > 0.999, (name, float(1 - ok.mean()))
 
 
+@pytest.mark.parametrize("case", mg.CONV_CASES2, ids=[c[0] for c in mg.CONV_CASES2])
+def test_more_shapes_and_leaky_relu_match_torch(case):
+    """The remaining channel pairs of the reference's conv test list (up to 256 -> 256) and LeakyReLU epilogues."""
+    name, h, w, ca, cb, k, relu, bias, up, leaky = case
+    a, b, wt, bs = mg.conv_case_tensors(case)
+    ref = GOLD["conv/" + name]
+    y = oracle.conv3x3(a, wt, bs, relu=relu, mode=oracle.ACC_F32, b=b, up_a=up, leaky=leaky)
+    assert y.shape == ref.shape == (h, w, k)
+    assert ref_allclose(y, ref).all()
+    d = np.abs(y.astype(np.float32) - ref.astype(np.float32))
+    # PyTorch applies the slope to the fp32 sum, the oracle (like the reference) to the rounded sum: two ulps
+    ulps = 2.0 if leaky is not None else 1.0
+    assert (d <= ulps * np.maximum(np.abs(ref.astype(np.float32)) * 2.0 ** -10, 2.0 ** -14)).all()
+    # binary16 accumulation: the reference's own tests relax to atol = 1e-1 at 256 channels (test_conv.py:113-123)
+    y16 = oracle.conv3x3(a, wt, bs, relu=relu, mode=oracle.ACC_F16, b=b, up_a=up, leaky=leaky)
+    if ca + cb >= 256:
+        assert ref_allclose(y16, ref, rtol=0.0, atol=1e-1).all()
+    else:
+        assert ref_allclose(y16, ref, rtol=1e-2, atol=2e-2).mean() > 0.995, name
+
+
+def test_leaky_relu_standalone_and_zero_signs():
+    xs = mg.rng.to_f16(mg.rng.uniform(9100, 12 * 20 * 24, -8.0, 8.0)).reshape(12, 20, 24)
+    y = oracle.leaky_relu(xs, 0.3)
+    assert ref_allclose(y, GOLD["leaky/standalone_c24"], rtol=1e-3, atol=1e-4).all()
+    z = np.array([0.0, -0.0, -6e-8, 1.0, -1.0], dtype=np.float16)
+    got = oracle.leaky_relu(z, 0.1).view(np.uint16)
+    # +0 stays +0, -0 stays -0, a product that underflows becomes -0, negative values scale
+    assert list(got[:3]) == [0x0000, 0x8000, 0x8000] and got[3] == np.float16(1.0).view(np.uint16)
+    assert oracle.leaky_relu(z, 0.1)[4] == np.float16(-0.1)
+
+
+def test_tiny_net_with_leaky_relu_matches_torch():
+    net = nets.tiny_unet(leaky=0.1)
+    x = nets.tiny_input(1003, 32, 48)
+    y = oracle.run_network(net, x, oracle.ACC_F32)[net.output_tensor]
+    assert ref_allclose(y, GOLD["tiny_leaky/out"]).all()
+
+
+@pytest.mark.parametrize("key,seed,shape", [("ref_unet_32x48/out", 1010, (32, 48)), ("ref_unet_40x52/out", 1011, (40, 52))])
+def test_reference_model_file_output(key, seed, shape):
+    """The oracle against the output of the reference's own PyTorch module (oidn_model.py UNet + UNetAlignment,
+    run in binary16 when the fixture was made), its channel list (first decoder conv 160 = 96 + 64), biases on,
+    an aligned and an unaligned extent."""
+    net = nets.oidn_unet_reference()
+    x = nets.oidn_input(seed, *shape)
+    ref = GOLD[key]
+    y32 = oracle.run_network_aligned(net, x, 16, oracle.ACC_F32)
+    assert y32.shape == ref.shape == shape + (3,)
+    assert ref_allclose(y32, ref).all()           # the reference's own test tolerance (test/__init__.py:48-49)
+    y16 = oracle.run_network_aligned(net, x, 16, oracle.ACC_F16)
+    assert ref_allclose(y16, ref, rtol=1e-2, atol=2e-2).mean() > 0.9  # 16 layers of binary16 accumulation drift
+
+
 def test_concat_phase_order_equals_explicit_concat_in_f32():
     case = next(c for c in mg.CONV_CASES if c[0] == "cat32_16_k16")
     a, b, wt, bs = mg.conv_case_tensors(case)

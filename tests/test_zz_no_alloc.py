@@ -11,6 +11,7 @@ import numpy as np
 import pytest
 
 from denox_b200 import lib, rng
+from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -50,6 +51,9 @@ def test_static_scratch_matches_fused_dispatch_twice_in_a_row():
         # both accumulate in fp32 and round once; the summation order differs: one binary16 ulp
         assert (np.abs(g - r) <= np.maximum(np.abs(r) * 2.0 ** -10, 2.0 ** -14) * 1.01).all()
         assert np.isfinite(g).all()
+        # and against the CPU oracle (conv + ReLU, then 2x2 max pool), the same bound
+        o = oracle.maxpool2x2(oracle.conv3x3(a, wt, bs, relu=True, mode=oracle.ACC_F32)).astype(np.float32)
+        assert (np.abs(g - o) <= np.maximum(np.abs(o) * 2.0 ** -10, 2.0 ** -14) * 1.01).all()
 
 
 def test_static_scratch_rejects_oversized_and_bad_arguments():
