@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libdnxcu.so")
-SOURCES = ["api.cu", "kernels_mem.cu", "conv_direct.cu", "conv_tc.cu", "runtime.cu", "db.cu", "static_scratch.cu"]
+SOURCES = ["api.cu", "kernels_mem.cu", "conv_direct.cu", "conv_tc.cu", "runtime.cu", "db.cu", "static_scratch.cu", "halo_xchg.cu", "select.cu", "supergraph.cu"]
 
 
 def nvcc_path():

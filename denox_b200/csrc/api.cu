@@ -116,6 +116,8 @@ static const Variant kVariants[] = {
     {{25, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=1#W=resident#PIPES=1", CONV_ALL, 1, 1, 1, 128, 0}, VK_CONV_TC, 0, 1, 2, 0},
     {{26, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=2#W=resident#NSPLIT=3", CONV_ALL, 1, 1, 16, 256, 0}, VK_CONV_TC, 0, 2, 0, 3},
     {{27, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=2#W=resident#NSPLIT=4", CONV_ALL, 1, 1, 16, 256, 0}, VK_CONV_TC, 0, 2, 0, 4},
+    {{28, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=1#W=resident#ER=2", CONV_ALL, 1, 8, 1, 128, 0}, VK_CONV_TC, 0, 1, 0, 0, 2},
+    {{29, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=1#W=resident#PIPES=1#ER=2", CONV_ALL, 1, 8, 1, 128, 0}, VK_CONV_TC, 0, 1, 2, 0, 2},
 };
 static const int kVariantCount = (int)(sizeof(kVariants) / sizeof(kVariants[0]));
 

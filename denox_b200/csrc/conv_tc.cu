@@ -77,6 +77,8 @@ struct Seg {
   int up;
   int tma;            // rows of this operand are fetched by TMA (tensor map below)
   int tbox;           // 8 channel chunks per TMA copy (box extent of the tensor map's chunk dimension)
+  int rg;             // ragged operand (C not a multiple of 8, at most 16 channels): its rows are fetched as raw
+                      // bytes by a bulk copy and re-laid into the chunk layout inside shared memory
 };
 
 struct TcArgs {
@@ -105,6 +107,7 @@ struct TcArgs {
   int cpa;               // producer warps copy part of the rows (cp.async) besides TMA
   int NB;                // stacked form: accumulator blocks in the TMEM ring (per pipeline)
   int P;                 // stacked form: pipelines per CTA (1 or 2)
+  int ER;                // stacked form: input rows per ring entry (1, or 2: one wait, one descriptor, one slot release per two rows)
   int xp;                // stacked form: operand a (2x upsampled) comes by TMA at half resolution and is expanded in shared memory
   uint32_t src_bytes;    // expand mode: bytes of one half resolution staging buffer (one per slot)
   int stage_pitch;       // stacked form: bytes per pixel row of an epilogue warp's staging tile, 0 = direct stores
@@ -360,10 +363,31 @@ __device__ __forceinline__ void cp_async_wait_dyn(int n) {
 // producer warps copy it): the operand has a tensor map and the row is not one
 // of the separately stored halo rows of a row band.
 __device__ __forceinline__ bool row_by_tma(const TcArgs &g, const Seg &s, int iy) {
-  if (!s.tma) return false;
+  if (!s.tma && !s.rg) return false;
   if (iy == -1 && s.top) return false;
   if (iy == g.H && s.bot) return false;
   return true;
+}
+
+// Raw byte span of a ragged operand's row for the strip starting at x0 (pixels x0-1 .. x0+128 clipped to the
+// image): the first fetched pixel, the 16 byte aligned source address, the bytes in front of the first pixel
+// and the copy size (a multiple of 16; the tensor's byte size is one too, so the copy stays inside it).
+struct RawSpan {
+  const unsigned char *src;
+  int xs;          // first pixel fetched
+  uint32_t lead;   // bytes between the aligned source address and pixel xs
+  uint32_t bytes;  // copy size
+};
+__device__ __forceinline__ RawSpan raw_span(const TcArgs &g, const Seg &s, int iy, int x0) {
+  RawSpan r;
+  r.xs = max(x0 - 1, 0);
+  const int xe = min(x0 + STRIP + 1, g.W);
+  const size_t start = ((size_t)iy * g.W + r.xs) * (size_t)s.C * 2u;
+  const unsigned char *p = reinterpret_cast<const unsigned char *>(s.ptr) + start;
+  r.lead = (uint32_t)(reinterpret_cast<uintptr_t>(p) & 15u);
+  r.src = p - r.lead;
+  r.bytes = (r.lead + (uint32_t)(xe - r.xs) * (uint32_t)s.C * 2u + 15u) & ~15u;
+  return r;
 }
 
 // TMA part of one ring entry: chunks [c_lo, c_hi) of input row iy, pixels x0-1 ..
@@ -380,7 +404,7 @@ __device__ __forceinline__ uint32_t tma_row(const TcArgs &g, uint32_t slot_addr,
     const Seg &s = sg ? g.b : g.a;
     if (s.nch == 0) continue;
     const int lo = max(c_lo - chbase, 0), hi = min(c_hi - chbase, s.nch);
-    if (hi > lo && row_by_tma(g, s, iy)) {
+    if (hi > lo && s.tma && row_by_tma(g, s, iy)) {
       const void *tm = sg ? (const void *)&g.tm_b : (const void *)&g.tm_a;
 #pragma unroll 1
       for (int c = lo; c < hi; c += s.tbox) {
@@ -961,7 +985,8 @@ static_assert(ST_BAR_COUNT * 8 + 16 <= HEADER_BYTES, "header too small");
 constexpr int ST_OFF_TMEM_PTR = ST_BAR_COUNT * 8;
 constexpr int ST_OFF_ABORT = ST_OFF_TMEM_PTR + 4;
 // entry descriptors, one per slot (index: pipeline's barrier offset + slot), written by the descriptor threads
-constexpr int ST_DESC_BYTES = 48;
+constexpr int ST_SUBDESC_BYTES = 48;                  // one input row
+constexpr int ST_DESC_BYTES = 2 * ST_SUBDESC_BYTES;   // an entry holds one or two input rows (TcArgs::ER)
 constexpr int ST_OFF_DESC = HEADER_BYTES;
 constexpr int ST_HEADER_BYTES = HEADER_BYTES + MAX_SLOTS * ST_DESC_BYTES;
 static_assert(ST_HEADER_BYTES % 128 == 0, "weights must start on a 128 byte boundary");
@@ -1117,7 +1142,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   const int N = g.N, NB = g.NB, P = g.P;
   const uint32_t wdx_bytes = (uint32_t)nch * 3u * N * 16u;  // one horizontal tap: all chunks x 3N rows
   const uint32_t w_addr = sbase + ST_HEADER_BYTES;
-  const uint32_t slot_bytes = (uint32_t)g.gmax * CHUNK_PITCH;
+  const uint32_t row_bytes = (uint32_t)g.gmax * CHUNK_PITCH;  // one input row (of one K group) in a slot
+  const uint32_t slot_bytes = row_bytes * (uint32_t)g.ER;
   const uint32_t slots_addr0 = w_addr + ((wdx_bytes * 3u + 127u) & ~127u);
   const int S = g.S;  // slots per pipeline
   const int unit_stride = (int)gridDim.x * P;
@@ -1195,24 +1221,42 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     const uint32_t slots_addr = slots_addr0 + (uint32_t)(pipe * S) * slot_bytes;
     const int nca = g.a.nch;
     const int iy = is.t.y0 - 1 + is.jj;
-    const bool a_tma = row_by_tma(g, g.a, iy), b_tma = g.b.nch > 0 && row_by_tma(g, g.b, iy);
+    const bool a_eng = row_by_tma(g, g.a, iy), b_eng = g.b.nch > 0 && row_by_tma(g, g.b, iy);
+    const bool in_image = iy >= 0 && iy < g.H;
     const int c_lo = g.gc0[is.gi], c_hi = c_lo + g.gch[is.gi];
     const int a_lo = min(c_lo, nca), a_hi = min(c_hi, nca);  // operand a's chunks in this group
+    const int b_lo = max(c_lo, nca), b_hi = max(c_hi, nca);  // operand b's
     if (!mbar_wait<64>(bar(ST_BAR_EMPTY + bofs + is.slot), is.ephase, abort_flag, g.status, 7)) return false;
     const uint32_t slot_addr = slots_addr + (uint32_t)is.slot * slot_bytes;
     const uint32_t rb = bar(ST_BAR_RAW + bofs + is.slot);
+    // what the copy engine brings for this entry: per operand a half resolution row (upsampled operand), the row
+    // itself (plain operand), or its raw bytes (ragged operand, rows inside the image only)
+    const bool a_raw = a_eng && g.a.rg && in_image && a_hi > a_lo;
+    const bool b_raw = b_eng && g.b.rg && in_image && b_hi > b_lo;
+    RawSpan ra = {nullptr, 0, 0, 0}, rbs = {nullptr, 0, 0, 0};
+    if (a_raw) ra = raw_span(g, g.a, iy, is.t.x0);
+    if (b_raw) rbs = raw_span(g, g.b, iy, is.t.x0);
     uint32_t bytes = 0;
-    if (a_tma) bytes += (uint32_t)(a_hi - a_lo) * SRC_PITCH;
-    if (b_tma) bytes += (uint32_t)max(0, c_hi - max(c_lo, nca)) * CHUNK_PITCH;
+    if (a_eng && g.a.tma) bytes += (uint32_t)(a_hi - a_lo) * (g.a.up ? (uint32_t)SRC_PITCH : (uint32_t)CHUNK_PITCH);
+    if (b_eng && g.b.tma) bytes += (uint32_t)(b_hi - b_lo) * CHUNK_PITCH;
+    bytes += ra.bytes + rbs.bytes;
     if (DBG_SKIP(g) & 1) bytes = 0;
     if (bytes) {
       mbar_expect_tx(rb, bytes);
-      if (a_tma)
-        for (int c = a_lo; c < a_hi; c += 2)  // two chunks of the half resolution row, packed, at the first one's place
-          tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, (is.t.x0 >> 1) - 1, c, iy >> 1, rb);
-      if (b_tma)
-        for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
+      if (a_eng && g.a.tma) {
+        if (g.a.up) {
+          for (int c = a_lo; c < a_hi; c += 2)  // two chunks of the half resolution row, packed, at the first one's place
+            tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, (is.t.x0 >> 1) - 1, c, iy >> 1, rb);
+        } else {
+          for (int c = a_lo; c < a_hi; c += g.a.tbox)
+            tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, is.t.x0 - 1, c, iy, rb);
+        }
+      }
+      if (b_eng && g.b.tma)
+        for (int c = b_lo; c < b_hi; c += g.b.tbox)
           tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, is.t.x0 - 1, c - nca, iy, rb);
+      if (a_raw) bulk_g2s(slot_addr + (uint32_t)((a_lo - c_lo) * CHUNK_PITCH), ra.src, ra.bytes, rb);
+      if (b_raw) bulk_g2s(slot_addr + (uint32_t)((b_lo - c_lo) * CHUNK_PITCH), rbs.src, rbs.bytes, rb);
     } else {
       mbar_arrive(rb);
     }
@@ -1245,8 +1289,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     };
     // The loop, instantiated per K step count: when all K groups have the same count, the choice of the
     // straight line form is made once here and not per row (NKC = 0: per row, by a switch).
-    auto mma_loop = [&](auto NKC) {
+    auto mma_loop = [&](auto NKC, auto ERC) {
       constexpr int NK = decltype(NKC)::value;
+      constexpr int ERT = decltype(ERC)::value;  // input rows per entry
       int slot = 0, pos = 0;
       uint32_t fphase = 0;
       for (;;) {
@@ -1254,38 +1299,52 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         if (!mbar_wait(bar(ST_BAR_FULL + bofs + slot), fphase, abort_flag, g.status, 2)) break;
         if (tr) trace(g, 0, pos, 1);
         const uint32_t da = sbase + ST_OFF_DESC + (uint32_t)(bofs + slot) * ST_DESC_BYTES;
-        const uint4 q0 = lds16(da), q1 = lds16(da + 16), q2 = lds16(da + 32);
-        const uint32_t flags = q0.z;
+        uint4 q[ERT][3];
+#pragma unroll
+        for (int r = 0; r < ERT; ++r) {
+          q[r][0] = lds16(da + (uint32_t)(r * ST_SUBDESC_BYTES));
+          q[r][1] = lds16(da + (uint32_t)(r * ST_SUBDESC_BYTES + 16));
+          q[r][2] = lds16(da + (uint32_t)(r * ST_SUBDESC_BYTES + 32));
+        }
         tc_fence_after();
-        if (!(DBG_SKIP(g) & 2)) {
-          const uint32_t row_lo = q0.x, b_lo = q0.y;
-          const Run R0 = {q1.x, q1.y, q1.z, 1u}, R1 = {q1.w, q2.x, q2.y, 1u};
-          if constexpr (NK > 0) {
-            if (flags & DF_NR2) st_issue_row<NK, 2>(a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1);
-            else st_issue_row<NK, 1>(a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0);
-          } else {
-            const int nk16 = (int)(flags & 15u);
-            bool done = false;
-            if (!DBG_LOOP_ISSUE(g))
-              done = (flags & DF_NR2) ? st_issue_nk<2>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1)
-                                      : st_issue_nk<1>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0);
-            if (!done) {
-              // more K steps than the straight line forms cover
-              for (int dx = 0; dx < 3; ++dx)
-                for (int kc = 0; kc < nk16; ++kc) {
-                  const uint32_t a = row_lo + (uint32_t)dx + (uint32_t)kc * kstep_a;
-                  const uint32_t b = b_lo + (uint32_t)dx * (wdx_bytes >> 4) + (uint32_t)kc * kstep_b;
-                  mma1(R0.col, a, b + R0.boff, R0.idesc, 1u);
-                  if (flags & DF_NR2) mma1(R1.col, a, b + R1.boff, R1.idesc, 1u);
-                }
+        uint32_t allflags = 0;
+#pragma unroll
+        for (int r = 0; r < ERT; ++r) {
+          const uint4 q0 = q[r][0], q1 = q[r][1], q2 = q[r][2];
+          const uint32_t flags = q0.z;
+          allflags |= flags;
+          if (!(DBG_SKIP(g) & 2)) {
+            const uint32_t row_lo = q0.x, b_lo = q0.y;
+            const Run R0 = {q1.x, q1.y, q1.z, 1u}, R1 = {q1.w, q2.x, q2.y, 1u};
+            if constexpr (NK > 0) {
+              if (flags & DF_NR2) st_issue_row<NK, 2>(a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1);
+              else st_issue_row<NK, 1>(a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0);
+            } else {
+              const int nk16 = (int)(flags & 15u);
+              bool done = false;
+              if (!DBG_LOOP_ISSUE(g))
+                done = (flags & DF_NR2) ? st_issue_nk<2>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1)
+                                        : st_issue_nk<1>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0);
+              if (!done) {
+                // more K steps than the straight line forms cover
+                for (int dx = 0; dx < 3; ++dx)
+                  for (int kc = 0; kc < nk16; ++kc) {
+                    const uint32_t a = row_lo + (uint32_t)dx + (uint32_t)kc * kstep_a;
+                    const uint32_t b = b_lo + (uint32_t)dx * (wdx_bytes >> 4) + (uint32_t)kc * kstep_b;
+                    mma1(R0.col, a, b + R0.boff, R0.idesc, 1u);
+                    if (flags & DF_NR2) mma1(R1.col, a, b + R1.boff, R1.idesc, 1u);
+                  }
+              }
             }
           }
+          if (tr) trace(g, 0, pos, 2);
+          // the slot is free once the MMAs of its last row are done; an output row completed by this input row
+          // is announced right behind that row's MMAs
+          if (r == ERT - 1) tc_commit(bar(ST_BAR_EMPTY + bofs + slot));
+          if (q0.w) tc_commit(q0.w);
         }
-        if (tr) trace(g, 0, pos, 2);
-        tc_commit(bar(ST_BAR_EMPTY + bofs + slot));
-        if (q0.w) tc_commit(q0.w);
         if (tr) trace(g, 0, pos, 3);
-        if (flags & DF_LAST) break;
+        if (allflags & DF_LAST) break;
         ++pos;
         if (++slot == S) {
           slot = 0;
@@ -1297,14 +1356,26 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
       bool same = !DBG_LOOP_ISSUE(g) && !DBG_SWITCH_ISSUE(g);
       for (int gi = 1; gi < g.G; ++gi) same = same && g.gch[gi] == g.gch[0];
       const int nkfix = same ? (g.gch[0] >> 1) : 0;
-      switch (nkfix) {
-        case 1: mma_loop(IntC<1>{}); break;
-        case 2: mma_loop(IntC<2>{}); break;
-        case 3: mma_loop(IntC<3>{}); break;
-        case 4: mma_loop(IntC<4>{}); break;
-        case 5: mma_loop(IntC<5>{}); break;
-        case 6: mma_loop(IntC<6>{}); break;
-        default: mma_loop(IntC<0>{}); break;
+      if (g.ER == 2) {
+        // two rows per entry: one K group, at most six K steps (the plan refuses anything else)
+        switch (nkfix) {
+          case 1: mma_loop(IntC<1>{}, IntC<2>{}); break;
+          case 2: mma_loop(IntC<2>{}, IntC<2>{}); break;
+          case 3: mma_loop(IntC<3>{}, IntC<2>{}); break;
+          case 4: mma_loop(IntC<4>{}, IntC<2>{}); break;
+          case 5: mma_loop(IntC<5>{}, IntC<2>{}); break;
+          default: mma_loop(IntC<6>{}, IntC<2>{}); break;
+        }
+      } else {
+        switch (nkfix) {
+          case 1: mma_loop(IntC<1>{}, IntC<1>{}); break;
+          case 2: mma_loop(IntC<2>{}, IntC<1>{}); break;
+          case 3: mma_loop(IntC<3>{}, IntC<1>{}); break;
+          case 4: mma_loop(IntC<4>{}, IntC<1>{}); break;
+          case 5: mma_loop(IntC<5>{}, IntC<1>{}); break;
+          case 6: mma_loop(IntC<6>{}, IntC<1>{}); break;
+          default: mma_loop(IntC<0>{}, IntC<1>{}); break;
+        }
       }
     }
     __syncwarp();
@@ -1454,26 +1525,29 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         const bool tr = DBG_TRACE_ON(g) && blockIdx.x == 0 && pipe == 0;
         for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
           const StUnit t = st_unit_of(g, u);
-          for (int jj = 0; ok && jj < t.rows_out + 2; ++jj) {
-            const int iy = t.y0 - 1 + jj;
+          for (int jj = 0; ok && jj < t.rows_out + 2; jj += g.ER) {
             for (int gi = 0; ok && gi < g.G; ++gi) {
               if (tr) trace(g, 2, pcount, 0);
               ok = mbar_wait<64>(bar(ST_BAR_EMPTY + bofs + slot), phase, abort_flag, g.status, 7);
               if (!ok) break;
               if (tr) trace(g, 2, pcount, 1);
-              const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes;
               const uint32_t fb = bar(ST_BAR_FULL + bofs + slot);
               const int c_lo = g.gc0[gi], c_hi = c_lo + g.gch[gi];
-              mbar_expect_tx(fb, (uint32_t)g.gch[gi] * CHUNK_PITCH);
+              mbar_expect_tx(fb, (uint32_t)g.gch[gi] * CHUNK_PITCH * (uint32_t)g.ER);
               if (!(DBG_SKIP(g) & 1)) {
-                for (int c = c_lo; c < min(c_hi, nca); c += g.a.tbox)
-                  tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, t.x0 - 1, c, iy, fb);
-                for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
-                  tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, t.x0 - 1, c - nca, iy, fb);
+                // the entry's rows one after the other in the slot (rows past the image are zero filled by the copy)
+                for (int r = 0; r < g.ER; ++r) {
+                  const int iy = t.y0 - 1 + jj + r;
+                  const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes + (uint32_t)r * row_bytes;
+                  for (int c = c_lo; c < min(c_hi, nca); c += g.a.tbox)
+                    tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, t.x0 - 1, c, iy, fb);
+                  for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
+                    tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, t.x0 - 1, c - nca, iy, fb);
+                }
               } else {
                 // timing aid: nothing will land, so complete the transaction count by hand
                 asm volatile("mbarrier.complete_tx.shared::cta.b64 [%0], %1;" ::"r"(fb),
-                             "r"((uint32_t)g.gch[gi] * CHUNK_PITCH)
+                             "r"((uint32_t)g.gch[gi] * CHUNK_PITCH * (uint32_t)g.ER)
                              : "memory");
               }
               if (tr) trace(g, 2, pcount, 2);
@@ -1512,7 +1586,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         // expand entry `ex`
         {
           const int iy = ex.t.y0 - 1 + ex.jj;
-          const bool a_tma = row_by_tma(g, g.a, iy), b_tma = g.b.nch > 0 && row_by_tma(g, g.b, iy);
+          const bool a_eng = row_by_tma(g, g.a, iy), b_eng = g.b.nch > 0 && row_by_tma(g, g.b, iy);
           const int c_lo = g.gc0[ex.gi], c_hi = c_lo + g.gch[ex.gi];
           const int a_lo = min(c_lo, nca), a_hi = min(c_hi, nca);
           const uint32_t slot_addr = slots_addr + (uint32_t)ex.slot * slot_bytes;
@@ -1539,12 +1613,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           if (tid == 32 && pipe == 0) trace(g, 2, xcount, 1);
           // rows TMA does not cover (halo rows of a row band) come the old way; the raw barrier has completed,
           // so the slot is free (thread 0 waited for that before it armed the barrier)
-          if (!(DBG_SKIP(g) & 1) && (!a_tma || (g.b.nch > 0 && !b_tma))) {
+          if (!(DBG_SKIP(g) & 1) && (!a_eng || (g.b.nch > 0 && !b_eng))) {
             load_row(g, slot_addr, iy, ex.t.x0, tid, nprod, c_lo, c_hi);
             cp_async_commit();
             cp_async_wait<0>();
           }
-          if (a_tma && !(DBG_SKIP(g) & 1)) {
+          if (a_eng && g.a.up && !(DBG_SKIP(g) & 1)) {
             // In place, one pair of chunks at a time: the copy left the pair's two half resolution rows packed
             // (2 x 72 pixels) at the start of the pair's 2 x 132 pixel area.  Every thread first loads the
             // sources of its pixels, then all producer threads of the pipeline meet, then they store.
@@ -1568,6 +1642,52 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
                   const uint32_t dp = pair + (uint32_t)(px * 16);
                   sts16(dp, v[i][0]);
                   sts16(dp + (uint32_t)CHUNK_PITCH, v[i][1]);
+                }
+              }
+            }
+          }
+          // Ragged operands (at most 16 channels, two chunks): the copy left the row's raw bytes, pixel after
+          // pixel at C halves each, at the start of the operand's two chunk area.  Re-laid in place into
+          // [chunk][pixel][8 halves] with zeros for the channels up to 16 and for pixels outside the image: every
+          // thread gathers its pixels, the producer threads of the pipeline meet, then they store.
+          if (!(DBG_SKIP(g) & 1)) {
+#pragma unroll 1
+            for (int sg = 0; sg < 2; ++sg) {
+              const Seg &sgm = sg ? g.b : g.a;
+              if (!sgm.rg || !(sg ? b_eng : a_eng)) continue;
+              const int lo = sg ? max(c_lo, nca) : a_lo, hi = sg ? max(c_hi, nca) : a_hi;
+              if (hi <= lo) continue;
+              const uint32_t area = slot_addr + (uint32_t)((lo - c_lo) * CHUNK_PITCH);
+              const bool in_image = iy >= 0 && iy < g.H;
+              RawSpan rs = {nullptr, 0, 0, 0};
+              if (in_image) rs = raw_span(g, sgm, iy, ex.t.x0);
+              const int C = sgm.C;
+              uint32_t wv[3][8];
+#pragma unroll
+              for (int i = 0; i < 3; ++i) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) wv[i][e] = 0u;
+                const int px = tid + i * nprod;
+                const int ix = ex.t.x0 - 1 + px;
+                if (px < SLOT_PX && in_image && ix >= 0 && ix < g.W) {
+                  const uint32_t sp = area + rs.lead + (uint32_t)((ix - rs.xs) * C * 2);
+#pragma unroll
+                  for (int e = 0; e < 16; ++e)
+                    if (e < C) {
+                      uint32_t hv;
+                      asm volatile("ld.shared.u16 %0, [%1];" : "=r"(hv) : "r"(sp + (uint32_t)(2 * e)) : "memory");
+                      wv[i][e >> 1] |= hv << ((e & 1) * 16);
+                    }
+                }
+              }
+              asm volatile("bar.sync %0, %1;" ::"r"(1 + pipe), "r"(nprod) : "memory");
+#pragma unroll
+              for (int i = 0; i < 3; ++i) {
+                const int px = tid + i * nprod;
+                if (px < SLOT_PX) {
+                  const uint32_t dp = area + (uint32_t)(px * 16);
+                  sts16(dp, make_uint4(wv[i][0], wv[i][1], wv[i][2], wv[i][3]));
+                  sts16(dp + (uint32_t)CHUNK_PITCH, make_uint4(wv[i][4], wv[i][5], wv[i][6], wv[i][7]));
                 }
               }
             }
@@ -1690,16 +1810,22 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           break;
         }
         const uint32_t rowflags = R1.acc != 2 ? DF_NR2 : 0u;
+        // with two rows per entry (one K group then) this row is the first or the second half of its entry: the
+        // slot is waited for before the first half is described and handed over after the second
+        const int sub = g.ER == 2 ? (jj & 1) : 0;
         for (int gi = 0; ok && gi < g.G; ++gi) {
-          ok = mbar_wait<32>(bar(ST_BAR_EMPTY + bofs + slot), ephase, abort_flag, g.status, 7);
-          if (!ok) break;
+          if (sub == 0) {
+            ok = mbar_wait<32>(bar(ST_BAR_EMPTY + bofs + slot), ephase, abort_flag, g.status, 7);
+            if (!ok) break;
+          }
           uint32_t flags = rowflags | (uint32_t)(g.gch[gi] >> 1);
           if (last_unit && jj == rows_in - 1 && gi == g.G - 1) flags |= DF_LAST;
-          const uint32_t row_lo = (((slots_addr + (uint32_t)slot * slot_bytes) & 0x3FFFFu) >> 4) | a_lo0;
+          const uint32_t row_lo =
+              (((slots_addr + (uint32_t)slot * slot_bytes + (uint32_t)sub * row_bytes) & 0x3FFFFu) >> 4) | a_lo0;
           const uint32_t wgrp = (uint32_t)g.gc0[gi] * 3u * N16;  // group's first chunk, in 16 byte units
           const uint32_t b_lo = (((w_addr & 0x3FFFFu) >> 4) + wgrp) | b_lo0;
           const uint32_t tfbar = (gi == g.G - 1 && vA) ? bar(ST_BAR_TFULL + bofs + blkA) : 0u;
-          const uint32_t da = sbase + ST_OFF_DESC + (uint32_t)(bofs + slot) * ST_DESC_BYTES;
+          const uint32_t da = sbase + ST_OFF_DESC + (uint32_t)(bofs + slot) * ST_DESC_BYTES + (uint32_t)(sub * ST_SUBDESC_BYTES);
           sts16(da, make_uint4(row_lo, b_lo, flags, tfbar));
           sts16(da + 16, make_uint4(R0.col, R0.boff, R0.idesc, R1.col));
           sts16(da + 32, make_uint4(R1.boff, R1.idesc, 0u, 0u));
@@ -1708,10 +1834,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
             ok = mbar_wait<32>(bar(ST_BAR_TEMPTY + bofs + blkC), cphase, abort_flag, g.status, 3);
             if (!ok) break;
           }
-          mbar_arrive(bar(ST_BAR_FULL + bofs + slot));
-          if (++slot == S) {
-            slot = 0;
-            ephase ^= 1u;
+          if (sub == g.ER - 1) {
+            mbar_arrive(bar(ST_BAR_FULL + bofs + slot));
+            if (++slot == S) {
+              slot = 0;
+              ephase ^= 1u;
+            }
           }
         }
         blkA = blkB;
@@ -1831,6 +1959,13 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
     for (; gi < MAX_GROUPS; ++gi) g.gc0[gi] = g.gch[gi] = 0;
     g.gmax = per < nch ? per : nch;
   }
+  // Two input rows per ring entry ("ER=2"): halves the per-entry work of the single-thread roles (slot wait,
+  // descriptor, slot release), which is what bounds thin layers.  Only where every row comes by one plain TMA
+  // copy per operand: one K group, no upsampled or ragged operand, no halo rows, an even number of rows, and
+  // at most six K steps per row (the straight line MMA forms).
+  const int ER = v.p4 == 2 ? 2 : 1;
+  if (ER == 2 && (g.cpa || g.a.up || g.G != 1 || (H & 1) || nch / 2 > 6)) return DNXCU_E_UNSUPPORTED;
+  g.ER = ER;
   // one TMA copy per operand and row when a slot holds all channels, else two chunks per copy
   g.a.tbox = (g.G == 1) ? g.a.nch : 2;
   g.b.tbox = (g.G == 1 && g.b.nch) ? g.b.nch : 2;
@@ -1840,7 +1975,13 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   // Shared memory budget.  Wanted, in this order of importance: four input slots; the epilogue staging tiles
   // (4 warps per pipeline x 32 pixels x (K*2 + 16) bytes, two rows when pooling); expand mode for an upsampled
   // operand a (TMA at half resolution + one staging buffer per slot); a second pipeline (eight slots).
-  const bool xp_possible = g.a.up && (g.a.C % 8) == 0 && (g.b.nch == 0 || g.b.tma) && !dbg_env("DNXCU_TC_NO_EXPAND") &&
+  // "fix-up" mode: the copy engine brings every row (a half resolution row of an upsampled operand, the raw
+  // bytes of a ragged one, a plain operand's row as it is) and the producer warps put it right inside shared
+  // memory.  Possible when at least one operand needs that and each operand is one of the three kinds.
+  const bool a_up_ok = g.a.up && (g.a.C % 8) == 0;
+  const bool a_kind_ok = a_up_ok || g.a.rg || (!g.a.up && g.a.tma);
+  const bool b_kind_ok = g.b.nch == 0 || g.b.tma || g.b.rg;
+  const bool xp_possible = (a_up_ok || g.a.rg || g.b.rg) && a_kind_ok && b_kind_ok && !dbg_env("DNXCU_TC_NO_EXPAND") &&
                            !dbg_env("DNXCU_TC_NO_TMA");
   uint32_t xp_src_bytes = 0;
   if (xp_possible) {
@@ -1857,7 +1998,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   const size_t stage_pitch = (size_t)g.K * 2 + 16;
   const size_t stage_per_warp = (g.pool ? 2 : 1) * 32 * stage_pitch;
   const size_t base_bytes = ST_HEADER_BYTES + wregion;
-  const size_t plain_slot = (size_t)g.gmax * CHUNK_PITCH;
+  const size_t plain_slot = (size_t)g.gmax * CHUNK_PITCH * ER;
   // v.p2 == 2 ("PIPES=1"): one pipeline with a longer slot ring even where two would fit
   const bool p2_possible = 4 * g.N <= 256 && !dbg_env("DNXCU_TC_PIPES") && v.p2 != 2;
   // candidate configurations, best first: (pipelines, expand, staging)
@@ -1868,11 +2009,17 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   for (int ti = 0; ti < 8 && P == 0; ++ti) {
     const int tp = tries[ti][0], txp = tries[ti][1], tst = tries[ti][2];
     if (tp == 2 && !p2_possible) continue;
+    {
+      // two rows per entry keep four accumulator blocks in use at once: the ring must leave the epilogue room
+      const int nb = tp == 2 ? (256 / g.N < ST_PIPE_STRIDE ? 256 / g.N : ST_PIPE_STRIDE)
+                             : (512 / g.N < ST_MAX_BLOCKS ? 512 / g.N : ST_MAX_BLOCKS);
+      if (ER == 2 && nb < 6) continue;
+    }
     if (txp != (xp_possible ? 1 : 0) && txp == 1) continue;
     if (tst && !stage_possible) continue;
     const size_t sb = plain_slot + (txp ? xp_src_bytes : 0);
     const size_t st = tst ? (size_t)4 * tp * stage_per_warp : 0;
-    const int min_slots = tp == 2 ? 3 : 4;  // two issuing threads pay for a shorter ring
+    const int min_slots = ER == 2 ? 2 : (tp == 2 ? 3 : 4);  // two issuing threads pay for a shorter ring
     if (base_bytes + st + (size_t)min_slots * tp * sb > SMEM_LIMIT) continue;
     P = tp;
     slot_bytes = sb;
@@ -1886,7 +2033,9 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   if (P == 0) return DNXCU_E_UNSUPPORTED;
   if (g.xp) {
     g.cpa = 1;
-    g.a.tma = 1;
+    if (g.a.up) g.a.tma = 1;  // by TMA at half resolution
+  } else {
+    g.a.rg = g.b.rg = 0;  // without the fix-up mode ragged operands are loaded by the producer warps
   }
   g.nstrips = (W + STRIP - 1) / STRIP;
   g.P = P;
@@ -1925,7 +2074,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   memset(&g.tm_a, 0, sizeof(g.tm_a));
   memset(&g.tm_b, 0, sizeof(g.tm_b));
   if (encode) {
-    if (g.xp) {
+    if (g.xp && g.a.up) {
       if (make_tensor_map(&g.tm_a, d.in_a, H / 2, W / 2, d.c_a, 2, SRC_PX)) return DNXCU_E_CUDA;
     } else if (g.a.tma && make_tensor_map(&g.tm_a, d.in_a, H, W, d.c_a, g.a.tbox)) {
       return DNXCU_E_CUDA;
@@ -1963,12 +2112,21 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
     return DNXCU_E_MISALIGNED;
 
   TcArgs &g = pl.args;
-  g.a = {(const __half *)d.in_a, (const __half *)d.halo[0], (const __half *)d.halo[1], d.c_a, nch_of(d.c_a), up ? 1 : 0, 0, 2};
-  g.b = {(const __half *)d.in_b, (const __half *)d.halo[2], (const __half *)d.halo[3], d.c_b, nch_of(d.c_b), 0, 0, 2};
+  g.a = {(const __half *)d.in_a, (const __half *)d.halo[0], (const __half *)d.halo[1], d.c_a, nch_of(d.c_a), up ? 1 : 0, 0, 2, 0};
+  g.b = {(const __half *)d.in_b, (const __half *)d.halo[2], (const __half *)d.halo[3], d.c_b, nch_of(d.c_b), 0, 0, 2, 0};
   // TMA takes the operands whose pixels are whole 16 byte chunks at full resolution
   const bool allow_tma = !dbg_env("DNXCU_TC_NO_TMA");
   g.a.tma = allow_tma && !up && (d.c_a % 8 == 0);
   g.b.tma = allow_tma && d.c_b > 0 && (d.c_b % 8 == 0);
+  // ragged operands of at most 16 channels (the 9 channel colour / albedo / normal input): raw row bytes by bulk
+  // copy, re-laid in shared memory (stacked form).  Bulk copies move whole 16 byte pieces from 16 byte aligned
+  // addresses, so the tensor must start on such an address and end on one.
+  auto raggable = [&](const void *ptr, int C, bool upsampled) {
+    return allow_tma && !upsampled && C > 0 && (C % 8) != 0 && C <= 16 && ((uintptr_t)ptr & 15) == 0 &&
+           ((size_t)H * W * C * 2) % 16 == 0;
+  };
+  g.a.rg = raggable(d.in_a, d.c_a, up) ? 1 : 0;
+  g.b.rg = raggable(d.in_b, d.c_b, false) ? 1 : 0;
   g.cpa = (!g.a.tma || (d.c_b > 0 && !g.b.tma) || d.halo[0] || d.halo[1] || d.halo[2] || d.halo[3]) ? 1 : 0;
   g.w = (const __half *)d.weights;
   g.bias = (d.flags & DNXCU_F_BIAS) ? (const __half *)d.bias : nullptr;
@@ -2005,6 +2163,8 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
 #endif
 
   if (R == 0) return make_plan_stack(v, d, pl, encode);
+  g.a.rg = g.b.rg = 0;  // the pass kernel loads ragged operands with its producer warps
+  g.ER = 1;
   uint32_t cols = 2u * R * g.Ns;
   if (cols > 512) return DNXCU_E_UNSUPPORTED;
   uint32_t p2 = 32;

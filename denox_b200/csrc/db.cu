@@ -6,6 +6,7 @@
 // replaced atomically, selection reads mean latencies.  The file is a text
 // table (one entry per line) instead of a flatbuffer.
 #include "runtime.h"
+#include "select.h"
 #include <math.h>
 #include <stdio.h>
 #include <string.h>
@@ -236,33 +237,24 @@ int dnxcu_db_populate(dnxcu_db *db, const dnxcu_model_desc *desc, int height, in
   }
   int st = build_fused_ops(*desc, allow_tc, m);
   if (st) return st;
+  m.options = desc->options;
+  // every candidate dispatch of the model at this extent: each node alone, each fusion pattern, each variant that
+  // takes it; reduced, like the reference's populate (populate.cpp:41), to the topologies with the fewest
+  // dispatches unless the model asks for selection by cost alone
+  HyperGraph g;
+  std::vector<Candidate> cands;
+  st = build_supergraph(m, allow_tc, height, width, g, cands);
+  if (st) return st;
+  if (!(desc->options & DNXCU_OPT_SELECT_BY_COST_ONLY) &&
+      !prune_topological(g, {desc->input_tensor}, {desc->output_tensor}))
+    return DNXCU_E_UNSUPPORTED;
   int added = 0;
-  for (const FusedOp &op : m.ops) {
-    std::vector<int> cand;
-    candidate_variants(op, allow_tc, cand);
-    dnxcu_dispatch d;
-    memset(&d, 0, sizeof(d));
-    d.flags = op.flags;
-    d.pc[0] = (uint32_t)(width >> op.level);
-    d.pc[1] = (uint32_t)(height >> op.level);
-    d.c_a = op.c_a;
-    d.c_b = op.c_b;
-    d.c_out = op.c_out;
-    d.leaky_alpha = op.alpha;
-    // aligned placeholders: validation never dereferences
-    d.in_a = (const void *)0x1000;
-    d.in_b = op.c_b ? (const void *)0x1000 : nullptr;
-    d.out = (void *)0x1000;
-    d.out_pool = (op.flags & DNXCU_F_POOL_OUT) ? (void *)0x1000 : nullptr;
-    d.weights = (const void *)0x1000;
-    d.bias = (op.flags & DNXCU_F_BIAS) ? (const void *)0x1000 : nullptr;
-    for (int id : cand) {
-      d.variant = id;
-      if (dnxcu_validate(&d) != DNXCU_OK) continue;
-      bool is_new = false;
-      find_or_add(*db, d, true, &is_new);
-      if (is_new) ++added;
-    }
+  for (const HyperEdge &e : g.edges) {
+    const Candidate &c = cands[e.payload];
+    const dnxcu_dispatch d = probe_dispatch(c.op, height, width, c.variant);
+    bool is_new = false;
+    find_or_add(*db, d, true, &is_new);
+    if (is_new) ++added;
   }
   return added;
 }

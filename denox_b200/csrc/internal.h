@@ -35,6 +35,7 @@ struct Variant {
   VariantKind kind;
   // tuning parameters (meaning depends on kind)
   int p0, p1, p2, p3;
+  int p4 = 0;
 };
 
 const Variant *get_variant(int id);

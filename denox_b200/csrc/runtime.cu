@@ -3,7 +3,10 @@
 // on this path (compiler/src/denox/compiler/implement/implement.cpp:11-68,
 // runtime/src/denox/runtime/model.cpp:637-659, instance.cpp:25-430).
 #include "runtime.h"
+#include "halo_xchg.h"
+#include "select.h"
 #include <string.h>
+#include <unistd.h>
 #include <map>
 #include <memory>
 
@@ -50,6 +53,8 @@ int build_fused_ops(const dnxcu_model_desc &desc, bool allow_tc, dnxcu_model &m)
     return DNXCU_E_BAD_ARG;
   const int NT = desc.n_tensors, NN = desc.n_nodes;
   m.tensors.assign(NT, TensorInfo());
+  m.n_model_tensors = NT;
+  m.nodes.clear();
   m.ops.clear();
   m.input_tensor = desc.input_tensor;
   m.output_tensor = desc.output_tensor;
@@ -97,6 +102,22 @@ int build_fused_ops(const dnxcu_model_desc &desc, bool allow_tc, dnxcu_model &m)
     to.materialized = false;
     defined[n.out] = true;
     producer[n.out] = i;
+    NodeRec rec;
+    rec.kind = n.kind;
+    rec.in0 = n.in0;
+    rec.in1 = n.kind == DNXCU_NODE_CONCAT ? n.in1 : -1;
+    rec.out = n.out;
+    rec.c_out = n.c_out;
+    rec.alpha = n.alpha;
+    if (n.kind == DNXCU_NODE_CONV) {
+      const size_t nw = (size_t)n.c_out * t0.channels * 9;
+      rec.weights.assign((const uint16_t *)n.weights_kcrs, (const uint16_t *)n.weights_kcrs + nw);
+      if (n.bias) {
+        rec.has_bias = true;
+        rec.bias.assign((const uint16_t *)n.bias, (const uint16_t *)n.bias + n.c_out);
+      }
+    }
+    m.nodes.push_back(std::move(rec));
   }
   if (!defined[desc.output_tensor]) return DNXCU_E_BAD_ARG;
 
@@ -274,11 +295,22 @@ int build_fused_ops(const dnxcu_model_desc &desc, bool allow_tc, dnxcu_model &m)
   return DNXCU_OK;
 }
 
+// preference when no benchmark data exists: tensor core variants first,
+// resident weights before streamed, then the CUDA core fallback; 128-bit before 2-byte.
+static const int conv_pref[] = {6, 7, 17, 18, 19, 26, 20, 27, 25, 28, 29, 2, 3, 1, 4, 5, 0};
+
+int variant_rank(int variant) {
+  int r = 0;
+  for (int id : conv_pref) {
+    if (id == variant) return r;
+    ++r;
+  }
+  const Variant *v = get_variant(variant);
+  return 100 + (v && v->p0 == 8 ? 0 : 1);  // memory kernels: the 128-bit form first
+}
+
 void candidate_variants(const FusedOp &op, bool allow_tc, std::vector<int> &out) {
   out.clear();
-  // preference when no benchmark data exists: tensor core variants first,
-  // resident weights before streamed, then the CUDA core fallback; 128-bit before 2-byte.
-  static const int conv_pref[] = {6, 7, 17, 18, 19, 26, 20, 27, 25, 2, 3, 1, 4, 5, 0};
   if (op.op == DNXCU_OP_CONV3X3) {
     for (int id : conv_pref) {
       const Variant *v = get_variant(id);
@@ -309,10 +341,29 @@ struct dnxcu_instance {
   void *user_in = nullptr, *user_out = nullptr;
   dnxcu_band band = {0, 0, 0};
   bool banded = false;
+  std::vector<dnxcu::FusedOp> ops;        // this instance's schedule: the model's default, or what the cost
+  std::vector<dnxcu::TensorInfo> tensors;  // driven selection chose for this extent
+  std::vector<int> preset_variant;         // selection's variant per dispatch (empty: chosen per dispatch below)
   std::vector<void *> tensor_ptr;    // per tensor device pointer (nullptr if not materialized)
   std::vector<void *> owned;         // everything to cudaFree
   std::vector<dnxcu_dispatch> disp;  // with the instance's own input / output buffers
   std::vector<dnxcu_halo_point> halos;
+  // Direct halo exchange over peer memory (row bands on several GPUs, or several bands on one device).
+  // All slabs and flags of the band live in one allocation with a layout that depends only on the model,
+  // the width and the band height, so neighbours address each other's slabs by offset.
+  struct HaloSlot {
+    size_t top_off, bot_off, flag_off;  // slab "row above", slab "row below", two flags (top, bottom)
+    int dispatch;
+  };
+  std::vector<HaloSlot> halo_slots;     // one per entry of `halos`
+  char *arena = nullptr;
+  size_t arena_bytes = 0;
+  uint64_t arena_layout = 0;            // hash of what determines the layout
+  unsigned *xchg_ctl = nullptr;         // per dispatch: blocks-done counter, push counter
+  char *peer_up = nullptr, *peer_down = nullptr;  // the neighbours' arenas as this device sees them
+  bool peer_up_ipc = false, peer_down_ipc = false;
+  bool connected = false, auto_exchange = false;
+  std::vector<dnxcu::XchgArgs> xchg;    // per dispatch, npoints == 0: nothing to exchange
   std::vector<dnxcu_plan *> plans;   // one per dispatch, made from the instance's own buffers
   int *status = nullptr;
   cudaStream_t stream = nullptr;
@@ -323,9 +374,12 @@ struct dnxcu_instance {
     void *out;
   };
   std::vector<Graph> graphs;
+  size_t graph_capacity = 4;
   std::vector<cudaEvent_t> events;
 
   ~dnxcu_instance() {
+    if (peer_up_ipc && peer_up) cudaIpcCloseMemHandle(peer_up);
+    if (peer_down_ipc && peer_down) cudaIpcCloseMemHandle(peer_down);
     for (Graph &g : graphs) cudaGraphExecDestroy(g.exec);
     for (dnxcu_plan *p : plans) dnxcu_plan_destroy(p);
     for (cudaEvent_t e : events) cudaEventDestroy(e);
@@ -350,7 +404,15 @@ int dev_alloc(dnxcu_instance &inst, size_t bytes, void **out) {
 
 // Enqueues dispatch i, substituting caller pointers for the model's input / output tensors.
 int launch_one(dnxcu_instance &inst, int i, const void *in_override, void *out_override, cudaStream_t s) {
-  const FusedOp &op = inst.model->ops[i];
+  const FusedOp &op = inst.ops[i];
+  if (inst.connected && inst.auto_exchange && inst.xchg[i].npoints > 0) {
+    // the neighbours' boundary rows of this conv's operands: push ours, wait for theirs
+    dnxcu::XchgArgs a = inst.xchg[i];
+    a.mode = XCHG_PUSH | XCHG_WAIT;
+    a.wait_limit = wait_limit_cycles();
+    int st = halo_xchg_launch(a, s);
+    if (st) return st;
+  }
   const int tin = inst.model->input_tensor, tout = inst.model->output_tensor;
   const bool sub_in = in_override && (op.in_a == tin || op.in_b == tin);
   const bool sub_out = out_override && (op.out == tout || op.out_pool == tout);
@@ -398,6 +460,36 @@ int dnxcu_model_create(const dnxcu_model_desc *desc, const dnxcu_db *db, int dev
 
 void dnxcu_model_destroy(dnxcu_model *m) { delete m; }
 int dnxcu_model_dispatch_count(const dnxcu_model *m) { return m ? (int)m->ops.size() : DNXCU_E_BAD_ARG; }
+int dnxcu_instance_dispatch_count(const dnxcu_instance *inst) { return inst ? (int)inst->disp.size() : DNXCU_E_BAD_ARG; }
+
+int dnxcu_select_min_cost(int n_nodes, int n_edges, const int32_t *src_off, const int32_t *srcs, const int32_t *dst_off,
+                          const int32_t *dsts, const double *weight, const int32_t *inputs, int n_inputs,
+                          const int32_t *outputs, int n_outputs, int min_dispatches, int32_t *chosen, int32_t *n_chosen,
+                          double *cost) {
+  if (n_nodes <= 0 || n_edges < 0 || !src_off || !dst_off || !weight || !inputs || !outputs || !chosen || !n_chosen ||
+      n_inputs < 0 || n_outputs <= 0 || (n_edges > 0 && (!srcs || !dsts)))
+    return DNXCU_E_BAD_ARG;
+  HyperGraph g;
+  g.n_nodes = n_nodes;
+  for (int e = 0; e < n_edges; ++e) {
+    if (src_off[e + 1] < src_off[e] || dst_off[e + 1] <= dst_off[e]) return DNXCU_E_BAD_ARG;
+    HyperEdge he;
+    he.src.assign(srcs + src_off[e], srcs + src_off[e + 1]);
+    he.dst.assign(dsts + dst_off[e], dsts + dst_off[e + 1]);
+    he.weight = weight[e];
+    he.payload = e;
+    g.edges.push_back(std::move(he));
+  }
+  const std::vector<int> in(inputs, inputs + n_inputs), out(outputs, outputs + n_outputs);
+  if (min_dispatches && !prune_topological(g, in, out)) return DNXCU_E_UNSUPPORTED;
+  std::vector<int> ch;
+  double c = 0;
+  if (!minimum_cost_subgraph(g, in, out, ch, &c)) return DNXCU_E_UNSUPPORTED;
+  *n_chosen = (int32_t)ch.size();
+  for (size_t i = 0; i < ch.size(); ++i) chosen[i] = g.edges[ch[i]].payload;
+  if (cost) *cost = c;
+  return DNXCU_OK;
+}
 
 int dnxcu_instance_create(const dnxcu_model *m, int height, int width, const dnxcu_band *band, dnxcu_instance **out) {
   if (!m || !out || height <= 0 || width <= 0) return DNXCU_E_BAD_ARG;
@@ -436,33 +528,92 @@ int dnxcu_instance_create(const dnxcu_model *m, int height, int width, const dnx
   const bool has_up = inst->banded && inst->band.row0 > 0;
   const bool has_down = inst->banded && inst->band.row0 + inst->band.rows < inst->band.image_h;
 
+  dnxcu_caps caps;
+  int st = dnxcu_get_device_caps(m->device, &caps);
+  if (st) return st;
+  const bool allow_tc = caps.tcgen05 && !(m->options & DNXCU_OPT_NO_TCGEN05);
+  // the schedule: with a benchmark database, the cheapest sub-graph of all candidate dispatches at this extent
+  // (row bands take the default schedule: every band must run the same dispatches)
+  inst->ops = m->ops;
+  inst->tensors = m->tensors;
+  if (m->db && !band) {
+    std::vector<FusedOp> sel_ops;
+    std::vector<TensorInfo> sel_tensors;
+    std::vector<int> sel_variants;
+    st = select_schedule(*m, m->db, allow_tc, inst->H, width, sel_ops, sel_tensors, sel_variants, nullptr);
+    if (st) return st;
+    inst->ops.swap(sel_ops);
+    inst->tensors.swap(sel_tensors);
+    inst->preset_variant.swap(sel_variants);
+  }
+  const std::vector<FusedOp> &ops = inst->ops;
+  const std::vector<TensorInfo> &tensors = inst->tensors;
+
   DNXCU_CUDA(cudaSetDevice(m->device));
   DNXCU_CUDA(cudaStreamCreateWithFlags(&inst->stream, cudaStreamNonBlocking));
-  int st = dev_alloc(*inst, 256, (void **)&inst->status);
+  st = dev_alloc(*inst, 256, (void **)&inst->status);
   if (st) return st;
   DNXCU_CUDA(cudaMemset(inst->status, 0, 256));
 
-  const int NT = (int)m->tensors.size();
+  const int NT = (int)tensors.size();
   inst->tensor_ptr.assign(NT, nullptr);
   for (int t = 0; t < NT; ++t) {
-    const TensorInfo &ti = m->tensors[t];
+    const TensorInfo &ti = tensors[t];
     if (!ti.materialized) continue;
     const size_t bytes = (size_t)(inst->H >> ti.level) * (width >> ti.level) * ti.channels * 2;
     st = dev_alloc(*inst, bytes, &inst->tensor_ptr[t]);
     if (st) return st;
   }
 
-  dnxcu_caps caps;
-  st = dnxcu_get_device_caps(m->device, &caps);
-  if (st) return st;
-  const bool allow_tc = caps.tcgen05 && !(m->options & DNXCU_OPT_NO_TCGEN05);
   // kernel attributes now, so that no launch needs set-up work later (a launch may sit inside a stream capture)
   if (allow_tc && (st = conv_tc_init_device())) return st;
 
-  inst->disp.resize(m->ops.size());
-  inst->plans.assign(m->ops.size(), nullptr);
-  for (size_t i = 0; i < m->ops.size(); ++i) {
-    const FusedOp &op = m->ops[i];
+  inst->disp.resize(ops.size());
+  inst->plans.assign(ops.size(), nullptr);
+  if (inst->banded) {
+    // lay out the halo arena: per conv operand a slab above and a slab below (256 byte aligned), then the flags
+    size_t off = 0;
+    uint64_t hsh = 1469598103934665603ull;
+    auto mix = [&](uint64_t v) { hsh = (hsh ^ v) * 1099511628211ull; };
+    mix((uint64_t)width);
+    mix((uint64_t)inst->H);
+    for (size_t i = 0; i < ops.size(); ++i) {
+      const FusedOp &op = ops[i];
+      if (op.op != DNXCU_OP_CONV3X3) continue;
+      for (int sgi = 0; sgi < 2; ++sgi) {
+        const int t = sgi ? op.in_b : op.in_a;
+        if (t < 0) continue;
+        const TensorInfo &ti = tensors[t];
+        const size_t row_bytes = (size_t)(width >> ti.level) * ti.channels * 2;
+        const size_t slab = (row_bytes + 255) & ~(size_t)255;
+        dnxcu_instance::HaloSlot hs;
+        hs.dispatch = (int)i;
+        hs.top_off = off;
+        hs.bot_off = off + slab;
+        hs.flag_off = 0;
+        off += 2 * slab;
+        inst->halo_slots.push_back(hs);
+        mix((uint64_t)i * 4 + (uint64_t)sgi);
+        mix((uint64_t)row_bytes);
+      }
+    }
+    for (size_t e = 0; e < inst->halo_slots.size(); ++e) inst->halo_slots[e].flag_off = off + e * 8;
+    off += (inst->halo_slots.size() * 8 + 255) & ~(size_t)255;
+    inst->arena_bytes = off;
+    inst->arena_layout = hsh;
+    void *ar = nullptr, *ctl = nullptr;
+    st = dev_alloc(*inst, off, &ar);
+    if (st) return st;
+    DNXCU_CUDA(cudaMemset(ar, 0, off));
+    inst->arena = (char *)ar;
+    st = dev_alloc(*inst, ops.size() * 2 * sizeof(unsigned), &ctl);
+    if (st) return st;
+    DNXCU_CUDA(cudaMemset(ctl, 0, ops.size() * 2 * sizeof(unsigned)));
+    inst->xchg_ctl = (unsigned *)ctl;
+  }
+  size_t next_slot = 0;
+  for (size_t i = 0; i < ops.size(); ++i) {
+    const FusedOp &op = ops[i];
     dnxcu_dispatch d;
     memset(&d, 0, sizeof(d));
     d.flags = op.flags;
@@ -485,7 +636,7 @@ int dnxcu_instance_create(const dnxcu_model *m, int height, int width, const dnx
         for (int sgi = 0; sgi < 2; ++sgi) {
           const int t = sgi ? op.in_b : op.in_a;
           if (t < 0) continue;
-          const TensorInfo &ti = m->tensors[t];
+          const TensorInfo &ti = tensors[t];
           const size_t row_bytes = (size_t)(width >> ti.level) * ti.channels * 2;
           const size_t th = (size_t)(inst->H >> ti.level);
           dnxcu_halo_point hp;
@@ -495,14 +646,9 @@ int dnxcu_instance_create(const dnxcu_model *m, int height, int width, const dnx
           hp.row_bytes = row_bytes;
           hp.send_top = inst->tensor_ptr[t];
           hp.send_bottom = (const char *)inst->tensor_ptr[t] + (th - 1) * row_bytes;
-          if (has_up) {
-            st = dev_alloc(*inst, row_bytes, &hp.recv_top);
-            if (st) return st;
-          }
-          if (has_down) {
-            st = dev_alloc(*inst, row_bytes, &hp.recv_bottom);
-            if (st) return st;
-          }
+          const dnxcu_instance::HaloSlot &hs = inst->halo_slots[next_slot++];
+          if (has_up) hp.recv_top = inst->arena + hs.top_off;
+          if (has_down) hp.recv_bottom = inst->arena + hs.bot_off;
           d.halo[sgi * 2 + 0] = hp.recv_top;
           d.halo[sgi * 2 + 1] = hp.recv_bottom;
           inst->halos.push_back(hp);
@@ -520,7 +666,8 @@ int dnxcu_instance_create(const dnxcu_model *m, int height, int width, const dnx
     // choose the variant: lowest database latency among those that accept the
     // dispatch (selection.cpp:43-123), else the first in preference order
     std::vector<int> cand;
-    candidate_variants(op, allow_tc, cand);
+    if (!inst->preset_variant.empty()) cand.push_back(inst->preset_variant[i]);  // the selection's choice
+    else candidate_variants(op, allow_tc, cand);
     int chosen = -1;
     double best_ms = 0;
     d.weights = (const void *)0x1000;  // placeholder that passes the alignment checks
@@ -559,7 +706,7 @@ int dnxcu_instance_create(const dnxcu_model *m, int height, int width, const dnx
     if (st) return st;
   }
   if (inst->padded) {
-    const TensorInfo &ti = m->tensors[m->input_tensor], &to = m->tensors[m->output_tensor];
+    const TensorInfo &ti = tensors[m->input_tensor], &to = tensors[m->output_tensor];
     st = dev_alloc(*inst, (size_t)inst->user_H * inst->user_W * ti.channels * 2, &inst->user_in);
     if (st) return st;
     st = dev_alloc(*inst, (size_t)inst->user_H * inst->user_W * to.channels * 2, &inst->user_out);
@@ -645,7 +792,7 @@ int dnxcu_instance_enqueue(dnxcu_instance *inst, const void *dev_in, void *dev_o
     e = cudaGraphInstantiate(&exec, gr, 0);
     cudaGraphDestroy(gr);
     if (e != cudaSuccess) return cuda_fail(e);
-    if (inst->graphs.size() >= 4) {  // keep the four most recently used pairs
+    if (inst->graphs.size() >= inst->graph_capacity) {  // keep the most recently used pairs
       cudaGraphExecDestroy(inst->graphs.back().exec);
       inst->graphs.pop_back();
     }
@@ -661,6 +808,16 @@ int dnxcu_instance_enqueue(dnxcu_instance *inst, const void *dev_in, void *dev_o
   return DNXCU_OK;
 }
 
+int dnxcu_instance_graph_cache(dnxcu_instance *inst, int pairs) {
+  if (!inst || pairs < 1 || pairs > 256) return DNXCU_E_BAD_ARG;
+  inst->graph_capacity = (size_t)pairs;
+  while (inst->graphs.size() > inst->graph_capacity) {
+    cudaGraphExecDestroy(inst->graphs.back().exec);
+    inst->graphs.pop_back();
+  }
+  return DNXCU_OK;
+}
+
 // Host in, host out, but stream ordered: the copies and the schedule are enqueued on the instance's own
 // stream and the call returns.  Several instances used round robin overlap one frame's copies with another
 // frame's kernels.  The host buffers must stay valid (and should be pinned) until dnxcu_instance_wait returns.
@@ -671,7 +828,7 @@ int dnxcu_instance_infer_async(dnxcu_instance *inst, const void *host_in, void *
   void *din = inst->padded ? inst->user_in : inst->tensor_ptr[m->input_tensor];
   void *dout = inst->padded ? inst->user_out : inst->tensor_ptr[m->output_tensor];
   if (!din || !dout) return DNXCU_E_STATE;
-  const TensorInfo &ti = m->tensors[m->input_tensor], &to = m->tensors[m->output_tensor];
+  const TensorInfo &ti = inst->tensors[m->input_tensor], &to = inst->tensors[m->output_tensor];
   const int fh = inst->padded ? inst->user_H : inst->H, fw = inst->padded ? inst->user_W : inst->W;
   const size_t in_bytes = (size_t)fh * fw * ti.channels * 2;
   const size_t out_bytes = (size_t)(fh >> to.level) * (fw >> to.level) * to.channels * 2;
@@ -698,7 +855,7 @@ int dnxcu_instance_infer(dnxcu_instance *inst, const void *host_in, void *host_o
   void *din = inst->padded ? inst->user_in : inst->tensor_ptr[m->input_tensor];
   void *dout = inst->padded ? inst->user_out : inst->tensor_ptr[m->output_tensor];
   if (!din || !dout) return DNXCU_E_STATE;
-  const TensorInfo &ti = m->tensors[m->input_tensor], &to = m->tensors[m->output_tensor];
+  const TensorInfo &ti = inst->tensors[m->input_tensor], &to = inst->tensors[m->output_tensor];
   const int fh = inst->padded ? inst->user_H : inst->H, fw = inst->padded ? inst->user_W : inst->W;
   const size_t in_bytes = (size_t)fh * fw * ti.channels * 2;
   const size_t out_bytes = (size_t)(fh >> to.level) * (fw >> to.level) * to.channels * 2;
@@ -714,7 +871,7 @@ int dnxcu_instance_infer(dnxcu_instance *inst, const void *host_in, void *host_o
 
 int dnxcu_instance_tensor(const dnxcu_instance *inst, int t, void **ptr, int *h, int *w, int *c) {
   if (!inst || t < 0 || t >= (int)inst->tensor_ptr.size()) return DNXCU_E_BAD_ARG;
-  const TensorInfo &ti = inst->model->tensors[t];
+  const TensorInfo &ti = inst->tensors[t];
   if (ptr) *ptr = inst->tensor_ptr[t];
   if (h) *h = inst->H >> ti.level;
   if (w) *w = inst->W >> ti.level;
@@ -740,7 +897,7 @@ int dnxcu_instance_extent(const dnxcu_instance *inst, int *h, int *w, int *h_run
 
 int dnxcu_instance_dispatch_info(const dnxcu_instance *inst, int i, dnxcu_dispatch_info *info) {
   if (!inst || !info || i < 0 || i >= (int)inst->disp.size()) return DNXCU_E_BAD_ARG;
-  const FusedOp &op = inst->model->ops[i];
+  const FusedOp &op = inst->ops[i];
   const dnxcu_dispatch &d = inst->disp[i];
   memset(info, 0, sizeof(*info));
   const dnxcu_variant_desc *vd = dnxcu_variant(d.variant);
@@ -800,6 +957,125 @@ int dnxcu_instance_bench(dnxcu_instance *inst, int warmup, int iters, dnxcu_disp
   int hstatus = 0;
   DNXCU_CUDA(cudaMemcpy(&hstatus, inst->status, sizeof(int), cudaMemcpyDeviceToHost));
   return take_status(*inst, hstatus);
+}
+
+// ---- halo exchange over peer memory ----------------------------------------------
+
+int dnxcu_instance_halo_export(const dnxcu_instance *inst, dnxcu_peer_handle *out) {
+  if (!inst || !out) return DNXCU_E_BAD_ARG;
+  if (!inst->banded || !inst->arena) return DNXCU_E_STATE;
+  memset(out, 0, sizeof(*out));
+  DNXCU_CUDA(cudaSetDevice(inst->model->device));
+  cudaIpcMemHandle_t h;
+  static_assert(sizeof(h) <= sizeof(out->ipc), "handle does not fit");
+  DNXCU_CUDA(cudaIpcGetMemHandle(&h, inst->arena));
+  memcpy(out->ipc, &h, sizeof(h));
+  out->arena_bytes = inst->arena_bytes;
+  out->layout = inst->arena_layout;
+  out->device = inst->model->device;
+  out->pid = (int64_t)getpid();
+  out->local_ptr = (uint64_t)(uintptr_t)inst->arena;
+  out->row0 = inst->band.row0;
+  out->rows = inst->band.rows;
+  return DNXCU_OK;
+}
+
+int dnxcu_instance_halo_connect(dnxcu_instance *inst, const dnxcu_peer_handle *up, const dnxcu_peer_handle *down,
+                                int auto_exchange) {
+  if (!inst) return DNXCU_E_BAD_ARG;
+  if (!inst->banded || !inst->arena || inst->connected) return DNXCU_E_STATE;
+  const bool has_up = inst->band.row0 > 0, has_down = inst->band.row0 + inst->band.rows < inst->band.image_h;
+  if ((has_up && !up) || (has_down && !down)) return DNXCU_E_BAD_ARG;
+  DNXCU_CUDA(cudaSetDevice(inst->model->device));
+  // the neighbour must be the band directly above / below, of the same height and layout (same model, same width)
+  auto check = [&](const dnxcu_peer_handle *p, bool above) -> int {
+    if (p->arena_bytes != inst->arena_bytes || p->layout != inst->arena_layout || p->rows != inst->band.rows)
+      return DNXCU_E_BAD_ARG;
+    const int want_row0 = above ? inst->band.row0 - inst->band.rows : inst->band.row0 + inst->band.rows;
+    return p->row0 == want_row0 ? DNXCU_OK : DNXCU_E_BAD_ARG;
+  };
+  auto open = [&](const dnxcu_peer_handle *p, char **base, bool *ipc) -> int {
+    if (p->pid == (int64_t)getpid()) {
+      // a band of this process: its pointer is usable as it is on the same device; another device of this
+      // process needs peer access switched on
+      if (p->device != inst->model->device) {
+        cudaError_t e = cudaDeviceEnablePeerAccess(p->device, 0);
+        if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return cuda_fail(e);
+        cudaGetLastError();
+      }
+      *base = (char *)(uintptr_t)p->local_ptr;
+      *ipc = false;
+      return DNXCU_OK;
+    }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, p->ipc, sizeof(h));
+    void *ptr = nullptr;
+    DNXCU_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    *base = (char *)ptr;
+    *ipc = true;
+    return DNXCU_OK;
+  };
+  int st;
+  if (has_up && ((st = check(up, true)) || (st = open(up, &inst->peer_up, &inst->peer_up_ipc)))) return st;
+  if (has_down && ((st = check(down, false)) || (st = open(down, &inst->peer_down, &inst->peer_down_ipc)))) return st;
+
+  inst->xchg.assign(inst->disp.size(), dnxcu::XchgArgs());
+  for (dnxcu::XchgArgs &a : inst->xchg) memset(&a, 0, sizeof(a));
+  for (size_t e = 0; e < inst->halos.size(); ++e) {
+    const dnxcu_halo_point &hp = inst->halos[e];
+    const dnxcu_instance::HaloSlot &hs = inst->halo_slots[e];
+    if (hp.row_bytes % 16) return DNXCU_E_UNSUPPORTED;
+    dnxcu::XchgArgs &a = inst->xchg[hs.dispatch];
+    if (a.npoints >= XCHG_MAX_POINTS) return DNXCU_E_LIMIT;
+    dnxcu::XchgPoint &q = a.pt[a.npoints++];
+    q.send_top = (const uint4 *)hp.send_top;
+    q.send_bottom = (const uint4 *)hp.send_bottom;
+    q.n16 = (unsigned)(hp.row_bytes / 16);
+    // my first row is the upper neighbour's "row below"; my last row is the lower neighbour's "row above"
+    q.peer_up_slab = has_up ? (uint4 *)(inst->peer_up + hs.bot_off) : nullptr;
+    q.peer_up_flag = has_up ? (unsigned *)(inst->peer_up + hs.flag_off + 4) : nullptr;
+    q.peer_down_slab = has_down ? (uint4 *)(inst->peer_down + hs.top_off) : nullptr;
+    q.peer_down_flag = has_down ? (unsigned *)(inst->peer_down + hs.flag_off) : nullptr;
+    q.my_flag_top = has_up ? (unsigned *)(inst->arena + hs.flag_off) : nullptr;
+    q.my_flag_bottom = has_down ? (unsigned *)(inst->arena + hs.flag_off + 4) : nullptr;
+    a.done = inst->xchg_ctl + 2 * hs.dispatch;
+    a.counter = inst->xchg_ctl + 2 * hs.dispatch + 1;
+    a.status = inst->status;
+  }
+  inst->connected = true;
+  inst->auto_exchange = auto_exchange != 0;
+  return DNXCU_OK;
+}
+
+int dnxcu_instance_halo_step(dnxcu_instance *inst, int dispatch, uint32_t mode, void *stream) {
+  if (!inst || dispatch < 0 || dispatch >= (int)inst->disp.size() || !(mode & 3u) || (mode & ~3u)) return DNXCU_E_BAD_ARG;
+  if (!inst->connected) return DNXCU_E_STATE;
+  if (inst->xchg[dispatch].npoints == 0) return DNXCU_OK;
+  dnxcu::XchgArgs a = inst->xchg[dispatch];
+  a.mode = mode;
+  a.wait_limit = wait_limit_cycles();
+  return halo_xchg_launch(a, (cudaStream_t)stream);
+}
+
+int dnxcu_instance_halo_reset(dnxcu_instance *inst) {
+  if (!inst) return DNXCU_E_BAD_ARG;
+  if (!inst->banded || !inst->arena) return DNXCU_E_STATE;
+  DNXCU_CUDA(cudaSetDevice(inst->model->device));
+  DNXCU_CUDA(cudaDeviceSynchronize());
+  const size_t flags_off = inst->halo_slots.empty() ? inst->arena_bytes : inst->halo_slots[0].flag_off;
+  DNXCU_CUDA(cudaMemset(inst->arena + flags_off, 0, inst->arena_bytes - flags_off));
+  DNXCU_CUDA(cudaMemset(inst->xchg_ctl, 0, inst->disp.size() * 2 * sizeof(unsigned)));
+  DNXCU_CUDA(cudaDeviceSynchronize());
+  return DNXCU_OK;
+}
+
+int dnxcu_instance_halo_auto(dnxcu_instance *inst, int on) {
+  if (!inst) return DNXCU_E_BAD_ARG;
+  if (!inst->connected) return DNXCU_E_STATE;
+  inst->auto_exchange = on != 0;
+  for (dnxcu_instance::Graph &g : inst->graphs) cudaGraphExecDestroy(g.exec);
+  inst->graphs.clear();  // captured under the other setting
+  return DNXCU_OK;
 }
 
 int dnxcu_instance_halo_count(const dnxcu_instance *inst) { return inst ? (int)inst->halos.size() : DNXCU_E_BAD_ARG; }

@@ -27,6 +27,7 @@ OP_CONV3X3, OP_MAXPOOL2X2, OP_UPSAMPLE2X, OP_CONCAT, OP_RELU, OP_PAD_CHANNELS, O
 F_RELU, F_BIAS, F_UP2X_A, F_POOL_OUT, F_NO_FULL_OUT, F_LEAKY = 0x01, 0x02, 0x04, 0x08, 0x10, 0x20
 OPT_NO_FUSE_ACTIVATION, OPT_NO_FUSE_POOL, OPT_NO_FUSE_UPSAMPLE, OPT_NO_FUSE_CONCAT, OPT_NO_TCGEN05 = 1, 2, 4, 8, 16
 OPT_NO_PAD_INPUT = 32
+OPT_SELECT_BY_COST_ONLY = 64
 
 
 class DnxcuError(RuntimeError):
@@ -87,6 +88,12 @@ class DispatchInfo(C.Structure):
                 ("c_b", C.c_int32), ("c_out", C.c_int32), ("out_tensor", C.c_int32)]
 
 
+class PeerHandle(C.Structure):
+    _fields_ = [("ipc", C.c_ubyte * 64), ("arena_bytes", C.c_uint64), ("layout", C.c_uint64),
+                ("local_ptr", C.c_uint64), ("pid", C.c_int64), ("device", C.c_int32), ("row0", C.c_int32),
+                ("rows", C.c_int32), ("reserved", C.c_int32)]
+
+
 class HaloPoint(C.Structure):
     _fields_ = [("before_dispatch", C.c_int32), ("tensor", C.c_int32), ("send_top", C.c_void_p),
                 ("send_bottom", C.c_void_p), ("recv_top", C.c_void_p), ("recv_bottom", C.c_void_p),
@@ -120,12 +127,18 @@ SIGNATURES = {
     "dnxcu_model_create": (C.c_int, [C.POINTER(ModelDesc), C.c_void_p, C.c_int, C.POINTER(C.c_void_p)]),
     "dnxcu_model_destroy": (None, [C.c_void_p]),
     "dnxcu_model_dispatch_count": (C.c_int, [C.c_void_p]),
+    "dnxcu_instance_dispatch_count": (C.c_int, [C.c_void_p]),
+    "dnxcu_select_min_cost": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                                        C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_double),
+                                        C.POINTER(C.c_int32), C.c_int, C.POINTER(C.c_int32), C.c_int, C.c_int,
+                                        C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_double)]),
     "dnxcu_instance_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(Band), C.POINTER(C.c_void_p)]),
     "dnxcu_instance_destroy": (None, [C.c_void_p]),
     "dnxcu_instance_infer": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "dnxcu_instance_infer_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "dnxcu_instance_wait": (C.c_int, [C.c_void_p]),
     "dnxcu_instance_enqueue": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "dnxcu_instance_graph_cache": (C.c_int, [C.c_void_p, C.c_int]),
     "dnxcu_instance_tensor": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_int),
                                         C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "dnxcu_instance_dispatch_info": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(DispatchInfo)]),
@@ -133,6 +146,11 @@ SIGNATURES = {
                                        C.POINTER(C.c_float)]),
     "dnxcu_instance_halo_count": (C.c_int, [C.c_void_p]),
     "dnxcu_instance_halo": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(HaloPoint)]),
+    "dnxcu_instance_halo_export": (C.c_int, [C.c_void_p, C.POINTER(PeerHandle)]),
+    "dnxcu_instance_halo_connect": (C.c_int, [C.c_void_p, C.POINTER(PeerHandle), C.POINTER(PeerHandle), C.c_int]),
+    "dnxcu_instance_halo_step": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_void_p]),
+    "dnxcu_instance_halo_auto": (C.c_int, [C.c_void_p, C.c_int]),
+    "dnxcu_instance_halo_reset": (C.c_int, [C.c_void_p]),
     "dnxcu_instance_enqueue_range": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "dnxcu_instance_io": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "dnxcu_instance_extent": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int),
@@ -189,6 +207,29 @@ def prepare_weights(variant: int, w_kcrs: np.ndarray, c_a: int, c_b: int = 0) ->
     check(L.dnxcu_prepare_weights(variant, w.ctypes.data, k, c_a, c_b, blob.ctypes.data, C.byref(n)),
           "prepare_weights")
     return blob
+
+
+def select_min_cost(n_nodes, edges, inputs, outputs, min_dispatches=False):
+    """The schedule search on a hand built hypergraph.  edges: list of (sources, destinations, weight).
+    Returns (chosen edge indices in firing order, total cost) or None when the outputs cannot be derived."""
+    i32 = C.c_int32
+    src_off, srcs, dst_off, dsts, w = [0], [], [0], [], []
+    for (s, d, wt) in edges:
+        srcs += list(s)
+        dsts += list(d)
+        src_off.append(len(srcs))
+        dst_off.append(len(dsts))
+        w.append(float(wt))
+    arr = lambda t, v: (t * max(1, len(v)))(*v)
+    chosen = (i32 * max(1, len(edges)))()
+    n, cost = i32(0), C.c_double(0)
+    st = L.dnxcu_select_min_cost(n_nodes, len(edges), arr(i32, src_off), arr(i32, srcs), arr(i32, dst_off), arr(i32, dsts),
+                                 arr(C.c_double, w), arr(i32, list(inputs)), len(inputs), arr(i32, list(outputs)),
+                                 len(outputs), int(min_dispatches), chosen, C.byref(n), C.byref(cost))
+    if st == E_UNSUPPORTED:
+        return None
+    check(st, "dnxcu_select_min_cost")
+    return list(chosen[:n.value]), cost.value
 
 
 def _model_desc(net, options=0):
@@ -303,6 +344,10 @@ class Instance:
     def enqueue(self, dev_in: int, dev_out: int, stream: int = 0):
         check(L.dnxcu_instance_enqueue(self._h, dev_in, dev_out, stream), "dnxcu_instance_enqueue")
 
+    def graph_cache(self, pairs: int):
+        """Keep the captured graphs of this many (input, output) pointer pairs."""
+        check(L.dnxcu_instance_graph_cache(self._h, pairs), "dnxcu_instance_graph_cache")
+
     def enqueue_range(self, first, last, stream=0):
         check(L.dnxcu_instance_enqueue_range(self._h, first, last, stream), "dnxcu_instance_enqueue_range")
 
@@ -323,8 +368,12 @@ class Instance:
               f"dnxcu_instance_tensor({tid})")
         return p.value, h.value, w.value, c.value
 
+    def dispatch_count(self):
+        """Dispatches of this instance's schedule (a database may have chosen another than the model's default)."""
+        return check(L.dnxcu_instance_dispatch_count(self._h))
+
     def dispatch_info(self):
-        n = self.model.dispatch_count()
+        n = self.dispatch_count()
         out = []
         for i in range(n):
             info = DispatchInfo()
@@ -333,7 +382,7 @@ class Instance:
         return out
 
     def bench(self, warmup=3, iters=10):
-        n = self.model.dispatch_count()
+        n = self.dispatch_count()
         infos = (DispatchInfo * n)()
         total = C.c_float()
         check(L.dnxcu_instance_bench(self._h, warmup, iters, infos, n, C.byref(total)), "dnxcu_instance_bench")
@@ -347,6 +396,25 @@ class Instance:
             check(L.dnxcu_instance_halo(self._h, e, C.byref(p)))
             pts.append(p)
         return pts
+
+    def halo_export(self) -> "PeerHandle":
+        h = PeerHandle()
+        check(L.dnxcu_instance_halo_export(self._h, C.byref(h)), "dnxcu_instance_halo_export")
+        return h
+
+    def halo_connect(self, up, down, auto_exchange=True):
+        check(L.dnxcu_instance_halo_connect(self._h, C.byref(up) if up is not None else None,
+                                            C.byref(down) if down is not None else None, int(auto_exchange)),
+              "dnxcu_instance_halo_connect")
+
+    def halo_reset(self):
+        check(L.dnxcu_instance_halo_reset(self._h), "dnxcu_instance_halo_reset")
+
+    def halo_auto(self, on: bool):
+        check(L.dnxcu_instance_halo_auto(self._h, int(on)), "dnxcu_instance_halo_auto")
+
+    def halo_step(self, dispatch, mode, stream=0):
+        check(L.dnxcu_instance_halo_step(self._h, dispatch, mode, stream), "dnxcu_instance_halo_step")
 
     def close(self):
         if self._h:

@@ -187,6 +187,14 @@ def oidn_input(seed: int = 1000, h: int = 1088, w: int = 1920) -> np.ndarray:
     return rng.to_f16(u)
 
 
+def oidn_input_torch(seed: int = 1000, h: int = 1088, w: int = 1920, device="cuda"):
+    """oidn_input generated on `device` with torch: the same bits (see rng.uniform_torch), in a fraction of the time."""
+    import torch
+    u = rng.uniform_torch(seed, h * w * 9, device=device).reshape(h, w, 9)
+    u[:, :, 6:9] = u[:, :, 6:9] * 2.0 - 1.0
+    return u.to(torch.float32).to(torch.float16)
+
+
 def total_flops(net: Net, h: int, w: int) -> int:
     """2 H W 9 C K summed over the convs, at each conv's own resolution."""
     level = {0: 0}

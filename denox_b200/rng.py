@@ -42,3 +42,25 @@ def he_normal_weights(seed: int, c_out: int, c_in: int) -> np.ndarray:
     """[c_out][c_in][3][3] binary16, N(0, 2 / (9 c_in))."""
     std = float(np.sqrt(2.0 / (9.0 * c_in)))
     return to_f16(normal(seed, c_out * c_in * 9, std)).reshape(c_out, c_in, 3, 3)
+
+
+def uniform_torch(seed: int, n: int, lo: float = 0.0, hi: float = 1.0, device="cuda"):
+    """`uniform` evaluated with torch on `device`: the same float64 values, bit for bit (64-bit integer
+    arithmetic wraps the same way; unsigned shifts are emulated with masks).  Returns a float64 tensor."""
+    import torch
+    i64 = torch.int64
+
+    def c(v):  # 64-bit constant as a signed value
+        v &= 0xFFFFFFFFFFFFFFFF
+        return v - (1 << 64) if v >= (1 << 63) else v
+
+    def lsr(z, k):  # logical shift right
+        return (z >> k) & ((1 << (64 - k)) - 1)
+
+    i = torch.arange(1, n + 1, dtype=i64, device=device)
+    z = i * c(0x9E3779B97F4A7C15) + c(seed)
+    z = (z ^ lsr(z, 30)) * c(0xBF58476D1CE4E5B9)
+    z = (z ^ lsr(z, 27)) * c(0x94D049BB133111EB)
+    z = z ^ lsr(z, 31)
+    u = lsr(z, 11).to(torch.float64) * (1.0 / 9007199254740992.0)
+    return lo + (hi - lo) * u

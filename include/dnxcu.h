@@ -297,16 +297,38 @@ typedef struct dnxcu_model_desc {
 #define DNXCU_OPT_NO_FUSE_CONCAT 0x8u
 #define DNXCU_OPT_NO_TCGEN05 0x10u /* reference --fcoopmat off */
 #define DNXCU_OPT_NO_PAD_INPUT 0x20u /* do not copy a ragged input into a zero padded tensor first */
+#define DNXCU_OPT_SELECT_BY_COST_ONLY 0x40u /* schedule selection with a database: skip the reference's pre-filter
+                                               that keeps only the topologies with the fewest dispatches
+                                               (dce/prune_topological.cpp:86-152), so that an un-fused schedule
+                                               can win when the database says it is faster */
 
 typedef struct dnxcu_model dnxcu_model;
 typedef struct dnxcu_instance dnxcu_instance;
 typedef struct dnxcu_db dnxcu_db;
 
-/* db may be NULL: variants are then picked by a fixed preference order. */
+/* db may be NULL: every fusion pattern that applies is taken and variants are picked by a fixed preference
+ * order.  With a database, dnxcu_instance_create builds the graph of all candidate dispatches (fused and
+ * un-fused, every variant) for its extent, weighs them with the database's latencies (1 hour for a candidate
+ * never timed, selection.cpp:21) and runs the minimum cost sub-graph search of the reference
+ * (common/src/denox/algorithm/minimum_const_subgraph.hpp:45-353). */
 DNXCU_API int dnxcu_model_create(const dnxcu_model_desc *desc, const dnxcu_db *db, int device,
                                  dnxcu_model **out);
 DNXCU_API void dnxcu_model_destroy(dnxcu_model *m);
+/* Dispatches of the default schedule (what an instance runs when the model has no database). */
 DNXCU_API int dnxcu_model_dispatch_count(const dnxcu_model *m);
+/* Dispatches of this instance's schedule (may differ from the model's default when a database chose it). */
+DNXCU_API int dnxcu_instance_dispatch_count(const dnxcu_instance *inst);
+/* The schedule search on a caller-built hypergraph: node ids 0 .. n_nodes-1; edge e reads the nodes
+ * srcs[src_off[e] .. src_off[e+1]) and writes dsts[dst_off[e] .. dst_off[e+1]) at cost weight[e].  Writes the
+ * chosen edges in an order in which they can fire to chosen[0 .. *n_chosen) (room for n_edges) and their total
+ * cost to *cost; DNXCU_E_UNSUPPORTED when the outputs cannot be derived from the inputs.  Stands in for
+ * algorithm::minimum_cost_subgraph (common/src/denox/algorithm/minimum_const_subgraph.hpp:45-353); with
+ * min_dispatches != 0 the edges are first reduced to those of sub-graphs with the fewest edges
+ * (prune_topological.cpp:86-152). */
+DNXCU_API int dnxcu_select_min_cost(int n_nodes, int n_edges, const int32_t *src_off, const int32_t *srcs,
+                                    const int32_t *dst_off, const int32_t *dsts, const double *weight,
+                                    const int32_t *inputs, int n_inputs, const int32_t *outputs, int n_outputs,
+                                    int min_dispatches, int32_t *chosen, int32_t *n_chosen, double *cost);
 
 /* Row band of a taller image: band rows [row0, row0+rows) of image height
  * image_h; (0, h, h) = whole image.  All three must be multiples of 16 when
@@ -334,9 +356,12 @@ DNXCU_API int dnxcu_instance_wait(dnxcu_instance *inst);
  * `stream`, nothing is synchronised and nothing else runs on the device.  The
  * schedule is replayed from a CUDA graph; the first call with a new (dev_in,
  * dev_out) pair captures one (host work only, no device work outside `stream`)
- * and the instance keeps the graphs of the last four pairs. */
+ * and the instance keeps the graphs of the most recently used pairs (dnxcu_instance_graph_cache). */
 DNXCU_API int dnxcu_instance_enqueue(dnxcu_instance *inst, const void *dev_in, void *dev_out,
                                      void *stream);
+/* Number of (dev_in, dev_out) pairs whose graph dnxcu_instance_enqueue keeps (default 4, 1 .. 256): a caller
+ * that feeds frames from a ring of n buffers sets it to n, so that no frame re-captures. */
+DNXCU_API int dnxcu_instance_graph_cache(dnxcu_instance *inst, int pairs);
 /* Device pointer and shape of any tensor of the instance after a run (for per
  * layer parity checks): returns the device pointer in *ptr. */
 DNXCU_API int dnxcu_instance_tensor(const dnxcu_instance *inst, int tensor_id, void **ptr,
@@ -380,6 +405,39 @@ typedef struct dnxcu_halo_point {
 } dnxcu_halo_point;
 DNXCU_API int dnxcu_instance_halo_count(const dnxcu_instance *inst);
 DNXCU_API int dnxcu_instance_halo(const dnxcu_instance *inst, int e, dnxcu_halo_point *p);
+/* Direct halo exchange over peer memory, for the row bands of one image on the GPUs of one node (or on one
+ * device).  Every band instance keeps its halo slabs and arrival flags in one allocation; a neighbour writes
+ * its boundary rows straight into them (plain stores through a peer mapping, then a flag), so no copy engine
+ * or collective sits between two convs.  No counterpart in the reference, which runs on one device.
+ *   dnxcu_instance_halo_export : a handle of this band's slabs that can be sent to another process
+ *     (cudaIpcMemHandle inside) or used in this one;
+ *   dnxcu_instance_halo_connect: `up` / `down` are the handles of the bands directly above / below (NULL at
+ *     the image border).  Fails with DNXCU_E_BAD_ARG when a neighbour has another band height, width or
+ *     model, or is not the adjacent band.  With auto_exchange != 0 every dnxcu_instance_enqueue /
+ *     dnxcu_instance_enqueue_range runs the exchange in front of each conv by itself: all bands must then
+ *     run the same frames in the same order, each on ONE stream, on different GPUs (a band that waits for a
+ *     neighbour queued behind it on the same device would wait until its limit);
+ *   dnxcu_instance_halo_step   : with auto_exchange == 0 the caller drives the two halves itself: mode 1
+ *     pushes this band's rows for the conv `dispatch`, mode 2 waits for the neighbours' rows, 3 does both.
+ *     Bands that share a device push for all bands first and wait afterwards.
+ * The wait is bounded (dnxcu_set_wait_limit_us); when it runs out the kernel stores code 10 to the
+ * instance's status word, which dnxcu_instance_wait / infer / bench report as DNXCU_E_DEVICE. */
+typedef struct dnxcu_peer_handle {
+  unsigned char ipc[64];
+  uint64_t arena_bytes, layout, local_ptr;
+  int64_t pid;
+  int32_t device, row0, rows, reserved;
+} dnxcu_peer_handle;
+DNXCU_API int dnxcu_instance_halo_export(const dnxcu_instance *inst, dnxcu_peer_handle *out);
+DNXCU_API int dnxcu_instance_halo_connect(dnxcu_instance *inst, const dnxcu_peer_handle *up,
+                                          const dnxcu_peer_handle *down, int auto_exchange);
+DNXCU_API int dnxcu_instance_halo_step(dnxcu_instance *inst, int dispatch, uint32_t mode, void *stream);
+/* After a wait that ran out the bands no longer agree on how many rows they have swapped.  Once every band
+ * of the image is idle, each calls this: its push counts and arrival flags return to zero (synchronous). */
+DNXCU_API int dnxcu_instance_halo_reset(dnxcu_instance *inst);
+/* Switches the automatic exchange of a connected instance on or off (takes effect for schedules enqueued or
+ * captured afterwards; graphs captured before keep what they were captured with). */
+DNXCU_API int dnxcu_instance_halo_auto(dnxcu_instance *inst, int on);
 /* Runs dispatches [first, last) on `stream` (row band callers interleave this
  * with their halo exchange). */
 DNXCU_API int dnxcu_instance_enqueue_range(dnxcu_instance *inst, int first, int last, void *stream);

@@ -66,3 +66,77 @@ def test_row_bands_equal_whole_image(tmp_path, which, h, w):
     got = np.concatenate([np.load(tmp_path / f"band{r}.npy") for r in range(world)], axis=0)
     assert got.shape == whole.shape
     assert (got == whole).all()
+
+
+# ---- failure paths of the exchange protocol (host side, gloo) ---------------------------------------------
+
+def _failure_worker(rank, world, port, scenario, out_dir):
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    result = "ok"
+    try:
+        if scenario == "mismatched_band_height":
+            # rank 1 believes the image is split 48 / 16 instead of 32 / 32
+            band = (64, 0, 32) if rank == 0 else (64, 48, 16)
+            try:
+                parallel.check_bands(dist, rank, world, band, 40)
+            except ValueError as e:
+                result = "refused: " + str(e)[:40]
+        elif scenario == "missing_peer":
+            row = torch.arange(8, dtype=torch.int16)
+            if rank == 0:
+                got = torch.empty_like(row)
+                t0 = time.time()
+                try:
+                    parallel.exchange_rows(dist, rank, world, row, row, None, got)
+                    result = "returned"
+                except Exception as e:  # the process group's timeout ends the wait
+                    result = f"timeout after {time.time() - t0:.0f}s: {type(e).__name__}"
+            else:
+                time.sleep(6)  # never takes part in the exchange
+                result = "absent"
+        elif scenario == "late_row":
+            row = torch.full((8,), 10 + rank, dtype=torch.int16)
+            got = torch.empty_like(row)
+            if rank == 1:
+                time.sleep(1.0)  # the neighbour is late, but inside the limit
+            if rank == 0:
+                parallel.exchange_rows(dist, rank, world, row, row, None, got)
+            else:
+                parallel.exchange_rows(dist, rank, world, row, row, got, None)
+            result = f"got {int(got[0])}"
+    finally:
+        with open(os.path.join(out_dir, f"r{rank}.txt"), "w") as f:
+            f.write(result)
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def _run_failure(tmp_path, scenario):
+    port = 29100 + (os.getpid() % 800) + {"mismatched_band_height": 1, "missing_peer": 2, "late_row": 3}[scenario]
+    try:
+        mp.spawn(_failure_worker, args=(2, port, scenario, str(tmp_path)), nprocs=2, join=True)
+    except Exception:
+        pass  # a rank may exit with an error after it wrote its result
+    return [open(tmp_path / f"r{r}.txt").read() for r in range(2)]
+
+
+def test_mismatched_band_heights_are_refused_on_every_rank(tmp_path):
+    r = _run_failure(tmp_path, "mismatched_band_height")
+    assert all(x.startswith("refused") for x in r), r
+
+
+def test_missing_peer_ends_in_a_timeout_not_a_hang(tmp_path):
+    r = _run_failure(tmp_path, "missing_peer")
+    assert r[0].startswith("timeout"), r
+    assert r[1] == "absent"
+
+
+def test_late_row_is_waited_for(tmp_path):
+    r = _run_failure(tmp_path, "late_row")
+    assert r == ["got 11", "got 10"], r

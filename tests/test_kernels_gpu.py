@@ -71,7 +71,10 @@ def test_conv_more_shapes_and_leaky_relu(variant, case):
     a, b, wt, bs = mg.conv_case_tensors(case)
     y, _ = run_conv(variant, a, wt, bs, relu=relu, b=b, up_a=up, leaky=leaky, planned=True)
     ref32 = oracle.conv3x3(a, wt, bs, relu=relu, mode=oracle.ACC_F32, b=b, up_a=up, leaky=leaky)
-    assert one_ulp(y, ref32).all(), (name, np.abs(y.astype(np.float32) - ref32.astype(np.float32)).max())
+    # one ulp of the sum (another summation order) becomes up to three of a negative output once it is scaled by alpha
+    ulps = 3.0 if leaky is not None else 1.0
+    d32 = np.abs(y.astype(np.float32) - ref32.astype(np.float32))
+    assert (d32 <= ulps * np.maximum(np.abs(ref32.astype(np.float32)) * 2.0 ** -10, 2.0 ** -14) * 1.01).all(), (name, d32.max())
     ref16 = oracle.conv3x3(a, wt, bs, relu=relu, mode=oracle.ACC_F16, b=b, up_a=up, leaky=leaky)
     if ca + cb >= 256:  # the reference's own tests relax to atol = 1e-1 here (test_conv.py:113-123)
         assert (np.abs(y.astype(np.float32) - ref16.astype(np.float32)) <= 1e-1).all()

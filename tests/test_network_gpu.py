@@ -22,7 +22,7 @@ def fetch(inst, tid):
     return wrap(p, (h, w, c)).cpu().numpy()
 
 
-@pytest.mark.parametrize("options", [0, lib.OPT_NO_TCGEN05,
+@pytest.mark.parametrize("options", [0, lib.OPT_NO_TCGEN05, lib.OPT_NO_PAD_INPUT,
                                      lib.OPT_NO_FUSE_POOL | lib.OPT_NO_FUSE_UPSAMPLE | lib.OPT_NO_FUSE_CONCAT
                                      | lib.OPT_NO_FUSE_ACTIVATION])
 @pytest.mark.parametrize("which,shape,seed,key", [
@@ -212,6 +212,43 @@ def test_database_populate_bench_select(tmp_path):
         d.pc[0], d.pc[1] = info.w, info.h
         assert db.query(d) is not None, info.name
     inst.close(); model.close(); db.close()
+
+
+def test_selection_prefers_the_unfused_schedule_when_the_database_says_so(tmp_path):
+    """Schedule selection by cost: with every candidate timed, the default choice is the fused schedule; after the
+    database is told that every conv with a pooling epilogue takes 100 ms, the search picks conv + basic-pool
+    instead, and the result still matches the oracle."""
+    net = nets.tiny_unet()
+    x = nets.tiny_input(9, 64, 128)
+    ref = oracle.run_network(net, x, oracle.ACC_F32)[net.output_tensor]
+    opts = lib.OPT_SELECT_BY_COST_ONLY
+    db = lib.Db(tmp_path / "sel.db")
+    assert db.populate(net, 64, 128, options=opts) > 20
+    db.bench(min_samples=3, max_relative_error=0.5, max_rounds=1)
+    model = lib.Model(net, db=db, options=opts)
+    inst = lib.Instance(model, 64, 128)
+    names = [i.name.decode() for i in inst.dispatch_info()]
+    assert_close(inst.infer(x), ref, "selected schedule")
+    inst.close()
+    # poison every fused conv + pool candidate of conv0 (16 output channels, full output kept for the skip
+    # connection), whichever way it reads the 3 channel input
+    for v in lib.variants():
+        if v["op"] != lib.OP_CONV3X3 or not (v["allowed_flags"] & lib.F_POOL_OUT):
+            continue
+        for c_in in (3, 16):
+            d = lib.Dispatch()
+            d.variant, d.flags, d.c_a, d.c_out = v["id"], lib.F_RELU | lib.F_POOL_OUT, c_in, 16
+            d.pc[0], d.pc[1] = 128, 64
+            db.add_result(d, [100.0] * 50)
+    inst2 = lib.Instance(model, 64, 128)
+    names2 = [i.name.decode() for i in inst2.dispatch_info()]
+    assert any(n.startswith("basic-pool") for n in names2), (names, names2)
+    assert not any("+pool" in n for n in names2), names2
+    assert inst2.dispatch_count() == len(names2)
+    assert_close(inst2.infer(x), ref, "un-fused schedule chosen by cost")
+    inst2.close()
+    model.close()
+    db.close()
 
 
 def test_infer_async_round_robin_matches_infer():
