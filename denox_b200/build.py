@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libdnxcu.so")
-SOURCES = ["api.cu", "kernels_mem.cu", "conv_direct.cu", "conv_tc.cu", "runtime.cu", "db.cu", "static_scratch.cu", "halo_xchg.cu", "select.cu", "supergraph.cu"]
+SOURCES = ["api.cu", "kernels_mem.cu", "conv_direct.cu", "conv_tc.cu", "runtime.cu", "db.cu", "static_scratch.cu", "halo_xchg.cu", "select.cu", "supergraph.cu", "flatbuf.cu", "dnx.cu", "onnx.cu"]
 
 
 def nvcc_path():
@@ -26,7 +26,10 @@ def needs_build():
     if not os.path.exists(OUT):
         return True
     t = os.path.getmtime(OUT)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(ROOT, "include", "dnxcu.h")]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(ROOT, "include", "dnxcu.h"),
+                                                             os.path.join(HERE, "cli", "main.cpp")]
+    if not os.path.exists(os.path.join(HERE, "dnxcu-cli")):
+        return True
     return any(os.path.getmtime(d) > t for d in deps)
 
 
@@ -77,7 +80,21 @@ def build(force=False, verbose=False, debug_aids=False):
         "-cudart", "static"]
     subprocess.check_call(link)
     os.replace(OUT + ".tmp", OUT)
+    build_cli()
     return OUT
+
+
+CLI = os.path.join(HERE, "dnxcu-cli")
+
+
+def build_cli():
+    """The command line front door (cli/main.cpp): plain C++ over the C ABI, linked against the library next to it."""
+    src = os.path.join(HERE, "cli", "main.cpp")
+    cmd = [os.environ.get("CXX") or shutil.which("g++") or "g++", "-std=c++17", "-O2", "-Wall", "-I", os.path.join(ROOT, "include"),
+           src, "-o", CLI + ".tmp", "-L", HERE, "-ldnxcu", "-Wl,-rpath,$ORIGIN"]
+    subprocess.check_call(cmd)
+    os.replace(CLI + ".tmp", CLI)
+    return CLI
 
 
 if __name__ == "__main__":

@@ -163,7 +163,9 @@ int dnxcu_get_device_caps(int device, dnxcu_caps *caps) {
   caps->smem_per_block_optin = p.sharedMemPerBlockOptin;
   caps->l2_bytes = (uint64_t)p.l2CacheSize;
   caps->global_bytes = (uint64_t)p.totalGlobalMem;
-  strncpy(caps->name, p.name, sizeof(caps->name) - 1);
+  const size_t nlen = strnlen(p.name, sizeof(caps->name) - 1);
+  memcpy(caps->name, p.name, nlen);
+  caps->name[nlen] = 0;
   return DNXCU_OK;
 }
 

@@ -86,6 +86,8 @@ struct TcArgs {
   // (8, 132, 2, 1) lands in shared memory as [chunk][pixel][8 halves] — the MMA's K major core matrix order
   alignas(64) CUtensorMap tm_a;
   alignas(64) CUtensorMap tm_b;
+  // the halo rows of a row band (one row tensors of their own): a above, a below, b above, b below
+  alignas(64) CUtensorMap tm_halo[4];
   Seg a, b;
   const __half *w;  // [9][nch_a + nch_b][N][8]
   const __half *bias;
@@ -284,15 +286,6 @@ __device__ __forceinline__ void tc_zero_cols(uint32_t taddr, int ncols) {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-// Shared memory matrix descriptor, no swizzle, K major:
-// bits [0,14) start >> 4, [16,30) leading byte offset >> 4 (between the two
-// 8 channel core matrices of a K = 16 step), [32,46) stride byte offset >> 4
-// (between 8 row groups), bits [46,48) = 1 (sm_100 descriptor version).
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
-         (1ull << 46);
-}
-
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t *>(&h);
@@ -322,7 +315,9 @@ __device__ __forceinline__ float activate_f(float v, int leaky, uint32_t alpha_h
 }
 
 // Debug time line: role `role` of CTA 0 stores clock64() at event `ev` of its n-th iteration.
+#ifdef DNXCU_DEBUG_AIDS
 constexpr int TRACE_ITERS = 64, TRACE_EVENTS = 6;
+#endif
 __device__ __forceinline__ void trace(const TcArgs &g, int role, int n, int ev) {
 #ifdef DNXCU_DEBUG_AIDS
   if (g.trace && blockIdx.x == 0 && n < TRACE_ITERS) g.trace[(role * TRACE_ITERS + n) * TRACE_EVENTS + ev] = clock64();
@@ -364,9 +359,28 @@ __device__ __forceinline__ void cp_async_wait_dyn(int n) {
 // of the separately stored halo rows of a row band.
 __device__ __forceinline__ bool row_by_tma(const TcArgs &g, const Seg &s, int iy) {
   if (!s.tma && !s.rg) return false;
-  if (iy == -1 && s.top) return false;
-  if (iy == g.H && s.bot) return false;
+  // halo rows of a TMA operand come by TMA too (tensor maps of their own); a ragged operand's by the producer warps
+  if (iy == -1 && s.top) return s.tma != 0;
+  if (iy == g.H && s.bot) return s.tma != 0;
   return true;
+}
+
+// Tensor map and row coordinate for input row iy of operand sg (0: a, 1: b): the operand itself, or the one row
+// tensor that holds the row above / below a row band.  `row` is the coordinate inside the operand (iy, or iy / 2
+// for an operand read through the 2x upsample).
+__device__ __forceinline__ bool banded(const TcArgs &g) { return g.a.top || g.a.bot || g.b.top || g.b.bot; }
+__device__ __forceinline__ const void *tmap_of(const TcArgs &g, int sg, int iy, int row, int *y) {
+  const Seg &s = sg ? g.b : g.a;
+  if (iy == -1 && s.top) {
+    *y = 0;
+    return &g.tm_halo[sg * 2];
+  }
+  if (iy == g.H && s.bot) {
+    *y = 0;
+    return &g.tm_halo[sg * 2 + 1];
+  }
+  *y = row;
+  return sg ? (const void *)&g.tm_b : (const void *)&g.tm_a;
 }
 
 // Raw byte span of a ragged operand's row for the strip starting at x0 (pixels x0-1 .. x0+128 clipped to the
@@ -405,10 +419,12 @@ __device__ __forceinline__ uint32_t tma_row(const TcArgs &g, uint32_t slot_addr,
     if (s.nch == 0) continue;
     const int lo = max(c_lo - chbase, 0), hi = min(c_hi - chbase, s.nch);
     if (hi > lo && s.tma && row_by_tma(g, s, iy)) {
+      int y = iy;
       const void *tm = sg ? (const void *)&g.tm_b : (const void *)&g.tm_a;
+      if (banded(g)) tm = tmap_of(g, sg, iy, iy, &y);
 #pragma unroll 1
       for (int c = lo; c < hi; c += s.tbox) {
-        if (ISSUE) tma_load_4d(slot_addr + (uint32_t)((chbase + c - c_lo) * CHUNK_PITCH), tm, 0, x0 - 1, c, iy, bar);
+        if (ISSUE) tma_load_4d(slot_addr + (uint32_t)((chbase + c - c_lo) * CHUNK_PITCH), tm, 0, x0 - 1, c, y, bar);
         bytes += (uint32_t)s.tbox * CHUNK_PITCH;
       }
     }
@@ -1216,6 +1232,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   };
   // Waits for the entry's slot to be free, arms its raw barrier with the byte count and starts the copies:
   // operand a's half resolution row into the slot's staging buffer, operand b's row straight into the slot.
+  const bool band = banded(g);
   auto xp_issue = [&](XpCursor &is, int pipe) -> bool {
     const int bofs = pipe * ST_PIPE_STRIDE;
     const uint32_t slots_addr = slots_addr0 + (uint32_t)(pipe * S) * slot_bytes;
@@ -1244,17 +1261,38 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     if (bytes) {
       mbar_expect_tx(rb, bytes);
       if (a_eng && g.a.tma) {
-        if (g.a.up) {
-          for (int c = a_lo; c < a_hi; c += 2)  // two chunks of the half resolution row, packed, at the first one's place
-            tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, (is.t.x0 >> 1) - 1, c, iy >> 1, rb);
+        // (the common case, no row band, keeps the operand's own map as a fixed address)
+        if (!band) {
+          if (g.a.up) {
+            for (int c = a_lo; c < a_hi; c += 2)  // two chunks of the half resolution row, packed, at the first one's place
+              tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, (is.t.x0 >> 1) - 1, c, iy >> 1, rb);
+          } else {
+            for (int c = a_lo; c < a_hi; c += g.a.tbox)
+              tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, is.t.x0 - 1, c, iy, rb);
+          }
         } else {
-          for (int c = a_lo; c < a_hi; c += g.a.tbox)
-            tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, is.t.x0 - 1, c, iy, rb);
+          int y;
+          const void *tm = tmap_of(g, 0, iy, g.a.up ? iy >> 1 : iy, &y);
+          if (g.a.up) {
+            for (int c = a_lo; c < a_hi; c += 2)
+              tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), tm, 0, (is.t.x0 >> 1) - 1, c, y, rb);
+          } else {
+            for (int c = a_lo; c < a_hi; c += g.a.tbox)
+              tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), tm, 0, is.t.x0 - 1, c, y, rb);
+          }
         }
       }
-      if (b_eng && g.b.tma)
-        for (int c = b_lo; c < b_hi; c += g.b.tbox)
-          tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, is.t.x0 - 1, c - nca, iy, rb);
+      if (b_eng && g.b.tma) {
+        if (!band) {
+          for (int c = b_lo; c < b_hi; c += g.b.tbox)
+            tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, is.t.x0 - 1, c - nca, iy, rb);
+        } else {
+          int y;
+          const void *tm = tmap_of(g, 1, iy, iy, &y);
+          for (int c = b_lo; c < b_hi; c += g.b.tbox)
+            tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), tm, 0, is.t.x0 - 1, c - nca, y, rb);
+        }
+      }
       if (a_raw) bulk_g2s(slot_addr + (uint32_t)((a_lo - c_lo) * CHUNK_PITCH), ra.src, ra.bytes, rb);
       if (b_raw) bulk_g2s(slot_addr + (uint32_t)((b_lo - c_lo) * CHUNK_PITCH), rbs.src, rbs.bytes, rb);
     } else {
@@ -1539,10 +1577,19 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
                 for (int r = 0; r < g.ER; ++r) {
                   const int iy = t.y0 - 1 + jj + r;
                   const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes + (uint32_t)r * row_bytes;
-                  for (int c = c_lo; c < min(c_hi, nca); c += g.a.tbox)
-                    tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, t.x0 - 1, c, iy, fb);
-                  for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
-                    tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, t.x0 - 1, c - nca, iy, fb);
+                  if (!band) {
+                    for (int c = c_lo; c < min(c_hi, nca); c += g.a.tbox)
+                      tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, t.x0 - 1, c, iy, fb);
+                    for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
+                      tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, t.x0 - 1, c - nca, iy, fb);
+                  } else {
+                    int ya, yb;
+                    const void *tma = tmap_of(g, 0, iy, iy, &ya), *tmb = tmap_of(g, 1, iy, iy, &yb);
+                    for (int c = c_lo; c < min(c_hi, nca); c += g.a.tbox)
+                      tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), tma, 0, t.x0 - 1, c, ya, fb);
+                    for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
+                      tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), tmb, 0, t.x0 - 1, c - nca, yb, fb);
+                  }
                 }
               } else {
                 // timing aid: nothing will land, so complete the transaction count by hand
@@ -1933,6 +1980,20 @@ int make_tensor_map(CUtensorMap *tm, const void *ptr, int H, int W, int C, int b
   return r == CUDA_SUCCESS ? DNXCU_OK : DNXCU_E_CUDA;
 }
 
+// One row tensor maps for the halo rows of a row band, per operand that is fetched by TMA: the same box as the
+// operand's own map (a half resolution row for an operand read through the 2x upsample).
+int encode_halo_maps(TcArgs &g, int W) {
+  memset(g.tm_halo, 0, sizeof(g.tm_halo));
+  for (int sg = 0; sg < 2; ++sg) {
+    const Seg &s = sg ? g.b : g.a;
+    if (!s.tma || s.nch == 0) continue;
+    const int Ws = s.up ? W / 2 : W, chunks = s.up ? 2 : s.tbox, px = s.up ? SRC_PX : WH;
+    if (s.top && make_tensor_map(&g.tm_halo[sg * 2], s.top, 1, Ws, s.C, chunks, px)) return DNXCU_E_CUDA;
+    if (s.bot && make_tensor_map(&g.tm_halo[sg * 2 + 1], s.bot, 1, Ws, s.C, chunks, px)) return DNXCU_E_CUDA;
+  }
+  return DNXCU_OK;
+}
+
 // Plan of the stacked form: weights resident, one K group, TMEM ring of NB blocks.
 // Expects pl.args filled up to the operand description (done by make_plan).
 int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode) {
@@ -2073,6 +2134,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   pl.R = 0;
   memset(&g.tm_a, 0, sizeof(g.tm_a));
   memset(&g.tm_b, 0, sizeof(g.tm_b));
+  memset(g.tm_halo, 0, sizeof(g.tm_halo));
   if (encode) {
     if (g.xp && g.a.up) {
       if (make_tensor_map(&g.tm_a, d.in_a, H / 2, W / 2, d.c_a, 2, SRC_PX)) return DNXCU_E_CUDA;
@@ -2080,6 +2142,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
       return DNXCU_E_CUDA;
     }
     if (g.b.tma && make_tensor_map(&g.tm_b, d.in_b, H, W, d.c_b, g.b.tbox)) return DNXCU_E_CUDA;
+    if (encode_halo_maps(g, W)) return DNXCU_E_CUDA;
   }
   return DNXCU_OK;
 }
@@ -2127,7 +2190,9 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   };
   g.a.rg = raggable(d.in_a, d.c_a, up) ? 1 : 0;
   g.b.rg = raggable(d.in_b, d.c_b, false) ? 1 : 0;
-  g.cpa = (!g.a.tma || (d.c_b > 0 && !g.b.tma) || d.halo[0] || d.halo[1] || d.halo[2] || d.halo[3]) ? 1 : 0;
+  // the producer warps copy what the copy engine cannot: operands without a tensor map (halo rows of operands
+  // with one come through one row tensor maps of their own)
+  g.cpa = (!g.a.tma || (d.c_b > 0 && !g.b.tma)) ? 1 : 0;
   g.w = (const __half *)d.weights;
   g.bias = (d.flags & DNXCU_F_BIAS) ? (const __half *)d.bias : nullptr;
   g.out = (__half *)d.out;
@@ -2229,9 +2294,11 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   pl.R = R;
   memset(&g.tm_a, 0, sizeof(g.tm_a));
   memset(&g.tm_b, 0, sizeof(g.tm_b));
+  memset(g.tm_halo, 0, sizeof(g.tm_halo));
   if (encode) {
     if (g.a.tma && make_tensor_map(&g.tm_a, d.in_a, H, W, d.c_a, g.a.tbox)) return DNXCU_E_CUDA;
     if (g.b.tma && make_tensor_map(&g.tm_b, d.in_b, H, W, d.c_b, g.b.tbox)) return DNXCU_E_CUDA;
+    if (encode_halo_maps(g, W)) return DNXCU_E_CUDA;
   }
   return DNXCU_OK;
 }

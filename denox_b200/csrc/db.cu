@@ -222,41 +222,60 @@ int dnxcu_db_atomic_writeback(dnxcu_db *db) {
   return DNXCU_OK;
 }
 
-int dnxcu_db_populate(dnxcu_db *db, const dnxcu_model_desc *desc, int height, int width, int device) {
-  if (!db || !desc || height <= 0 || width <= 0) return DNXCU_E_BAD_ARG;
-  dnxcu_model m;
-  // the candidates are those the device can run (the reference prunes its configuration space with the
-  // device info the same way, DirectConvShaderCM.cpp:19-28); device < 0: no device at hand, every variant counts
-  bool allow_tc = !(desc->options & DNXCU_OPT_NO_TCGEN05);
-  if (device >= 0) {
-    dnxcu_caps caps;
-    int cst = dnxcu_get_device_caps(device, &caps);
-    if (cst) return cst;
-    allow_tc = allow_tc && caps.tcgen05;
-    cudaSetDevice(device);  // launch geometry (part of an entry's key) follows this device's SM count
-  }
-  int st = build_fused_ops(*desc, allow_tc, m);
-  if (st) return st;
-  m.options = desc->options;
-  // every candidate dispatch of the model at this extent: each node alone, each fusion pattern, each variant that
-  // takes it; reduced, like the reference's populate (populate.cpp:41), to the topologies with the fewest
-  // dispatches unless the model asks for selection by cost alone
+// Every candidate dispatch of the model at this extent: each node alone, each fusion pattern, each variant that
+// takes it; reduced, like the reference's populate (populate.cpp:41), to the topologies with the fewest
+// dispatches unless the model asks for selection by cost alone.
+static int populate_model(dnxcu_db &db, const dnxcu_model &m, bool allow_tc, int height, int width) {
+  if (m.from_dnx || m.nodes.empty()) return DNXCU_E_STATE;  // a compiled model has no candidates left to choose from
   HyperGraph g;
   std::vector<Candidate> cands;
-  st = build_supergraph(m, allow_tc, height, width, g, cands);
+  int st = build_supergraph(m, allow_tc, height, width, g, cands);
   if (st) return st;
-  if (!(desc->options & DNXCU_OPT_SELECT_BY_COST_ONLY) &&
-      !prune_topological(g, {desc->input_tensor}, {desc->output_tensor}))
+  if (!(m.options & DNXCU_OPT_SELECT_BY_COST_ONLY) && !prune_topological(g, {m.input_tensor}, {m.output_tensor}))
     return DNXCU_E_UNSUPPORTED;
   int added = 0;
   for (const HyperEdge &e : g.edges) {
     const Candidate &c = cands[e.payload];
     const dnxcu_dispatch d = probe_dispatch(c.op, height, width, c.variant);
     bool is_new = false;
-    find_or_add(*db, d, true, &is_new);
+    find_or_add(db, d, true, &is_new);
     if (is_new) ++added;
   }
   return added;
+}
+
+// The candidates are those the device can run (the reference prunes its configuration space with the device info
+// the same way, DirectConvShaderCM.cpp:19-28); device < 0: no device at hand, every variant counts.
+static int device_allows_tc(int device, uint32_t options, bool *allow_tc) {
+  *allow_tc = !(options & DNXCU_OPT_NO_TCGEN05);
+  if (device >= 0) {
+    dnxcu_caps caps;
+    int cst = dnxcu_get_device_caps(device, &caps);
+    if (cst) return cst;
+    *allow_tc = *allow_tc && caps.tcgen05;
+    cudaSetDevice(device);  // launch geometry follows this device's SM count
+  }
+  return DNXCU_OK;
+}
+
+int dnxcu_db_populate(dnxcu_db *db, const dnxcu_model_desc *desc, int height, int width, int device) {
+  if (!db || !desc || height <= 0 || width <= 0) return DNXCU_E_BAD_ARG;
+  bool allow_tc;
+  int st = device_allows_tc(device, desc->options, &allow_tc);
+  if (st) return st;
+  dnxcu_model m;
+  st = build_fused_ops(*desc, allow_tc, m);
+  if (st) return st;
+  m.options = desc->options;
+  return populate_model(*db, m, allow_tc, height, width);
+}
+
+int dnxcu_db_populate_model(dnxcu_db *db, const dnxcu_model *m, int height, int width, int device) {
+  if (!db || !m || height <= 0 || width <= 0) return DNXCU_E_BAD_ARG;
+  bool allow_tc;
+  int st = device_allows_tc(device, m->options, &allow_tc);
+  if (st) return st;
+  return populate_model(*db, *m, allow_tc, height, width);
 }
 
 int dnxcu_db_query(const dnxcu_db *db, const dnxcu_dispatch *d, double *mean_ms, double *std_ms, int *samples) {

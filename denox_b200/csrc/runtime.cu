@@ -444,21 +444,131 @@ extern "C" {
 
 int dnxcu_model_create(const dnxcu_model_desc *desc, const dnxcu_db *db, int device, dnxcu_model **out) {
   if (!desc || !out) return DNXCU_E_BAD_ARG;
-  dnxcu_caps caps;
-  int st = dnxcu_get_device_caps(device, &caps);
-  if (st) return st;
+  int st;
+  bool allow_tc = !(desc->options & DNXCU_OPT_NO_TCGEN05);
+  if (device >= 0) {
+    dnxcu_caps caps;
+    st = dnxcu_get_device_caps(device, &caps);
+    if (st) return st;
+    allow_tc = allow_tc && caps.tcgen05;
+  }  // device < 0: no device at hand (compiling a model to a dnx file): every capability is assumed
   std::unique_ptr<dnxcu_model> m(new (std::nothrow) dnxcu_model());
   if (!m) return DNXCU_E_NO_MEMORY;
-  const bool allow_tc = caps.tcgen05 && !(desc->options & DNXCU_OPT_NO_TCGEN05);
   st = build_fused_ops(*desc, allow_tc, *m);
   if (st) return st;
-  m->device = device;
+  m->device = device < 0 ? 0 : device;
   m->db = db;
   *out = m.release();
   return DNXCU_OK;
 }
 
 void dnxcu_model_destroy(dnxcu_model *m) { delete m; }
+const char *dnxcu_last_error_message(void) { return error_text(); }
+
+int dnxcu_model_create_from_onnx(const void *bytes, size_t n, const dnxcu_db *db, int device, uint32_t options,
+                                 dnxcu_model **out) {
+  if (!bytes || !out) return DNXCU_E_BAD_ARG;
+  int st;
+  bool allow_tc = !(options & DNXCU_OPT_NO_TCGEN05);
+  if (device >= 0) {
+    dnxcu_caps caps;
+    st = dnxcu_get_device_caps(device, &caps);
+    if (st) return st;
+    allow_tc = allow_tc && caps.tcgen05;
+  }
+  std::unique_ptr<dnxcu_model> m(new (std::nothrow) dnxcu_model());
+  if (!m) return DNXCU_E_NO_MEMORY;
+  st = import_onnx(bytes, n, options, *m, allow_tc);
+  if (st) return st;
+  m->device = device < 0 ? 0 : device;
+  m->db = db;
+  *out = m.release();
+  return DNXCU_OK;
+}
+
+int dnxcu_model_create_from_dnx(const void *bytes, size_t n, int device, dnxcu_model **out) {
+  if (!bytes || !out) return DNXCU_E_BAD_ARG;
+  std::unique_ptr<dnxcu_model> m(new (std::nothrow) dnxcu_model());
+  if (!m) return DNXCU_E_NO_MEMORY;
+  int st = read_dnx(bytes, n, *m, &m->dnx_align);
+  if (st) return st;
+  if (device >= 0) {
+    dnxcu_caps caps;
+    st = dnxcu_get_device_caps(device, &caps);
+    if (st) return st;
+    for (int v : m->dnx_variants)
+      if (get_variant(v)->desc.needs_tcgen05 && !caps.tcgen05) return DNXCU_E_UNSUPPORTED;
+  }
+  m->device = device < 0 ? 0 : device;
+  *out = m.release();
+  return DNXCU_OK;
+}
+
+static int hand_out(const std::vector<uint8_t> &blob, void *out, size_t *bytes) {
+  if (!out) {
+    *bytes = blob.size();
+    return DNXCU_OK;
+  }
+  if (*bytes < blob.size()) return DNXCU_E_BAD_ARG;
+  memcpy(out, blob.data(), blob.size());
+  *bytes = blob.size();
+  return DNXCU_OK;
+}
+
+static int model_align(const std::vector<TensorInfo> &tensors) {
+  int maxlevel = 0;
+  for (const TensorInfo &t : tensors) maxlevel = t.level > maxlevel ? t.level : maxlevel;
+  return 1 << maxlevel;
+}
+
+int dnxcu_model_write_dnx(const dnxcu_model *m, void *out, size_t *bytes) {
+  if (!m || !bytes) return DNXCU_E_BAD_ARG;
+  std::vector<int> variants;
+  if (m->from_dnx) {
+    variants = m->dnx_variants;
+  } else {
+    // no extent, no database: per dispatch the first variant of the preference order that takes it
+    const int align = model_align(m->tensors);
+    const int probe = 16 * align;
+    for (const FusedOp &op : m->ops) {
+      std::vector<int> cand;
+      candidate_variants(op, !(m->options & DNXCU_OPT_NO_TCGEN05), cand);
+      int chosen = -1;
+      for (int id : cand) {
+        const dnxcu_dispatch d = probe_dispatch(op, probe, probe, id);
+        if (dnxcu_validate(&d) == DNXCU_OK) {
+          chosen = id;
+          break;
+        }
+      }
+      if (chosen < 0) return DNXCU_E_UNSUPPORTED;
+      variants.push_back(chosen);
+    }
+  }
+  std::vector<uint8_t> blob;
+  int st = write_dnx(*m, m->ops, m->tensors, variants, model_align(m->tensors), blob);
+  if (st) return st;
+  return hand_out(blob, out, bytes);
+}
+
+int dnxcu_instance_write_dnx(const dnxcu_instance *inst, void *out, size_t *bytes) {
+  if (!inst || !bytes) return DNXCU_E_BAD_ARG;
+  std::vector<int> variants;
+  for (const dnxcu_dispatch &d : inst->disp) variants.push_back(d.variant);
+  std::vector<uint8_t> blob;
+  int st = write_dnx(*inst->model, inst->ops, inst->tensors, variants, model_align(inst->tensors), blob);
+  if (st) return st;
+  return hand_out(blob, out, bytes);
+}
+
+int dnxcu_model_io(const dnxcu_model *m, int *input_tensor, int *input_channels, int *output_tensor) {
+  if (!m) return DNXCU_E_BAD_ARG;
+  if (input_tensor) *input_tensor = m->input_tensor;
+  if (input_channels) *input_channels = m->input_channels;
+  if (output_tensor) *output_tensor = m->output_tensor;
+  return DNXCU_OK;
+}
+
 int dnxcu_model_dispatch_count(const dnxcu_model *m) { return m ? (int)m->ops.size() : DNXCU_E_BAD_ARG; }
 int dnxcu_instance_dispatch_count(const dnxcu_instance *inst) { return inst ? (int)inst->disp.size() : DNXCU_E_BAD_ARG; }
 
@@ -536,7 +646,8 @@ int dnxcu_instance_create(const dnxcu_model *m, int height, int width, const dnx
   // (row bands take the default schedule: every band must run the same dispatches)
   inst->ops = m->ops;
   inst->tensors = m->tensors;
-  if (m->db && !band) {
+  if (m->from_dnx) inst->preset_variant = m->dnx_variants;  // a compiled model: schedule and variants are the file's
+  if (m->db && !band && !m->from_dnx) {
     std::vector<FusedOp> sel_ops;
     std::vector<TensorInfo> sel_tensors;
     std::vector<int> sel_variants;
@@ -693,8 +804,13 @@ int dnxcu_instance_create(const dnxcu_model *m, int height, int width, const dnx
       st = dnxcu_prepare_weights(chosen, nullptr, op.c_out, op.c_a, op.c_b, nullptr, &bytes);
       if (st) return st;
       std::vector<unsigned char> blob(bytes);
-      st = dnxcu_prepare_weights(chosen, op.weights_kcrs.data(), op.c_out, op.c_a, op.c_b, blob.data(), &bytes);
-      if (st) return st;
+      if (!op.prepared.empty()) {
+        if (op.prepared.size() != bytes) return DNXCU_E_STATE;
+        blob = op.prepared;  // a dnx file carries the weights in the variant's layout already
+      } else {
+        st = dnxcu_prepare_weights(chosen, op.weights_kcrs.data(), op.c_out, op.c_a, op.c_b, blob.data(), &bytes);
+        if (st) return st;
+      }
       void *dw = nullptr;
       st = dev_alloc(*inst, bytes, &dw);
       if (st) return st;

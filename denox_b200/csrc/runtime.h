@@ -22,6 +22,7 @@ struct FusedOp {
   int src_node = -1;
   float alpha = 0.0f;                  // slope of a (fused or standalone) LeakyReLU
   bool pad_a = false, pad_b = false;   // the operand is the zero padded copy of the ragged network input
+  std::vector<unsigned char> prepared; // conv of a model read from a dnx file: the weights in the variant's layout
   std::vector<uint16_t> weights_kcrs;  // conv
   std::vector<uint16_t> bias;          // conv, may be empty
   std::string name;
@@ -49,6 +50,9 @@ struct dnxcu_model {
   int n_model_tensors = 0;
   std::vector<dnxcu::NodeRec> nodes;
   std::vector<dnxcu::FusedOp> ops;         // the default schedule: every fusion pattern that applies
+  bool from_dnx = false;                   // read from a dnx file: `ops` is the file's schedule, variants fixed
+  std::vector<int> dnx_variants;
+  int dnx_align = 1;
   int input_tensor = -1, output_tensor = -1, input_channels = 0;
   uint32_t options = 0;
   int device = 0;
@@ -74,4 +78,13 @@ int select_schedule(const dnxcu_model &m, const dnxcu_db *db, bool allow_tc, int
                     std::vector<TensorInfo> &tensors, std::vector<int> &variants, double *total_ms);
 // Validation probe of an op at an extent (placeholder pointers).
 dnxcu_dispatch probe_dispatch(const FusedOp &op, int H, int W, int variant);
+// dnx container (dnx.cu): a schedule with its variants and parameters -> bytes, and back.
+int write_dnx(const dnxcu_model &m, const std::vector<FusedOp> &ops, const std::vector<TensorInfo> &tensors,
+              const std::vector<int> &variants, int align, std::vector<uint8_t> &out);
+int read_dnx(const void *bytes, size_t n, dnxcu_model &m, int *align_out);
+// ONNX subset import (onnx.cu): fills the model like dnxcu_model_create does from a node list.
+int import_onnx(const void *bytes, size_t n, uint32_t options, dnxcu_model &m, bool allow_tc);
+// Text of the last import failure on this thread.
+void set_error_text(const std::string &s);
+const char *error_text();
 }  // namespace dnxcu

@@ -126,6 +126,12 @@ SIGNATURES = {
     "dnxcu_f16_to_float": (C.c_float, [C.c_uint16]),
     "dnxcu_model_create": (C.c_int, [C.POINTER(ModelDesc), C.c_void_p, C.c_int, C.POINTER(C.c_void_p)]),
     "dnxcu_model_destroy": (None, [C.c_void_p]),
+    "dnxcu_model_write_dnx": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_size_t)]),
+    "dnxcu_instance_write_dnx": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_size_t)]),
+    "dnxcu_model_create_from_dnx": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int, C.POINTER(C.c_void_p)]),
+    "dnxcu_model_create_from_onnx": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_int, C.c_uint32, C.POINTER(C.c_void_p)]),
+    "dnxcu_last_error_message": (C.c_char_p, []),
+    "dnxcu_model_io": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "dnxcu_model_dispatch_count": (C.c_int, [C.c_void_p]),
     "dnxcu_instance_dispatch_count": (C.c_int, [C.c_void_p]),
     "dnxcu_select_min_cost": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int32),
@@ -159,6 +165,7 @@ SIGNATURES = {
     "dnxcu_db_close": (None, [C.c_void_p]),
     "dnxcu_db_size": (C.c_int, [C.c_void_p]),
     "dnxcu_db_populate": (C.c_int, [C.c_void_p, C.POINTER(ModelDesc), C.c_int, C.c_int, C.c_int]),
+    "dnxcu_db_populate_model": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "dnxcu_db_bench": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_double, C.c_int]),
     "dnxcu_db_atomic_writeback": (C.c_int, [C.c_void_p]),
     "dnxcu_db_query": (C.c_int, [C.c_void_p, C.POINTER(Dispatch), C.POINTER(C.c_double), C.POINTER(C.c_double),
@@ -288,6 +295,14 @@ class Db:
         return check(L.dnxcu_db_add_result(self._h, C.byref(d), arr, len(samples_ms)), "dnxcu_db_add_result")
 
 
+def _write_blob(fn, handle, what):
+    n = C.c_size_t(0)
+    check(fn(handle, None, C.byref(n)), what + "(size)")
+    buf = (C.c_ubyte * n.value)()
+    check(fn(handle, buf, C.byref(n)), what)
+    return bytes(buf[:n.value])
+
+
 class Model:
     """Fused dispatch list of a network (runtime::Model)."""
 
@@ -299,6 +314,37 @@ class Model:
         check(L.dnxcu_model_create(C.byref(desc), db._h if db else None, device, C.byref(self._h)),
               "dnxcu_model_create")
         self.device = device
+
+    @classmethod
+    def from_dnx(cls, blob: bytes, net=None, device=0):
+        """A model that runs the dispatches of a dnx file (runtime::Model::make).  `net` only supplies the
+        channel counts the host-side convenience calls need; device < 0 parses without touching a device."""
+        self = cls.__new__(cls)
+        self.net, self._keep, self._db, self.device = net, None, None, device
+        self._h = C.c_void_p()
+        check(L.dnxcu_model_create_from_dnx(blob, len(blob), device, C.byref(self._h)), "dnxcu_model_create_from_dnx")
+        return self
+
+    @classmethod
+    def from_onnx(cls, blob: bytes, device=0, options=0, db: Db = None):
+        """A model imported from the bytes of an ONNX file (the reference's frontend subset)."""
+        self = cls.__new__(cls)
+        self.net, self._keep, self._db, self.device = None, None, db, device
+        self._h = C.c_void_p()
+        st = L.dnxcu_model_create_from_onnx(blob, len(blob), db._h if db else None, device, options, C.byref(self._h))
+        if st < 0:
+            raise DnxcuError(st, "dnxcu_model_create_from_onnx: " + L.dnxcu_last_error_message().decode())
+        return self
+
+    def io(self):
+        """(input tensor id, input channels, output tensor id)."""
+        a, c, b = C.c_int(), C.c_int(), C.c_int()
+        check(L.dnxcu_model_io(self._h, C.byref(a), C.byref(c), C.byref(b)))
+        return a.value, c.value, b.value
+
+    def write_dnx(self) -> bytes:
+        """The default schedule with the preferred variant per dispatch as a dnx file (no device needed)."""
+        return _write_blob(L.dnxcu_model_write_dnx, self._h, "dnxcu_model_write_dnx")
 
     def dispatch_count(self):
         return check(L.dnxcu_model_dispatch_count(self._h))
@@ -323,10 +369,10 @@ class Instance:
 
     def infer(self, x: np.ndarray) -> np.ndarray:
         """Host in, host out, synchronous (Instance::infer)."""
-        net = self.model.net
+        _, in_channels, out_tensor = self.model.io()
         x = np.ascontiguousarray(x, dtype=np.float16)
-        assert x.shape == (self.rows, self.w, net.in_channels), x.shape
-        _, h, w, c = self.tensor(net.output_tensor)
+        assert x.shape == (self.rows, self.w, in_channels), x.shape
+        _, h, w, c = self.tensor(out_tensor)
         fh, fw, rh, rw = self.extent()
         if (fh, fw) != (rh, rw):  # the instance pads the frame and slices the output back
             h, w = fh, fw
@@ -343,6 +389,10 @@ class Instance:
 
     def enqueue(self, dev_in: int, dev_out: int, stream: int = 0):
         check(L.dnxcu_instance_enqueue(self._h, dev_in, dev_out, stream), "dnxcu_instance_enqueue")
+
+    def write_dnx(self) -> bytes:
+        """This instance's schedule and variants (what a benchmark database chose) as a dnx file."""
+        return _write_blob(L.dnxcu_instance_write_dnx, self._h, "dnxcu_instance_write_dnx")
 
     def graph_cache(self, pairs: int):
         """Keep the captured graphs of this many (input, output) pointer pairs."""

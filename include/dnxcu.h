@@ -310,10 +310,14 @@ typedef struct dnxcu_db dnxcu_db;
  * order.  With a database, dnxcu_instance_create builds the graph of all candidate dispatches (fused and
  * un-fused, every variant) for its extent, weighs them with the database's latencies (1 hour for a candidate
  * never timed, selection.cpp:21) and runs the minimum cost sub-graph search of the reference
- * (common/src/denox/algorithm/minimum_const_subgraph.hpp:45-353). */
+ * (common/src/denox/algorithm/minimum_const_subgraph.hpp:45-353).
+ * device < 0: no device is touched and every capability is assumed (a model that is only written to a dnx
+ * file); instances of such a model run on device 0. */
 DNXCU_API int dnxcu_model_create(const dnxcu_model_desc *desc, const dnxcu_db *db, int device,
                                  dnxcu_model **out);
 DNXCU_API void dnxcu_model_destroy(dnxcu_model *m);
+/* Tensor ids of the model's input and output and the input's channel count (any pointer may be NULL). */
+DNXCU_API int dnxcu_model_io(const dnxcu_model *m, int *input_tensor, int *input_channels, int *output_tensor);
 /* Dispatches of the default schedule (what an instance runs when the model has no database). */
 DNXCU_API int dnxcu_model_dispatch_count(const dnxcu_model *m);
 /* Dispatches of this instance's schedule (may differ from the model's default when a database chose it). */
@@ -329,6 +333,35 @@ DNXCU_API int dnxcu_select_min_cost(int n_nodes, int n_edges, const int32_t *src
                                     const int32_t *dst_off, const int32_t *dsts, const double *weight,
                                     const int32_t *inputs, int n_inputs, const int32_t *outputs, int n_outputs,
                                     int min_dispatches, int32_t *chosen, int32_t *n_chosen, double *cost);
+
+/* A model from the bytes of an ONNX file.  Accepts what the reference's importer accepts of the operators this
+ * backend runs (compiler/src/denox/compiler/frontend/onnx/onnx.cpp:32-160, details/ops/{conv,max_pool,resize,
+ * concat,relu,leaky_relu}.cpp): Conv 3x3 with stride 1, dilation 1, group 1 and extent preserving padding
+ * (OIHW weights, float or float16 constants), Relu, LeakyRelu, MaxPool 2x2 / stride 2 without auto_pad,
+ * ceil_mode or indices, Resize / Upsample nearest x2 with asymmetric coordinates and constant scales, Concat of
+ * two runtime tensors on the channel axis; one runtime input (NCHW, constant channel count) and one output.
+ * Anything else: DNXCU_E_UNSUPPORTED, with the reason in dnxcu_last_error_message().  fp32 weights become
+ * binary16 by the reference's truncating conversion.  db / device / options as for dnxcu_model_create. */
+DNXCU_API int dnxcu_model_create_from_onnx(const void *bytes, size_t n, const dnxcu_db *db, int device,
+                                           uint32_t options, dnxcu_model **out);
+/* Text that explains the most recent import failure on this thread (empty if none). */
+DNXCU_API const char *dnxcu_last_error_message(void);
+
+/* dnx files (dnx.fbs:1-195 of the reference: tensors with symbolic extents, buffers, parameter initializers,
+ * dispatches with bindings and push constants, the symbolic expression list over H and W).
+ *   dnxcu_model_write_dnx    : the model's default schedule with the preferred variant per dispatch: a
+ *                              compiled model that does not depend on an extent (no device needed);
+ *   dnxcu_instance_write_dnx : the instance's own schedule and variants (what a benchmark database chose);
+ *   dnxcu_model_create_from_dnx : a model that runs exactly the file's dispatches; instances of it take any
+ *                              extent the file's alignment allows.  device < 0: parse only.
+ * Call the writers with out == NULL to get the size in *bytes.  Stands in for the reference's serialize step
+ * (compiler/src/denox/compiler/serialize/serialize.cpp:1-635) and runtime::Model::make
+ * (runtime/src/denox/runtime/model.hpp:109-118).  The `shader_binaries` of these files hold a descriptor of the
+ * CUDA kernel variant (first word "DNXC") where the reference holds SPIR-V; a file with SPIR-V binaries is
+ * refused with DNXCU_E_UNSUPPORTED. */
+DNXCU_API int dnxcu_model_write_dnx(const dnxcu_model *m, void *out, size_t *bytes);
+DNXCU_API int dnxcu_instance_write_dnx(const dnxcu_instance *inst, void *out, size_t *bytes);
+DNXCU_API int dnxcu_model_create_from_dnx(const void *bytes, size_t n, int device, dnxcu_model **out);
 
 /* Row band of a taller image: band rows [row0, row0+rows) of image height
  * image_h; (0, h, h) = whole image.  All three must be multiples of 16 when
@@ -468,6 +501,8 @@ DNXCU_API int dnxcu_db_size(const dnxcu_db *db);
  * without touching one. */
 DNXCU_API int dnxcu_db_populate(dnxcu_db *db, const dnxcu_model_desc *desc, int height, int width,
                                 int device);
+/* The same for a model that exists already (imported from ONNX, say). */
+DNXCU_API int dnxcu_db_populate_model(dnxcu_db *db, const dnxcu_model *m, int height, int width, int device);
 /* Samples un-converged entries until n >= min_samples and
  * sem / mean <= max_relative_error, coldest first then largest relative error
  * (db.cpp:71-175, 630-649); writes back atomically when done. */

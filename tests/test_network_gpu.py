@@ -251,6 +251,88 @@ def test_selection_prefers_the_unfused_schedule_when_the_database_says_so(tmp_pa
     db.close()
 
 
+@pytest.mark.parametrize("which,shape,other", [("tiny", (128, 128), (64, 160)), ("oidn", (64, 96), (32, 48)),
+                                               ("oidn", (40, 52), (64, 96))])
+def test_dnx_round_trip_runs_bit_identical(which, shape, other):
+    """model -> dnx file -> model: the file's dispatches give the same bits as the node list path, at the extent
+    the instance was made for and (the file's extents are symbolic) at another one."""
+    net = nets.oidn_unet() if which == "oidn" else nets.tiny_unet(bias=True)
+    mk = (lambda seed, hw: nets.oidn_input(seed, *hw)) if which == "oidn" else (lambda seed, hw: nets.tiny_input(seed, *hw))
+    model = lib.Model(net)
+    inst = lib.Instance(model, *shape)
+    x = mk(77, shape)
+    y = inst.infer(x)
+    blob = inst.write_dnx()
+    assert blob[4:8] == b"dnxx" and len(blob) > 1000
+    m2 = lib.Model.from_dnx(blob)
+    i2 = lib.Instance(m2, *shape)
+    assert i2.dispatch_count() == inst.dispatch_count()
+    assert [a.variant for a in i2.dispatch_info()] == [a.variant for a in inst.dispatch_info()]
+    y2 = i2.infer(x)
+    assert (y2.view(np.uint16) == y.view(np.uint16)).all()
+    # the same file at another extent against the node list path at that extent
+    x3 = mk(78, other)
+    i3a, i3b = lib.Instance(model, *other), lib.Instance(m2, *other)
+    assert (i3a.infer(x3).view(np.uint16) == i3b.infer(x3).view(np.uint16)).all()
+    # the extent independent file written from the model alone
+    m4 = lib.Model.from_dnx(model.write_dnx())
+    i4 = lib.Instance(m4, *shape)
+    ref = oracle.run_network_aligned(net, x, 16 if which == "oidn" else 2, oracle.ACC_F32)
+    assert_close(i4.infer(x), ref, "dnx written from the model")
+    for o in (inst, i2, i3a, i3b, i4, m2, m4, model):
+        o.close()
+
+
+def test_onnx_import_runs_like_the_node_list():
+    """ONNX bytes -> model -> instance: the same bits as the same network handed over as a node list."""
+    import sys
+    sys.path.insert(0, HERE)
+    import onnx_writer
+    net = nets.oidn_unet_reference()
+    x = nets.oidn_input(55, 48, 80)
+    a = lib.Model(net)
+    b = lib.Model.from_onnx(onnx_writer.from_net(net))
+    ia, ib = lib.Instance(a, 48, 80), lib.Instance(b, 48, 80)
+    assert (ia.infer(x).view(np.uint16) == ib.infer(x).view(np.uint16)).all()
+    with pytest.raises(lib.DnxcuError) as err:
+        lib.Model.from_onnx(b"\x08\x08")
+    assert "ONNX import" in str(err.value)
+    for o in (ia, ib, a, b):
+        o.close()
+
+
+def test_cli_populate_bench_compile_infer(tmp_path):
+    """The reference's three stage flow through the command line: populate a database for an assumed extent, bench
+    it, compile the ONNX file to a dnx file with it, run a frame (an .npy file in, an .npy file out)."""
+    import subprocess
+    import sys
+    sys.path.insert(0, HERE)
+    import onnx_writer
+    cli = os.path.join(os.path.dirname(lib.LIB_PATH), "dnxcu-cli")
+    net = nets.tiny_unet(bias=True)
+    onnx, db, dnx = tmp_path / "net.onnx", tmp_path / "gpu.db", tmp_path / "net.dnx"
+    onnx.write_bytes(onnx_writer.from_net(net))
+
+    def run(*args):
+        p = subprocess.run([cli, *map(str, args)], capture_output=True, text=True, timeout=600)
+        assert p.returncode == 0, (args, p.stdout, p.stderr)
+        return p.stdout
+
+    run("populate", db, onnx, "--assume", "H=64", "W=96")
+    run("bench", db, "--samples=3", "--relative-error=0.5", "--rounds=1")
+    out = run("compile", onnx, "-o", dnx, "--db", db, "--assume", "H=64", "W=96")
+    assert "dispatches" in out and dnx.exists()
+    x = nets.tiny_input(5, 64, 96)
+    np.save(tmp_path / "x.npy", x)
+    run("infer", dnx, "--input", tmp_path / "x.npy", "--output", tmp_path / "y.npy")
+    y = np.load(tmp_path / "y.npy")
+    assert y.dtype == np.float16 and y.shape == (64, 96, 3)
+    ref = oracle.run_network(net, x, oracle.ACC_F32)[net.output_tensor]
+    assert_close(y, ref, "frame through the command line")
+    table = run("bench", dnx, "--spec", "H=64", "W=96", "--samples=3")
+    assert "frames/s" in table and "direct-conv" in table
+
+
 def test_infer_async_round_robin_matches_infer():
     import torch
     net = nets.tiny_unet()
