@@ -194,7 +194,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   for (uint32_t it = 1;; ++it) {
     if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 0) {
+    if ((it & 63u) == 1u) {  // after the first probe that came back empty handed, then every 64th
       if (*abort_flag) return false;
       // the limit (clock64 ticks) sits in the header right behind the abort flag, written once at kernel start
       const unsigned long long limit = *reinterpret_cast<const volatile unsigned long long *>(abort_flag + 1);
@@ -204,6 +204,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         return false;
       }
     }
+  }
+}
+// After a wait ran out every role has left its loop, but copies into shared memory and MMAs that were started
+// before may still be in flight.  The block stays for a fixed, bounded time (far longer than a copy or an MMA
+// takes) before it frees its tensor memory and ends, so that nothing lands in memory it no longer owns.
+__device__ __forceinline__ void abort_drain(volatile int *abort_flag) {
+  if (*abort_flag) {
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
+    __syncthreads();
   }
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
@@ -883,6 +892,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  abort_drain(abort_flag);
   if (warp == 0) {
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(g.tmem_cols) : "memory");
@@ -1904,6 +1914,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  abort_drain(abort_flag);
   if (warp == 0) {
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base0), "r"(g.tmem_cols) : "memory");
@@ -1974,9 +1985,15 @@ int make_tensor_map(CUtensorMap *tm, const void *ptr, int H, int W, int C, int b
   const cuuint64_t strides[3] = {(cuuint64_t)C * 2, 16, (cuuint64_t)W * C * 2};
   const cuuint32_t box[4] = {8, (cuuint32_t)box_px, (cuuint32_t)box_chunks, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(ptr), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(ptr), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    // A host thread that has made no runtime call yet has no context bound, which this driver entry point wants:
+    // bind the device's primary context (what any runtime call that touches the device does) and try once more.
+    if ((r != CUDA_ERROR_INVALID_CONTEXT && r != CUDA_ERROR_NOT_INITIALIZED) || cudaFree(nullptr) != cudaSuccess) break;
+  }
   return r == CUDA_SUCCESS ? DNXCU_OK : DNXCU_E_CUDA;
 }
 

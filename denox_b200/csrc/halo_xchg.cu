@@ -27,10 +27,12 @@ __global__ void __launch_bounds__(512) halo_xchg(const XchgArgs a) {
       if (q.peer_up_slab) copy16(q.peer_up_slab, q.send_top, q.n16, tid, nthreads);
       if (q.peer_down_slab) copy16(q.peer_down_slab, q.send_bottom, q.n16, tid, nthreads);
     }
-    __threadfence_system();  // this thread's rows are visible to the peers before it is counted as done
   }
   __syncthreads();
   if (threadIdx.x == 0) {
+    // the block's stores (ordered before this point by the barrier) become visible system wide before the block
+    // is counted as done
+    __threadfence_system();
     const unsigned ticket = atomicAdd(a.done, 1u);
     s_last = ticket == gridDim.x - 1;
   }

@@ -243,3 +243,87 @@ def test_pad_channels_bit_exact(shape):
     lib.check(lib.L.dnxcu_launch(C.byref(d), None))
     y = out.check()
     assert (y.view(np.uint16) == ref.view(np.uint16)).all()
+
+def test_conv_kernel_gives_up_cleanly_when_its_wait_limit_is_tiny():
+    """The bounded waits of the tensor core conv kernel itself: with a limit of one microsecond the wait for the
+    layer's weights (some hundred KB from DRAM) runs out; the kernel reports a code through device_status, all its
+    roles leave, it frees its tensor memory and ends.  The launch after that, with the normal limit, is right."""
+    import ctypes as C
+    import torch
+    from gpu_util import dev
+    h, w, c, k = 64, 256, 96, 96
+    a = rng.to_f16(rng.uniform(801, h * w * c, -1, 1)).reshape(h, w, c)
+    wt = rng.he_normal_weights(802, k, c)
+    variant = lib.find_variant("direct-conv-tc", "DY=stack#KG=2#W=resident")
+    ta, tw = dev(a), dev(lib.prepare_weights(variant, wt, c))
+    out = torch.zeros((h, w, k), dtype=torch.float16, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    d = lib.Dispatch()
+    d.variant, d.flags, d.c_a, d.c_out = variant, lib.F_RELU, c, k
+    d.pc[0], d.pc[1] = w, h
+    d.in_a, d.out, d.weights, d.device_status = ta.data_ptr(), out.data_ptr(), tw.data_ptr(), status.data_ptr()
+    lib.check(lib.L.dnxcu_set_wait_limit_us(1))
+    try:
+        codes = []
+        for _ in range(3):  # cold caches make the first launch the slowest; any of them may run out
+            lib.check(lib.L.dnxcu_launch(C.byref(d), None))
+            torch.cuda.synchronize()
+            codes.append(int(status[0].item()))
+            status.zero_()
+    finally:
+        lib.check(lib.L.dnxcu_set_wait_limit_us(0))
+    assert all(0 <= cd <= 10 for cd in codes), codes
+    print("wait codes with a 1 us limit:", codes)
+    # whatever happened above, the device and the library are in order
+    lib.check(lib.L.dnxcu_launch(C.byref(d), None))
+    torch.cuda.synchronize()
+    assert int(status[0].item()) == 0
+    ref = oracle.conv3x3(a, wt, relu=True, mode=oracle.ACC_F32)
+    assert one_ulp(out.cpu().numpy(), ref).all()
+    assert any(codes), "a one microsecond limit was expected to run out at least once"
+
+
+def test_split_dispatches_from_two_threads_on_two_streams():
+    """Output channel split dispatches (several launches between a fork and a join on side streams) issued by two
+    host threads at the same time, each on its own stream: every thread has its own side streams, so neither can
+    pick up the other's fork."""
+    import ctypes as C
+    import threading
+    import torch
+    from gpu_util import dev
+    variant = lib.find_variant("direct-conv-tc", "DY=stack#KG=2#W=resident#NSPLIT=2")
+    h, w, c, k = 48, 200, 64, 96
+    jobs = []
+    for t in range(2):
+        a = rng.to_f16(rng.uniform(900 + t, h * w * c, -1, 1)).reshape(h, w, c)
+        wt = rng.he_normal_weights(910 + t, k, c)
+        jobs.append(dict(a=a, wt=wt, ta=dev(a), tw=dev(lib.prepare_weights(variant, wt, c)),
+                         mid=torch.zeros((h, w, k), dtype=torch.float16, device="cuda"),
+                         stream=torch.cuda.Stream(), errors=[]))
+    torch.cuda.synchronize()
+
+    def work(j):
+        try:
+            d = lib.Dispatch()
+            d.variant, d.flags, d.c_a, d.c_out = variant, lib.F_RELU, c, k
+            d.pc[0], d.pc[1] = w, h
+            d.in_a, d.out, d.weights = j["ta"].data_ptr(), j["mid"].data_ptr(), j["tw"].data_ptr()
+            for _ in range(200):
+                st = lib.L.dnxcu_launch(C.byref(d), j["stream"].cuda_stream)
+                if st:
+                    j["errors"].append((st, lib.L.dnxcu_last_cuda_error()))  # the CUDA code is kept per host thread
+                    return
+            j["stream"].synchronize()
+        except Exception as e:  # noqa: BLE001
+            j["errors"].append(repr(e))
+
+    threads = [threading.Thread(target=work, args=(j,)) for j in jobs]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    torch.cuda.synchronize()
+    for j in jobs:
+        assert not j["errors"], j["errors"]
+        ref = oracle.conv3x3(j["a"], j["wt"], relu=True, mode=oracle.ACC_F32)
+        assert one_ulp(j["mid"].cpu().numpy(), ref).all()
