@@ -118,6 +118,11 @@ static const Variant kVariants[] = {
     {{27, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=2#W=resident#NSPLIT=4", CONV_ALL, 1, 1, 16, 256, 0}, VK_CONV_TC, 0, 2, 0, 4},
     {{28, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=1#W=resident#ER=2", CONV_ALL, 1, 8, 1, 128, 0}, VK_CONV_TC, 0, 1, 0, 0, 2},
     {{29, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=1#W=resident#PIPES=1#ER=2", CONV_ALL, 1, 8, 1, 128, 0}, VK_CONV_TC, 0, 1, 2, 0, 2},
+    {{30, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=1#W=resident#CSPLIT=2", CONV_ALL, 1, 1, 8, 256, 0}, VK_CONV_TC, 0, 1, 0, 0, 0, 2},
+    {{31, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=1#W=resident#CSPLIT=3", CONV_ALL, 1, 1, 8, 256, 0}, VK_CONV_TC, 0, 1, 0, 0, 0, 3},
+    {{32, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=1#W=resident#CSPLIT=4", CONV_ALL, 1, 1, 8, 256, 0}, VK_CONV_TC, 0, 1, 0, 0, 0, 4},
+    {{33, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=2#W=resident#CSPLIT=2", CONV_ALL, 1, 1, 8, 256, 0}, VK_CONV_TC, 0, 2, 0, 0, 0, 2},
+    {{34, DNXCU_OP_CONV3X3, "direct-conv-tc", "DY=stack#KG=2#W=resident#CSPLIT=4", CONV_ALL, 1, 1, 8, 256, 0}, VK_CONV_TC, 0, 2, 0, 0, 0, 4},
 };
 static const int kVariantCount = (int)(sizeof(kVariants) / sizeof(kVariants[0]));
 
@@ -397,3 +402,14 @@ float dnxcu_f16_to_float(uint16_t h) {
 }
 
 }  // extern "C"
+
+#ifdef DNXCU_DEBUG_AIDS
+// Development builds only (not part of the public header): hands the conv kernels a device buffer for their time
+// line stamps, used while the environment variable DNXCU_TC_TRACE is 1; nullptr switches tracing off again.
+namespace dnxcu {
+int conv_tc_debug_trace_buffer(void *device_buffer, size_t bytes);
+}
+extern "C" DNXCU_API int dnxcu_debug_trace_buffer(void *device_buffer, size_t bytes) {
+  return dnxcu::conv_tc_debug_trace_buffer(device_buffer, bytes);
+}
+#endif

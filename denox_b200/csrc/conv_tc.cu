@@ -116,6 +116,8 @@ struct TcArgs {
   uint32_t stage_warp_bytes;  // staging bytes per epilogue warp
   uint32_t tmem_cols;
   int parts;       // launches of this dispatch that run side by side (output channel split): each plans for 1/parts of the SMs
+  int cparts;      // stacked form: output channel parts inside ONE launch (blockIdx.y): part p computes channels
+                   // [p * N, p * N + N) from its own weight blob; K is then the dispatch's whole channel count
   unsigned long long wait_limit;  // clock64 ticks after which a barrier wait gives up (see mbar_wait)
 #ifdef DNXCU_DEBUG_AIDS
   int desc_swap;     // exchange the two descriptor strides
@@ -326,10 +328,14 @@ __device__ __forceinline__ float activate_f(float v, int leaky, uint32_t alpha_h
 // Debug time line: role `role` of CTA 0 stores clock64() at event `ev` of its n-th iteration.
 #ifdef DNXCU_DEBUG_AIDS
 constexpr int TRACE_ITERS = 64, TRACE_EVENTS = 6;
+constexpr int TRACE_CTAS = 1024;
+// behind the role stamps: CTA 0's kernel entry, set-up done, roles done (clock64), entry and end (globaltimer); then
+// per CTA (the first TRACE_CTAS) its cycles from entry to roles done and its entry time (globaltimer)
+constexpr int TRACE_EXTRA = 8 + 2 * TRACE_CTAS;
 #endif
 __device__ __forceinline__ void trace(const TcArgs &g, int role, int n, int ev) {
 #ifdef DNXCU_DEBUG_AIDS
-  if (g.trace && blockIdx.x == 0 && n < TRACE_ITERS) g.trace[(role * TRACE_ITERS + n) * TRACE_EVENTS + ev] = clock64();
+  if (g.trace && blockIdx.x == 0 && blockIdx.y == 0 && n < TRACE_ITERS) g.trace[(role * TRACE_ITERS + n) * TRACE_EVENTS + ev] = clock64();
 #else
   (void)g; (void)role; (void)n; (void)ev;
 #endif
@@ -905,14 +911,24 @@ __global__ void __launch_bounds__(THREADS, 1) conv3x3_tc(const __grid_constant__
 // ReLU and the 2x2 max then work on packed pairs (max commutes with the rounding).
 constexpr int EPI_BIAS = 1, EPI_RELU = 2, EPI_POOL = 4, EPI_FULL = 8;
 
+// What differs between the output channel parts of one launch (TcArgs::cparts): the part's first channel is
+// folded into the pointers, K is the number of valid channels of the part.
+struct OutPart {
+  const __half *bias;
+  __half *out;
+  __half *out_pool;
+  int K;
+};
+
 template <int NC, int EPI>
-__device__ __forceinline__ void round_row(const TcArgs &g, const uint32_t (&v)[NC], int c0, uint32_t (&h)[NC / 2]) {
+__device__ __forceinline__ void round_row(const TcArgs &g, const OutPart &o, const uint32_t (&v)[NC], int c0,
+                                          uint32_t (&h)[NC / 2]) {
 #pragma unroll
   for (int j = 0; j < NC; j += 2) {
     float lo = __uint_as_float(v[j]), hi = __uint_as_float(v[j + 1]);
     if (EPI & EPI_BIAS) {
-      lo += (c0 + j < g.K) ? __half2float(__ldg(g.bias + c0 + j)) : 0.0f;
-      hi += (c0 + j + 1 < g.K) ? __half2float(__ldg(g.bias + c0 + j + 1)) : 0.0f;
+      lo += (c0 + j < o.K) ? __half2float(__ldg(o.bias + c0 + j)) : 0.0f;
+      hi += (c0 + j + 1 < o.K) ? __half2float(__ldg(o.bias + c0 + j + 1)) : 0.0f;
     }
     uint32_t p = pack_h2(lo, hi);
     if (EPI & EPI_RELU) p = activate_h2(p, g.leaky, g.alpha_h2);
@@ -922,16 +938,16 @@ __device__ __forceinline__ void round_row(const TcArgs &g, const uint32_t (&v)[N
 
 // Stores NC channels [c0, c0 + NC) of one pixel from packed pairs.
 template <int NC>
-__device__ __forceinline__ void store_row(const TcArgs &g, __half *o, const uint32_t (&h)[NC / 2], int c0) {
-  if ((g.K & 7) == 0) {
+__device__ __forceinline__ void store_row(int K, __half *o, const uint32_t (&h)[NC / 2], int c0) {
+  if ((K & 7) == 0) {
 #pragma unroll
     for (int j8 = 0; j8 < NC; j8 += 8)
-      if (c0 + j8 + 8 <= g.K)
+      if (c0 + j8 + 8 <= K)
         *reinterpret_cast<uint4 *>(o + j8) = make_uint4(h[j8 / 2], h[j8 / 2 + 1], h[j8 / 2 + 2], h[j8 / 2 + 3]);
   } else {
 #pragma unroll
     for (int j = 0; j < NC; ++j)
-      if (c0 + j < g.K) {
+      if (c0 + j < K) {
         const uint32_t p = h[j / 2];
         reinterpret_cast<unsigned short *>(o)[j] = (unsigned short)((j & 1) ? (p >> 16) : (p & 0xffffu));
       }
@@ -939,8 +955,8 @@ __device__ __forceinline__ void store_row(const TcArgs &g, __half *o, const uint
 }
 
 template <int NC, int RSTEP, int EPI>
-__device__ __forceinline__ void epi_fast(const TcArgs &g, uint32_t t0, uint32_t t1, int c0, int x, int y, bool xin,
-                                         int lane) {
+__device__ __forceinline__ void epi_fast(const TcArgs &g, const OutPart &o, uint32_t t0, uint32_t t1, int c0, int x,
+                                         int y, bool xin, int lane) {
   uint32_t v0[NC], v1[RSTEP == 2 ? NC : 2];
   if constexpr (NC == 32) {
     tc_ld32(t0 + (uint32_t)c0, v0);
@@ -953,15 +969,15 @@ __device__ __forceinline__ void epi_fast(const TcArgs &g, uint32_t t0, uint32_t 
   if (DBG_SKIP(g) & 16) return;
   if (DBG_SKIP(g) & 4) xin = false;
   uint32_t h0[NC / 2], h1[RSTEP == 2 ? NC / 2 : 1];
-  round_row<NC, EPI>(g, v0, c0, h0);
-  if constexpr (RSTEP == 2) round_row<NC, EPI>(g, v1, c0, h1);
+  round_row<NC, EPI>(g, o, v0, c0, h0);
+  if constexpr (RSTEP == 2) round_row<NC, EPI>(g, o, v1, c0, h1);
   const bool row1 = RSTEP == 2 && (y + 1 < g.H);
   if (EPI & EPI_FULL) {
     if (xin) {
-      __half *o0 = g.out + ((long long)y * g.W + x) * g.os + c0;
-      store_row<NC>(g, o0, h0, c0);
+      __half *o0 = o.out + ((long long)y * g.W + x) * g.os + c0;
+      store_row<NC>(o.K, o0, h0, c0);
       if constexpr (RSTEP == 2) {
-        if (row1) store_row<NC>(g, o0 + (long long)g.W * g.os, h1, c0);
+        if (row1) store_row<NC>(o.K, o0 + (long long)g.W * g.os, h1, c0);
       }
     }
   }
@@ -973,7 +989,7 @@ __device__ __forceinline__ void epi_fast(const TcArgs &g, uint32_t t0, uint32_t 
       pm[j] = hmax2_u32(vm, __shfl_xor_sync(0xffffffffu, vm, 1));
     }
     if (xin && !(lane & 1) && row1)
-      store_row<NC>(g, g.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (x >> 1)) * g.os + c0, pm, c0);
+      store_row<NC>(o.K, o.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (x >> 1)) * g.os + c0, pm, c0);
   }
 }
 
@@ -1087,13 +1103,13 @@ __device__ __forceinline__ bool st_issue_nk(int nk, uint32_t hi, uint32_t row_lo
 
 // TMEM -> registers -> (+bias) -> binary16 pairs -> (ReLU) -> this lane's pixel row of the staging tile
 template <int NC, int EPI>
-__device__ __forceinline__ void stage_cols(const TcArgs &g, uint32_t taddr, int c0, uint32_t dst) {
+__device__ __forceinline__ void stage_cols(const TcArgs &g, const OutPart &o, uint32_t taddr, int c0, uint32_t dst) {
   uint32_t v[NC];
   if constexpr (NC == 32) tc_ld32(taddr + (uint32_t)c0, v);
   else tc_ld16(taddr + (uint32_t)c0, v);
   tc_wait_ld();
   uint32_t h[NC / 2];
-  round_row<NC, EPI>(g, v, c0, h);
+  round_row<NC, EPI>(g, o, v, c0, h);
 #pragma unroll
   for (int j8 = 0; j8 < NC; j8 += 8)
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (uint32_t)((c0 + j8) * 2)), "r"(h[j8 / 2]),
@@ -1164,6 +1180,23 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   volatile uint32_t *tmem_ptr = reinterpret_cast<volatile uint32_t *>(smem + ST_OFF_TMEM_PTR);
   auto bar = [&](int i) { return sbase + (uint32_t)i * 8u; };
 
+#ifdef DNXCU_DEBUG_AIDS
+  if (g.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    g.trace[3 * TRACE_ITERS * TRACE_EVENTS + 0] = clock64();
+    g.trace[3 * TRACE_ITERS * TRACE_EVENTS + 3] = (long long)gt;
+  }
+#endif
+#ifdef DNXCU_DEBUG_AIDS
+  const long long dbg_entry = clock64();
+  const int dbg_cta = (int)(blockIdx.x + gridDim.x * blockIdx.y);
+  if (g.trace && threadIdx.x == 0 && dbg_cta < TRACE_CTAS) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    g.trace[3 * TRACE_ITERS * TRACE_EVENTS + 8 + TRACE_CTAS + dbg_cta] = (long long)gt;
+  }
+#endif
   const int nch = g.a.nch + g.b.nch;
   const int N = g.N, NB = g.NB, P = g.P;
   const uint32_t wdx_bytes = (uint32_t)nch * 3u * N * 16u;  // one horizontal tap: all chunks x 3N rows
@@ -1174,6 +1207,15 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   const int S = g.S;  // slots per pipeline
   const int unit_stride = (int)gridDim.x * P;
   const int nprod_warps = P == 2 ? 2 : 4;  // producer warps per pipeline
+  // Output channel parts of one launch: blockIdx.y picks the part (always 0 when the launch has one part).
+  // Pipeline p of CTA b starts at unit b + p * gridDim.x, so a launch with fewer units than pipelines spreads
+  // over the SMs before any SM runs two units side by side.
+  const int kofs = (int)blockIdx.y * N;
+  OutPart part;
+  part.K = min(N, g.K - kofs);
+  part.bias = g.bias ? g.bias + kofs : nullptr;
+  part.out = g.out ? g.out + kofs : nullptr;
+  part.out_pool = g.out_pool ? g.out_pool + kofs : nullptr;
 
   if (warp == 2) {
     // barrier set-up by a whole warp (one barrier per lane and round) while warp 0 allocates tensor memory
@@ -1198,8 +1240,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     // ---------------- weights (resident), copies of at most 32 KB: started before anything else ----------------
     mbar_init(bar(ST_BAR_WRES), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(g.w);
     const uint32_t total = wdx_bytes * 3u;
+    const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(g.w) + (size_t)blockIdx.y * total;
     mbar_expect_tx(bar(ST_BAR_WRES), total);
     for (uint32_t off = 0; off < total; off += 32768u)
       bulk_g2s(w_addr + off, wsrc + off, min(32768u, total - off), bar(ST_BAR_WRES));
@@ -1214,6 +1256,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base0 = *tmem_ptr;
+#ifdef DNXCU_DEBUG_AIDS
+  if (g.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g.trace[3 * TRACE_ITERS * TRACE_EVENTS + 1] = clock64();
+#endif
 
   // ---- expand mode: cursor over the (unit, input row, K group) entries of one pipeline, and the TMA issue of one entry
   struct XpCursor {
@@ -1223,7 +1268,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     bool valid;
   };
   auto xp_start = [&](XpCursor &c, int pipe) {
-    c.u = (int)blockIdx.x * P + pipe;
+    c.u = (int)blockIdx.x + pipe * (int)gridDim.x;
     c.jj = c.gi = c.slot = 0;
     c.ephase = 1;
     c.rphase = 0;
@@ -1400,7 +1445,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         }
       }
     };
-    if (lane == 0 && ok && (int)blockIdx.x * P + pipe < g.nunits) {
+    if (lane == 0 && ok && (int)blockIdx.x + pipe * (int)gridDim.x < g.nunits) {
       bool same = !DBG_LOOP_ISSUE(g) && !DBG_SWITCH_ISSUE(g);
       for (int gi = 1; gi < g.G; ++gi) same = same && g.gch[gi] == g.gch[0];
       const int nkfix = same ? (g.gch[0] >> 1) : 0;
@@ -1439,7 +1484,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const bool tr = DBG_TRACE_ON(g) && blockIdx.x == 0 && threadIdx.x == 64;
     const int pitch = g.stage_pitch;  // 0: no staging tile, direct stores
-    const int nck = g.K >> 3;
+    const int nck = part.K >> 3;
     const int os8 = g.os >> 3;  // output pixel stride in 16 byte units (= nck unless the output channels are split)
     const uint32_t stage_base = slots_addr0 + (uint32_t)(P * S) * (slot_bytes + g.src_bytes) + (uint32_t)(warp - 2) * g.stage_warp_bytes;
     bool ok = true;
@@ -1453,7 +1498,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     __syncwarp();
     if (lane == 0)
       for (int b = 0; b < NB; ++b) mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b));
-    for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
+    for (int u = (int)blockIdx.x + pipe * (int)gridDim.x; ok && u < g.nunits; u += unit_stride) {
       const StUnit t = st_unit_of(g, u);
       const int x = t.x0 + m;
       const bool xin = x < g.W;
@@ -1489,8 +1534,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
               const uint32_t tile = (pool2 && r) ? tile1 : tile0;
               int c0 = 0;
 #pragma unroll 1
-              for (; c0 + 32 <= N; c0 += 32) stage_cols<32, EPI>(g, tr_addr, c0, tile + mine);
-              if (c0 < N) stage_cols<16, EPI>(g, tr_addr, c0, tile + mine);
+              for (; c0 + 32 <= N; c0 += 32) stage_cols<32, EPI>(g, part, tr_addr, c0, tile + mine);
+              if (c0 < N) stage_cols<16, EPI>(g, part, tr_addr, c0, tile + mine);
               if (r == nrows - 1) {
                 // last TMEM read of the item done: give the blocks back, zeroed (every MMA accumulates)
                 tc_zero_cols(t0, N);
@@ -1506,18 +1551,18 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
               }
               if (!pool2) {
                 if ((EPI & EPI_FULL) && !(DBG_SKIP(g) & 4))
-                  copy_out(tile, pitch, nck, os8, npx, g.out + ((long long)(y + r) * g.W + xw) * g.os, lane);
+                  copy_out(tile, pitch, nck, os8, npx, part.out + ((long long)(y + r) * g.W + xw) * g.os, lane);
                 __syncwarp();
               }
             }
             if (pool2) {
               if (!(DBG_SKIP(g) & 4)) {
                 if (EPI & EPI_FULL) {
-                  copy_out(tile0, pitch, nck, os8, npx, g.out + ((long long)y * g.W + xw) * g.os, lane);
-                  copy_out(tile1, pitch, nck, os8, npx, g.out + ((long long)(y + 1) * g.W + xw) * g.os, lane);
+                  copy_out(tile0, pitch, nck, os8, npx, part.out + ((long long)y * g.W + xw) * g.os, lane);
+                  copy_out(tile1, pitch, nck, os8, npx, part.out + ((long long)(y + 1) * g.W + xw) * g.os, lane);
                 }
                 copy_out_pooled(tile0, tile1, pitch, nck, os8, npx,
-                                g.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (xw >> 1)) * g.os, lane);
+                                part.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (xw >> 1)) * g.os, lane);
               }
               __syncwarp();
             }
@@ -1537,12 +1582,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         int c0 = (DBG_SKIP(g) & 8) ? N : 0;
         if (nrows == 2) {
 #pragma unroll 1
-          for (; c0 + 32 <= N; c0 += 32) epi_fast<32, 2, EPI>(g, t0, t1, c0, x, y, xin, lane);
-          if (c0 < N) epi_fast<16, 2, EPI>(g, t0, t1, c0, x, y, xin, lane);
+          for (; c0 + 32 <= N; c0 += 32) epi_fast<32, 2, EPI>(g, part, t0, t1, c0, x, y, xin, lane);
+          if (c0 < N) epi_fast<16, 2, EPI>(g, part, t0, t1, c0, x, y, xin, lane);
         } else {
 #pragma unroll 1
-          for (; c0 + 32 <= N; c0 += 32) epi_fast<32, 1, EPI>(g, t0, t1, c0, x, y, xin, lane);
-          if (c0 < N) epi_fast<16, 1, EPI>(g, t0, t1, c0, x, y, xin, lane);
+          for (; c0 + 32 <= N; c0 += 32) epi_fast<32, 1, EPI>(g, part, t0, t1, c0, x, y, xin, lane);
+          if (c0 < N) epi_fast<16, 1, EPI>(g, part, t0, t1, c0, x, y, xin, lane);
         }
         if (tr) trace(g, 1, item >> 1, 2);
         tc_zero_cols(t0, N);
@@ -1571,7 +1616,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         uint32_t phase = 1;  // parity to wait for on the empty barrier: first round passes
         const int nca = g.a.nch;
         const bool tr = DBG_TRACE_ON(g) && blockIdx.x == 0 && pipe == 0;
-        for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
+        for (int u = (int)blockIdx.x + pipe * (int)gridDim.x; ok && u < g.nunits; u += unit_stride) {
           const StUnit t = st_unit_of(g, u);
           for (int jj = 0; ok && jj < t.rows_out + 2; jj += g.ER) {
             for (int gi = 0; ok && gi < g.G; ++gi) {
@@ -1764,7 +1809,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
       // thread 0 also issues the TMA part; each thread keeps up to D rows of cp.async in flight
       int pos = 0, signalled = 0;
       const int D = g.D;
-      for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
+      for (int u = (int)blockIdx.x + pipe * (int)gridDim.x; ok && u < g.nunits; u += unit_stride) {
         const StUnit t = st_unit_of(g, u);
         for (int jj = 0; ok && jj < t.rows_out + 2; ++jj) {
           const int iy = t.y0 - 1 + jj;
@@ -1824,7 +1869,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     int blkC = 0;
     uint32_t cphase = 0;  // parity to wait for on tempty[blkC]: the epilogue's first zeroing completes phase 0
     bool ok = true;
-    for (int u = (int)blockIdx.x * P + pipe; ok && u < g.nunits; u += unit_stride) {
+    for (int u = (int)blockIdx.x + pipe * (int)gridDim.x; ok && u < g.nunits; u += unit_stride) {
       const StUnit t = st_unit_of(g, u);
       const int rows_in = t.rows_out + 2;
       const bool last_unit = u + unit_stride >= g.nunits;
@@ -1914,6 +1959,18 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+#ifdef DNXCU_DEBUG_AIDS
+  if (g.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    g.trace[3 * TRACE_ITERS * TRACE_EVENTS + 2] = clock64();
+    g.trace[3 * TRACE_ITERS * TRACE_EVENTS + 4] = (long long)gt;
+  }
+#endif
+#ifdef DNXCU_DEBUG_AIDS
+  if (g.trace && threadIdx.x == 0 && dbg_cta < TRACE_CTAS)
+    g.trace[3 * TRACE_ITERS * TRACE_EVENTS + 8 + dbg_cta] = clock64() - dbg_entry;
+#endif
   abort_drain(abort_flag);
   if (warp == 0) {
     __syncwarp();
@@ -1940,8 +1997,17 @@ struct Plan {
   TcArgs args;
   size_t smem;
   int grid;
+  int grid_y;  // output channel parts inside the launch (stacked form), else 1
   int R;
 };
+
+// Output channel parts inside one launch ("CSPLIT=n", v.p5): channels per part, a multiple of 16, the same for
+// every part (the last part may hold fewer valid channels; its weights are zero padded).
+int csplit_of(const Variant &v) { return (v.p0 == 0 && v.p5 > 1) ? v.p5 : 1; }
+int csplit_n(const Variant &v, int K) {
+  const int want = csplit_of(v);
+  return ((K + want - 1) / want + 15) / 16 * 16;
+}
 
 constexpr size_t SMEM_LIMIT = 232448;  // 227 KB opt-in per block on sm_100
 
@@ -2016,6 +2082,15 @@ int encode_halo_maps(TcArgs &g, int W) {
 int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode) {
   TcArgs &g = pl.args;
   const int W = g.W, H = g.H;
+  g.cparts = 1;
+  if (csplit_of(v) > 1) {
+    // every part stages whole 16 byte pieces of its channels and starts on a 16 byte boundary of the pixel
+    if (g.K % 8) return DNXCU_E_UNSUPPORTED;
+    g.N = csplit_n(v, g.K);
+    g.cparts = (g.K + g.N - 1) / g.N;
+    if (g.cparts < 2) return DNXCU_E_UNSUPPORTED;  // nothing to split: the plain variant covers it
+    g.parts = g.cparts;
+  }
   if (g.N > 128) return DNXCU_E_UNSUPPORTED;
   g.Ns = g.N;
   g.wstream = 0;
@@ -2073,7 +2148,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
     (void)amax;
   }
   const bool stage_possible = g.K % 8 == 0 && !dbg_env("DNXCU_TC_NO_STAGE");
-  const size_t stage_pitch = (size_t)g.K * 2 + 16;
+  const size_t stage_pitch = (size_t)(g.cparts > 1 ? g.N : g.K) * 2 + 16;
   const size_t stage_per_warp = (g.pool ? 2 : 1) * 32 * stage_pitch;
   const size_t base_bytes = ST_HEADER_BYTES + wregion;
   const size_t plain_slot = (size_t)g.gmax * CHUNK_PITCH * ER;
@@ -2146,8 +2221,8 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   }
   g.RB = bestRB;
   g.nunits = g.nstrips * ((H + g.RB - 1) / g.RB);
-  const int ctas = (g.nunits + P - 1) / P;
-  pl.grid = ctas < sms ? ctas : sms;
+  pl.grid = g.nunits < sms ? g.nunits : sms;  // spread first: a second unit per SM only when every SM has one
+  pl.grid_y = g.cparts;
   pl.R = 0;
   memset(&g.tm_a, 0, sizeof(g.tm_a));
   memset(&g.tm_b, 0, sizeof(g.tm_b));
@@ -2191,6 +2266,7 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   if (((uintptr_t)d.in_a | (uintptr_t)d.in_b | (uintptr_t)d.out | (uintptr_t)d.out_pool | (uintptr_t)d.bias) & 1)
     return DNXCU_E_MISALIGNED;
 
+  pl.grid_y = 1;
   TcArgs &g = pl.args;
   g.a = {(const __half *)d.in_a, (const __half *)d.halo[0], (const __half *)d.halo[1], d.c_a, nch_of(d.c_a), up ? 1 : 0, 0, 2, 0};
   g.b = {(const __half *)d.in_b, (const __half *)d.halo[2], (const __half *)d.halo[3], d.c_b, nch_of(d.c_b), 0, 0, 2, 0};
@@ -2247,6 +2323,7 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   if (R == 0) return make_plan_stack(v, d, pl, encode);
   g.a.rg = g.b.rg = 0;  // the pass kernel loads ragged operands with its producer warps
   g.ER = 1;
+  g.cparts = 1;
   uint32_t cols = 2u * R * g.Ns;
   if (cols > 512) return DNXCU_E_UNSUPPORTED;
   uint32_t p2 = 32;
@@ -2348,7 +2425,7 @@ int launch_stack_epi(const Plan &pl, cudaStream_t s, bool attr_only = false) {
   static std::atomic<bool> done[64];
   int st = ensure_smem_attr(conv3x3_tc_stack<EPI>, done);
   if (st || attr_only) return st;
-  conv3x3_tc_stack<EPI><<<pl.grid, ST_THREADS, pl.smem, s>>>(pl.args);
+  conv3x3_tc_stack<EPI><<<dim3((unsigned)pl.grid, (unsigned)pl.grid_y), ST_THREADS, pl.smem, s>>>(pl.args);
   DNXCU_CUDA(cudaGetLastError());
   return DNXCU_OK;
 }
@@ -2385,6 +2462,10 @@ int split_parts(const Variant &v, int K, int k0[8], int kp[8]) {
 size_t conv_tc_weight_bytes(const Variant &v, int k, int ca, int cb) {
   int k0[8], kp[8];
   const int n = split_parts(v, k, k0, kp);
+  if (csplit_of(v) > 1) {
+    const int np = csplit_n(v, k);
+    return (size_t)9 * (nch_of(ca) + nch_of(cb)) * np * 16 * ((k + np - 1) / np);
+  }
   size_t total = 0;
   for (int p = 0; p < n; ++p) total += (size_t)9 * (nch_of(ca) + nch_of(cb)) * pad16(kp[p]) * 16;
   return total;
@@ -2403,10 +2484,18 @@ void conv_tc_prepare(const Variant &v, const uint16_t *kcrs, int K, int ca, int 
   for (size_t i = 0; i < total; ++i) out[i] = 0;
   if (v.p0 == 0) {
     int k0[8], kp[8];
-    const int n = split_parts(v, K, k0, kp);
+    int n = split_parts(v, K, k0, kp);
+    const int cs_n = csplit_of(v) > 1 ? csplit_n(v, K) : 0;
+    if (cs_n) {  // parts of one launch: every part cs_n channels wide
+      n = 0;
+      for (int c = 0; c < K && n < 8; c += cs_n, ++n) {
+        k0[n] = c;
+        kp[n] = K - c < cs_n ? K - c : cs_n;
+      }
+    }
     size_t off = 0;
     for (int p = 0; p < n; ++p) {
-      const int N = pad16(kp[p]);
+      const int N = cs_n ? cs_n : pad16(kp[p]);
       for (int seg = 0; seg < 2; ++seg) {
         const int Cs = seg ? cb : ca, cbase = seg ? ca : 0, chbase = seg ? nch_of(ca) : 0;
         for (int r = 0; r < 3; ++r)
@@ -2469,7 +2558,10 @@ void conv_tc_grid(const Variant &v, const dnxcu_dispatch &d, uint32_t g[3]) {
   Plan pl;
   g[0] = g[1] = g[2] = 1;
   const dnxcu_dispatch dp = n == 1 ? d : part_dispatch(d, k0[0], kp[0], 0);
-  if (make_plan(v, dp, pl, false, n == 1 ? 0 : d.c_out, n) == DNXCU_OK) g[0] = (uint32_t)pl.grid;
+  if (make_plan(v, dp, pl, false, n == 1 ? 0 : d.c_out, n) == DNXCU_OK) {
+    g[0] = (uint32_t)pl.grid;
+    g[1] = (uint32_t)pl.grid_y;
+  }
   g[2] = (uint32_t)n;  // launches
 }
 
@@ -2608,7 +2700,7 @@ int conv_tc_init_device() {
 
 #ifdef DNXCU_DEBUG_AIDS
 int conv_tc_debug_trace_buffer(void *device_buffer, size_t bytes) {
-  const size_t need = (size_t)3 * TRACE_ITERS * TRACE_EVENTS * sizeof(long long);
+  const size_t need = ((size_t)3 * TRACE_ITERS * TRACE_EVENTS + TRACE_EXTRA) * sizeof(long long);
   if (device_buffer && bytes < need) return DNXCU_E_BAD_ARG;
   g_trace_buffer = (long long *)device_buffer;
   return DNXCU_OK;

@@ -36,6 +36,7 @@ struct Variant {
   // tuning parameters (meaning depends on kind)
   int p0, p1, p2, p3;
   int p4 = 0;
+  int p5 = 0;
 };
 
 const Variant *get_variant(int id);

@@ -488,8 +488,17 @@ DNXCU_API int dnxcu_instance_extent(const dnxcu_instance *inst, int *h, int *w, 
  * Benchmark database.
  * Stands in for denox::Db (database/src/denox/db/Db.hpp:15-76) and the
  * sampling loop of runtime::Db::bench (runtime/src/denox/runtime/db.cpp:665-868).
- * Key = (variant sha-256, push constants, channel counts, flags, grid); value
- * = sample count, mean and standard deviation of the latency in ms.
+ * Key = (variant sha-256, push constants {IN_W, IN_H}, channel counts, flags);
+ * value = every latency sample with its time stamp and benchmark environment,
+ * their mean and standard deviation.
+ * The file is a FlatBuffer of the reference's schema (db.fbs:1-139, identifier
+ * "dbdb"): BenchEnv records, one ShaderBinary per variant identity (src_sha256 =
+ * the identity, spirv = a "DNXC" descriptor instead of SPIR-V), one
+ * ComputeDispatch per key with the launch grid as workgroup counts, the key's
+ * numbers as push_constant bytes, Timing and ComputeDispatchInfo.  A file of
+ * the reference itself (SPIR-V binaries) is refused with DNXCU_E_IO: its
+ * timings are those of other kernels.  Entries of identities this build does
+ * not know are kept and written back as read.
  * ---------------------------------------------------------------------- */
 DNXCU_API int dnxcu_db_open(const char *path, dnxcu_db **out); /* missing file = empty db */
 DNXCU_API void dnxcu_db_close(dnxcu_db *db);
