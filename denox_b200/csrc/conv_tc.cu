@@ -1672,6 +1672,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
       // pipeline) starts the TMA copies; it runs ahead of the expansion as far as free slots allow, so the copy
       // latency overlaps the expansion of earlier rows.
       const bool self_issue = P == 2;
+      const bool meet = g.a.rg || g.b.rg;  // the producer threads of a pipeline meet at a named barrier per entry
       const int LA = S - 1 < 4 ? S - 1 : 4;
       XpCursor is, ex;
       xp_start(is, pipe);
@@ -1695,9 +1696,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           const uint32_t rb = bar(ST_BAR_RAW + bofs + ex.slot);
           if (tid == 32 && pipe == 0) trace(g, 2, xcount, 0);
           if (ok) ok = mbar_wait<32>(rb, ex.rphase, abort_flag, g.status, 8);
-          // The expansion below meets at a named barrier, so the producer threads of a pipeline must leave
-          // this loop together: they vote, and a wait that ran out in one of them takes all of them out.
-          {
+          // The re-lay of a ragged operand meets at a named barrier, so there the producer threads of a pipeline
+          // must leave this loop together: they vote, and a wait that ran out in one of them takes all of them
+          // out.  Without a ragged operand every warp works on chunk pairs of its own and only its lanes vote.
+          if (!meet) {
+            ok = __all_sync(0xffffffffu, ok);
+          } else {
             uint32_t all_ok;
             asm volatile(
                 "{\n\t"
@@ -1721,25 +1725,27 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
             cp_async_wait<0>();
           }
           if (a_eng && g.a.up && !(DBG_SKIP(g) & 1)) {
-            // In place, one pair of chunks at a time: the copy left the pair's two half resolution rows packed
-            // (2 x 72 pixels) at the start of the pair's 2 x 132 pixel area.  Every thread first loads the
-            // sources of its pixels, then all producer threads of the pipeline meet, then they store.
-            for (int c = a_lo; c < a_hi; c += 2) {
+            // In place, a pair of chunks per warp: the copy left the pair's two half resolution rows packed
+            // (2 x 72 pixels) at the start of the pair's 2 x 132 pixel area.  The lanes of a warp first load the
+            // sources of all pixels of the pair, meet, then store; no other warp touches that pair, so the warps
+            // of a pipeline expand different pairs side by side without meeting.
+            static_assert(SLOT_PX <= 5 * 32, "five pixels per lane cover a slot row");
+            for (int c = a_lo + 2 * (tid >> 5); c < a_hi; c += 2 * nprod_warps) {
               const uint32_t pair = slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH);
-              uint4 v[3][2];
+              uint4 v[5][2];
 #pragma unroll
-              for (int i = 0; i < 3; ++i) {
-                const int px = tid + i * nprod;
+              for (int i = 0; i < 5; ++i) {
+                const int px = lane + i * 32;
                 if (px < SLOT_PX) {
                   const uint32_t sp = pair + (uint32_t)(((px + 1) >> 1) * 16);
                   v[i][0] = lds16(sp);
                   v[i][1] = lds16(sp + (uint32_t)SRC_PITCH);
                 }
               }
-              asm volatile("bar.sync %0, %1;" ::"r"(1 + pipe), "r"(nprod) : "memory");
+              __syncwarp();
 #pragma unroll
-              for (int i = 0; i < 3; ++i) {
-                const int px = tid + i * nprod;
+              for (int i = 0; i < 5; ++i) {
+                const int px = lane + i * 32;
                 if (px < SLOT_PX) {
                   const uint32_t dp = pair + (uint32_t)(px * 16);
                   sts16(dp, v[i][0]);
