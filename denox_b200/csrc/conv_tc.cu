@@ -79,6 +79,8 @@ struct Seg {
   int tbox;           // 8 channel chunks per TMA copy (box extent of the tensor map's chunk dimension)
   int rg;             // ragged operand (C not a multiple of 8, at most 16 channels): its rows are fetched as raw
                       // bytes by a bulk copy and re-laid into the chunk layout inside shared memory
+  int dup;            // 2x upsampled operand whose tensor map has a pixel doubling dimension of stride 0: the copy
+                      // engine writes every half resolution pixel twice, i.e. the upsampled row itself
 };
 
 struct TcArgs {
@@ -116,6 +118,10 @@ struct TcArgs {
   uint32_t stage_warp_bytes;  // staging bytes per epilogue warp
   uint32_t tmem_cols;
   int parts;       // launches of this dispatch that run side by side (output channel split): each plans for 1/parts of the SMs
+  int ab;          // stacked form, one pipeline: two MMA warps issue alternate entries (see the kernel)
+  int eteams;      // stacked form: epilogue teams per pipeline (2: one pipeline, the teams take alternate items)
+  int shift;       // stacked form: the slots hold pixels x0 - 2 .. x0 + 129 instead of x0 - 1 .. x0 + 130 (a row that
+                   // comes through a pixel doubling map starts on an even pixel), so the MMAs read one pixel further
   int cparts;      // stacked form: output channel parts inside ONE launch (blockIdx.y): part p computes channels
                    // [p * N, p * N + N) from its own weight blob; K is then the dispatch's whole channel count
   unsigned long long wait_limit;  // clock64 ticks after which a barrier wait gives up (see mbar_wait)
@@ -195,9 +201,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const unsigned long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
     if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 1u) {  // after the first probe that came back empty handed, then every 64th
-      if (*abort_flag) return false;
+    // (a probe may itself suspend the thread for a while, so a wait that was over the limit when it came true
+    // counts as run out too: the limit is then honoured whatever the probe does)
+    const bool done = mbar_try_wait(bar, parity);
+    if (done || (it & 63u) == 1u) {  // after the first probe that came back empty handed, then every 64th
+      if (!done && *abort_flag) return false;
       // the limit (clock64 ticks) sits in the header right behind the abort flag, written once at kernel start
       const unsigned long long limit = *reinterpret_cast<const volatile unsigned long long *>(abort_flag + 1);
       if ((unsigned long long)clock64() - t0 > limit) {
@@ -205,6 +213,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (status) atomicCAS(status, 0, code);
         return false;
       }
+      if (done) return true;
     }
   }
 }
@@ -268,6 +277,14 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
       : "memory");
 }
 // 4-D tiled TMA load, global -> shared, completion counted in bytes on an mbarrier.
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const void *tmap, int c0, int c1, int c2, int c3, int c4,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], "
+      "[%7];" ::"r"(dst),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, int c0, int c1, int c2, int c3,
                                             uint32_t bar) {
   asm volatile(
@@ -1025,7 +1042,9 @@ constexpr int ST_BAR_RAW = ST_BAR_WRES + 1;  // [MAX_SLOTS] expand mode: TMA dat
 constexpr int ST_BAR_COUNT = ST_BAR_RAW + MAX_SLOTS;
 static_assert(ST_BAR_COUNT * 8 + 16 <= HEADER_BYTES, "header too small");
 constexpr int ST_OFF_TMEM_PTR = ST_BAR_COUNT * 8;
-constexpr int ST_OFF_ABORT = ST_OFF_TMEM_PTR + 4;
+constexpr int ST_OFF_ABORT = ST_OFF_TMEM_PTR + 4;   // int abort flag, then the 64-bit wait limit
+constexpr int ST_OFF_TURN = ST_OFF_ABORT + 12;      // entries issued so far (two alternating MMA threads)
+static_assert(ST_OFF_TURN + 4 <= HEADER_BYTES, "header too small");
 // entry descriptors, one per slot (index: pipeline's barrier offset + slot), written by the descriptor threads
 constexpr int ST_SUBDESC_BYTES = 48;                  // one input row
 constexpr int ST_DESC_BYTES = 2 * ST_SUBDESC_BYTES;   // an entry holds one or two input rows (TcArgs::ER)
@@ -1033,7 +1052,31 @@ constexpr int ST_OFF_DESC = HEADER_BYTES;
 constexpr int ST_HEADER_BYTES = HEADER_BYTES + MAX_SLOTS * ST_DESC_BYTES;
 static_assert(ST_HEADER_BYTES % 128 == 0, "weights must start on a 128 byte boundary");
 // descriptor flag word: bits 0-3 K steps of 16, then
-constexpr uint32_t DF_NR2 = 1u << 4, DF_LAST = 1u << 7;
+constexpr uint32_t DF_NR2 = 1u << 4, DF_PENULT = 1u << 6, DF_LAST = 1u << 7;
+
+// The stacked kernel's MMA warps run their loop with all lanes (so that two of them can meet at a named
+// barrier); only the lane with `leader` set issues.
+__device__ __forceinline__ void tc_mma_e(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t leader) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, e;\n\t"
+      "setp.ne.b32 p, 1, 0;\n\t"
+      "setp.ne.b32 e, %4, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(leader)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_e(uint32_t bar, uint32_t leader) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred e;\n\t"
+      "setp.ne.b32 e, %1, 0;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}" ::"r"(bar),
+      "r"(leader)
+      : "memory");
+}
 
 struct StUnit {
   int x0, y0, rows_out;
@@ -1059,7 +1102,7 @@ struct Run {
 // several MMAs in flight; a loop that reuses the registers issues three times slower (measured).
 template <int NK, int NR>
 __device__ __forceinline__ void st_issue_row(uint32_t hi, uint32_t row_lo, uint32_t b_lo, uint32_t wdx16, uint32_t kstep_b,
-                                             const Run &r0, const Run &r1) {
+                                             const Run &r0, const Run &r1, uint32_t leader) {
   constexpr uint32_t kstep_a = (2u * CHUNK_PITCH) >> 4;
 #pragma unroll
   for (int dx = 0; dx < 3; ++dx) {
@@ -1067,8 +1110,8 @@ __device__ __forceinline__ void st_issue_row(uint32_t hi, uint32_t row_lo, uint3
     for (int kc = 0; kc < NK; ++kc) {
       const uint32_t a = row_lo + (uint32_t)dx + (uint32_t)kc * kstep_a;
       const uint32_t b = b_lo + (uint32_t)dx * wdx16 + (uint32_t)kc * kstep_b;
-      tc_mma(r0.col, ((uint64_t)hi << 32) | a, ((uint64_t)hi << 32) | (b + r0.boff), r0.idesc, 1u);
-      if (NR == 2) tc_mma(r1.col, ((uint64_t)hi << 32) | a, ((uint64_t)hi << 32) | (b + r1.boff), r1.idesc, 1u);
+      tc_mma_e(r0.col, ((uint64_t)hi << 32) | a, ((uint64_t)hi << 32) | (b + r0.boff), r0.idesc, leader);
+      if (NR == 2) tc_mma_e(r1.col, ((uint64_t)hi << 32) | a, ((uint64_t)hi << 32) | (b + r1.boff), r1.idesc, leader);
     }
   }
 }
@@ -1078,16 +1121,16 @@ struct IntC {
 };
 template <int NR>
 __device__ __forceinline__ bool st_issue_nk(int nk, uint32_t hi, uint32_t row_lo, uint32_t b_lo, uint32_t wdx16,
-                                            uint32_t kstep_b, const Run &r0, const Run &r1) {
+                                            uint32_t kstep_b, const Run &r0, const Run &r1, uint32_t leader) {
   switch (nk) {
-    case 1: st_issue_row<1, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
-    case 2: st_issue_row<2, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
-    case 3: st_issue_row<3, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
-    case 4: st_issue_row<4, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
-    case 5: st_issue_row<5, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
-    case 6: st_issue_row<6, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
-    case 7: st_issue_row<7, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
-    case 8: st_issue_row<8, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1); return true;
+    case 1: st_issue_row<1, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 2: st_issue_row<2, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 3: st_issue_row<3, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 4: st_issue_row<4, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 5: st_issue_row<5, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 6: st_issue_row<6, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 7: st_issue_row<7, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 8: st_issue_row<8, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
     default: return false;
   }
 }
@@ -1132,11 +1175,23 @@ __device__ __forceinline__ void copy_out(uint32_t tile, int pitch, int nck, int 
   int px = lane / nck, ch = lane - px * nck;
   const int dpx = 32 / nck, dch = 32 - dpx * nck;
   uint4 *o = reinterpret_cast<uint4 *>(dst);
-  for (int i = lane; i < total; i += 32) {
-    o[px * os8 + ch] = lds16(tile + (uint32_t)(px * pitch + ch * 16));
+  // two pieces per lane and round: both loads are under way before the first store waits for its data (one at a
+  // time, every piece pays the shared memory latency by itself; more at a time cost registers the epilogue lacks)
+  for (int i = lane; i < total; i += 64) {
+    const int at0 = px * os8 + ch;
+    const uint4 v0 = lds16(tile + (uint32_t)(px * pitch + ch * 16));
     px += dpx;
     ch += dch;
     if (ch >= nck) { ch -= nck; ++px; }
+    const bool two = i + 32 < total;
+    const int at1 = px * os8 + ch;
+    uint4 v1 = v0;
+    if (two) v1 = lds16(tile + (uint32_t)(px * pitch + ch * 16));
+    px += dpx;
+    ch += dch;
+    if (ch >= nck) { ch -= nck; ++px; }
+    o[at0] = v0;
+    if (two) o[at1] = v1;
   }
 }
 
@@ -1222,6 +1277,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     if (lane == 0) {
       *abort_flag = 0;
       *reinterpret_cast<volatile unsigned long long *>(abort_flag + 1) = g.wait_limit;
+      *reinterpret_cast<volatile uint32_t *>(smem + ST_OFF_TURN) = 0u;
     }
     // who completes a slot: the TMA bytes alone; or TMA bytes + the producer warps' cp.async part; or, in expand
     // mode, the producer warps alone after they have expanded the TMA data that landed on the raw barrier;
@@ -1366,31 +1422,60 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   }
   if (warp == 1) __syncwarp();
 
-  if (warp < P) {
-    // ---------------- MMA issue of pipeline `warp`: one thread, one descriptor per entry ----------------
+  // Two issuing threads on one pipeline (TcArgs::ab, one pipeline only): lane 0 of warp 0 takes the even entries,
+  // lane 0 of warp 15 the odd ones.  A thread that issues tcgen05.mma gets nothing else done until the tensor pipe
+  // has taken the instruction, so with one issuing thread the per entry work (slot wait, descriptor, commits) is
+  // time the pipe idles; with two, one prepares its next entry while the other one issues, and the MMAs of
+  // consecutive entries follow each other without a gap.  The hand-over is a counter in shared memory (entries
+  // issued so far) that the thread whose turn it is next polls, bounded like every other wait; the order of the
+  // MMAs, and with it the order of the additions into an accumulator, stays that of the entries.
+  const bool ab = g.ab != 0;
+  if (warp < P || (ab && warp == 15)) {
+    // ---------------- MMA issue: one thread, one descriptor per entry ----------------
     // Everything that depends on where an entry sits in its unit (TMEM blocks, runs, barriers) was worked
     // out by the pipeline's descriptor thread and lies in shared memory when the slot's barrier completes;
     // this thread only waits, loads six vectors and issues.  It is the thread the kernel's speed hangs on.
-    const int pipe = warp;
+    const int pipe = warp == 15 ? 0 : warp;
+    const int me = warp == 15 ? 1 : 0;  // which of the two alternating threads
+    const int nw = ab ? 2 : 1;
+    const uint32_t leader = 1u;
     const int bofs = pipe * ST_PIPE_STRIDE;
     const uint32_t a_hi = (128u >> 4) | (1u << 14), b_hi = a_hi;
     const uint32_t kstep_a = (2u * CHUNK_PITCH) >> 4, kstep_b = 2u * 3u * N;
-    bool ok = mbar_wait(bar(ST_BAR_WRES), 0, abort_flag, g.status, 1);
-    const bool tr = DBG_TRACE_ON(g) && blockIdx.x == 0 && lane == 0 && pipe == 0;
-    auto mma1 = [&](uint32_t d, uint32_t alo, uint32_t blo, uint32_t idesc, uint32_t acc) {
-      tc_mma(d, ((uint64_t)a_hi << 32) | alo, ((uint64_t)b_hi << 32) | blo, idesc, acc);
+    bool ok = lane == 0 && mbar_wait(bar(ST_BAR_WRES), 0, abort_flag, g.status, 1);
+    const bool tr = DBG_TRACE_ON(g) && blockIdx.x == 0 && lane == 0 && warp == 0;
+    auto mma1 = [&](uint32_t d, uint32_t alo, uint32_t blo, uint32_t idesc) {
+      tc_mma_e(d, ((uint64_t)a_hi << 32) | alo, ((uint64_t)b_hi << 32) | blo, idesc, leader);
+    };
+    // Waits until `want` entries have been issued (this thread's turn); gives up like mbar_wait does.
+    volatile uint32_t *turn = reinterpret_cast<volatile uint32_t *>(smem + ST_OFF_TURN);
+    auto my_turn = [&](uint32_t want) -> bool {
+      if (*turn == want) return true;
+      const unsigned long long t0 = clock64();
+      for (uint32_t it = 1;; ++it) {
+        if (*turn == want) return true;
+        if ((it & 63u) == 0) {
+          if (*abort_flag) return false;
+          const unsigned long long limit = *reinterpret_cast<const volatile unsigned long long *>(abort_flag + 1);
+          if ((unsigned long long)clock64() - t0 > limit) {
+            *abort_flag = 1;
+            if (g.status) atomicCAS(g.status, 0, 11);
+            return false;
+          }
+        }
+      }
     };
     // The loop, instantiated per K step count: when all K groups have the same count, the choice of the
     // straight line form is made once here and not per row (NKC = 0: per row, by a switch).
     auto mma_loop = [&](auto NKC, auto ERC) {
       constexpr int NK = decltype(NKC)::value;
       constexpr int ERT = decltype(ERC)::value;  // input rows per entry
-      int slot = 0, pos = 0;
+      int slot = me, pos = me;                    // (the ring has at least two slots)
       uint32_t fphase = 0;
       for (;;) {
-        if (tr) trace(g, 0, pos, 0);
+        if (tr) trace(g, 0, pos >> (nw - 1), 0);
         if (!mbar_wait(bar(ST_BAR_FULL + bofs + slot), fphase, abort_flag, g.status, 2)) break;
-        if (tr) trace(g, 0, pos, 1);
+        if (tr) trace(g, 0, pos >> (nw - 1), 1);
         const uint32_t da = sbase + ST_OFF_DESC + (uint32_t)(bofs + slot) * ST_DESC_BYTES;
         uint4 q[ERT][3];
 #pragma unroll
@@ -1399,6 +1484,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           q[r][1] = lds16(da + (uint32_t)(r * ST_SUBDESC_BYTES + 16));
           q[r][2] = lds16(da + (uint32_t)(r * ST_SUBDESC_BYTES + 32));
         }
+        // my turn: the other thread has issued the entry before this one
+        if (ab && !my_turn((uint32_t)pos)) break;
         tc_fence_after();
         uint32_t allflags = 0;
 #pragma unroll
@@ -1410,37 +1497,44 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
             const uint32_t row_lo = q0.x, b_lo = q0.y;
             const Run R0 = {q1.x, q1.y, q1.z, 1u}, R1 = {q1.w, q2.x, q2.y, 1u};
             if constexpr (NK > 0) {
-              if (flags & DF_NR2) st_issue_row<NK, 2>(a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1);
-              else st_issue_row<NK, 1>(a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0);
+              if (flags & DF_NR2) st_issue_row<NK, 2>(a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1, leader);
+              else st_issue_row<NK, 1>(a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0, leader);
             } else {
               const int nk16 = (int)(flags & 15u);
               bool done = false;
               if (!DBG_LOOP_ISSUE(g))
-                done = (flags & DF_NR2) ? st_issue_nk<2>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1)
-                                        : st_issue_nk<1>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0);
+                done = (flags & DF_NR2) ? st_issue_nk<2>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1, leader)
+                                        : st_issue_nk<1>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0, leader);
               if (!done) {
                 // more K steps than the straight line forms cover
                 for (int dx = 0; dx < 3; ++dx)
                   for (int kc = 0; kc < nk16; ++kc) {
                     const uint32_t a = row_lo + (uint32_t)dx + (uint32_t)kc * kstep_a;
                     const uint32_t b = b_lo + (uint32_t)dx * (wdx_bytes >> 4) + (uint32_t)kc * kstep_b;
-                    mma1(R0.col, a, b + R0.boff, R0.idesc, 1u);
-                    if (flags & DF_NR2) mma1(R1.col, a, b + R1.boff, R1.idesc, 1u);
+                    mma1(R0.col, a, b + R0.boff, R0.idesc);
+                    if (flags & DF_NR2) mma1(R1.col, a, b + R1.boff, R1.idesc);
                   }
               }
             }
           }
-          if (tr) trace(g, 0, pos, 2);
+          if (tr) trace(g, 0, pos >> (nw - 1), 2);
+          if (ab && r == ERT - 1) {
+            // hand over: the other thread may issue the next entry; the commits below are this thread's own time
+            tc_fence_before();
+            *turn = (uint32_t)pos + 1u;
+          }
           // the slot is free once the MMAs of its last row are done; an output row completed by this input row
           // is announced right behind that row's MMAs
-          if (r == ERT - 1) tc_commit(bar(ST_BAR_EMPTY + bofs + slot));
-          if (q0.w) tc_commit(q0.w);
+          if (r == ERT - 1) tc_commit_e(bar(ST_BAR_EMPTY + bofs + slot), leader);
+          if (q0.w) tc_commit_e(q0.w, leader);
         }
-        if (tr) trace(g, 0, pos, 3);
+        if (tr) trace(g, 0, pos >> (nw - 1), 3);
         if (allflags & DF_LAST) break;
-        ++pos;
-        if (++slot == S) {
-          slot = 0;
+        if (ab && (allflags & DF_PENULT)) break;  // the other thread issues the last entry
+        pos += nw;
+        slot += nw;
+        if (slot >= S) {
+          slot -= S;
           fphase ^= 1u;
         }
       }
@@ -1472,11 +1566,14 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
       }
     }
     __syncwarp();
-  } else if (warp >= 2 && warp < 2 + 4 * P) {
-    // ---------------- epilogue: one team of four warps per pipeline ----------------
-    // (with the staged copy-out a team drains a row pair faster than the MMAs produce one)
+  } else if (warp >= 2 && warp < 2 + 4 * P * g.eteams) {
+    // ---------------- epilogue: teams of four warps ----------------
+    // Two pipelines: one team each.  One pipeline: one team, or two teams that take alternate items (a team
+    // needs about 3800 cycles for a row pair of 64 channels, two alternating MMA warps produce one in 2300).
     const int team = (warp - 2) >> 2;
-    const int pipe = team;
+    const int nteams = g.eteams;
+    const int pipe = nteams == 2 ? 0 : team;
+    const int myteam = nteams == 2 ? team : 0;
     const int bofs = pipe * ST_PIPE_STRIDE;
     const uint32_t tmem_base = tmem_base0 + (uint32_t)(pipe * NB * N);
     const int q = warp & 3;
@@ -1493,11 +1590,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     uint32_t tphase = 0;  // parity of tfull[blk] for the current round of the ring
     // Every MMA accumulates, so a block is zero when the MMA thread gets it: all of them once here (this
     // completes the first phase of the block barriers), and each one again when it has been read out.
-    for (int b = 0; b < NB; ++b) tc_zero_cols(lane_addr + (uint32_t)(b * N), N);
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0)
-      for (int b = 0; b < NB; ++b) mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b));
+    if (myteam == 0) {
+      for (int b = 0; b < NB; ++b) tc_zero_cols(lane_addr + (uint32_t)(b * N), N);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        for (int b = 0; b < NB; ++b) mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b));
+    }
     for (int u = (int)blockIdx.x + pipe * (int)gridDim.x; ok && u < g.nunits; u += unit_stride) {
       const StUnit t = st_unit_of(g, u);
       const int x = t.x0 + m;
@@ -1513,6 +1612,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         if (nrows == 2) {
           if (++blk == NB) { blk = 0; tphase ^= 1u; }
         }
+        if (nteams == 2 && (item & 1) != myteam) continue;  // the other team's item
         if (tr) trace(g, 1, item >> 1, 0);
         ok = mbar_wait<64>(bar(ST_BAR_TFULL + bofs + b0), ph0, abort_flag, g.status, 6);
         if (ok && nrows == 2) ok = mbar_wait<64>(bar(ST_BAR_TFULL + bofs + b1), ph1, abort_flag, g.status, 6);
@@ -1536,6 +1636,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
 #pragma unroll 1
               for (; c0 + 32 <= N; c0 += 32) stage_cols<32, EPI>(g, part, tr_addr, c0, tile + mine);
               if (c0 < N) stage_cols<16, EPI>(g, part, tr_addr, c0, tile + mine);
+              if (tr && r == 0) trace(g, 1, item >> 1, 3);
               if (r == nrows - 1) {
                 // last TMEM read of the item done: give the blocks back, zeroed (every MMA accumulates)
                 tc_zero_cols(t0, N);
@@ -1546,6 +1647,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
                   mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b0));
                   if (nrows == 2) mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b1));
                 }
+                if (tr) trace(g, 1, item >> 1, 4);
               } else {
                 __syncwarp();
               }
@@ -1553,6 +1655,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
                 if ((EPI & EPI_FULL) && !(DBG_SKIP(g) & 4))
                   copy_out(tile, pitch, nck, os8, npx, part.out + ((long long)(y + r) * g.W + xw) * g.os, lane);
                 __syncwarp();
+                if (tr && r == 0) trace(g, 1, item >> 1, 5);
               }
             }
             if (pool2) {
@@ -1632,18 +1735,29 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
                 for (int r = 0; r < g.ER; ++r) {
                   const int iy = t.y0 - 1 + jj + r;
                   const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes + (uint32_t)r * row_bytes;
+                  // first pixel of the slot row: x0 - 1, or x0 - 2 when an operand comes through a pixel doubling
+                  // map (whose rows start on an even pixel: half resolution pixel x0 / 2 - 1, row iy >> 1)
+                  const int xs = t.x0 - 1 - g.shift;
                   if (!band) {
-                    for (int c = c_lo; c < min(c_hi, nca); c += g.a.tbox)
-                      tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, t.x0 - 1, c, iy, fb);
+                    for (int c = c_lo; c < min(c_hi, nca); c += g.a.tbox) {
+                      if (g.a.dup)
+                        tma_load_5d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, 0, (t.x0 >> 1) - 1, c, iy >> 1, fb);
+                      else
+                        tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, xs, c, iy, fb);
+                    }
                     for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
-                      tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, t.x0 - 1, c - nca, iy, fb);
+                      tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, xs, c - nca, iy, fb);
                   } else {
                     int ya, yb;
-                    const void *tma = tmap_of(g, 0, iy, iy, &ya), *tmb = tmap_of(g, 1, iy, iy, &yb);
-                    for (int c = c_lo; c < min(c_hi, nca); c += g.a.tbox)
-                      tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), tma, 0, t.x0 - 1, c, ya, fb);
+                    const void *tma = tmap_of(g, 0, iy, g.a.dup ? iy >> 1 : iy, &ya), *tmb = tmap_of(g, 1, iy, iy, &yb);
+                    for (int c = c_lo; c < min(c_hi, nca); c += g.a.tbox) {
+                      if (g.a.dup)
+                        tma_load_5d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), tma, 0, 0, (t.x0 >> 1) - 1, c, ya, fb);
+                      else
+                        tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), tma, 0, xs, c, ya, fb);
+                    }
                     for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
-                      tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), tmb, 0, t.x0 - 1, c - nca, yb, fb);
+                      tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), tmb, 0, xs, c - nca, yb, fb);
                   }
                 }
               } else {
@@ -1870,11 +1984,15 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     const uint32_t idesc0 = (1u << 4) | ((uint32_t)(STRIP >> 4) << 24);
     const bool two = 2 * N <= 256, three = 3 * N <= 256;
     const uint32_t N16 = (uint32_t)N;  // weight rows of one vertical tap, in 16 byte units of a chunk
+    // instruction descriptors of runs of one, two and three blocks
+    const uint32_t idesc_len[3] = {idesc0 | ((uint32_t)(N >> 3) << 17), idesc0 | ((uint32_t)((2 * N) >> 3) << 17),
+                                   idesc0 | ((uint32_t)((3 * N) >> 3) << 17)};
     int slot = 0;
     uint32_t ephase = 1;  // parity to wait for on the empty barrier: first round passes
     int blkC = 0;
     uint32_t cphase = 0;  // parity to wait for on tempty[blkC]: the epilogue's first zeroing completes phase 0
     bool ok = true;
+    [[maybe_unused]] int dcount = 0;
     for (int u = (int)blockIdx.x + pipe * (int)gridDim.x; ok && u < g.nunits; u += unit_stride) {
       const StUnit t = st_unit_of(g, u);
       const int rows_in = t.rows_out + 2;
@@ -1894,7 +2012,21 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         // runs of neighbouring blocks one MMA can cover (every block starts zeroed, so all MMAs accumulate);
         // acc == 2: unused
         Run R0 = {0, 0, 0, 2}, R1 = R0, R2 = R0;
-        {
+        const bool mAB_mid = blkB != 0 && two, mBC_mid = blkC != 0 && two && (!mAB_mid || three);
+        if (vA && vB && vC && (mAB_mid || mBC_mid)) {
+          // the rows in the middle of a unit (all but four), spelled out: this thread has about a thousand cycles
+          // per entry when two MMA warps alternate, and the general form below takes most of them
+          const uint32_t cA = tmem_base + (uint32_t)(blkA * N);
+          if (mAB_mid && mBC_mid) {
+            R0 = {cA, 0u, idesc_len[2], 1u};
+          } else if (mAB_mid) {
+            R0 = {cA, 0u, idesc_len[1], 1u};
+            R1 = {tmem_base + (uint32_t)(blkC * N), 2u * N16, idesc_len[0], 1u};
+          } else {
+            R0 = {cA, 0u, idesc_len[0], 1u};
+            R1 = {tmem_base + (uint32_t)(blkB * N), N16, idesc_len[1], 1u};
+          }
+        } else {
           const bool mAB = vA && vB && blkB != 0 && two;
           const bool mBC = vB && vC && blkC != 0 && two && (!mAB || three);
           if (mAB && mBC) {
@@ -1922,14 +2054,19 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         // slot is waited for before the first half is described and handed over after the second
         const int sub = g.ER == 2 ? (jj & 1) : 0;
         for (int gi = 0; ok && gi < g.G; ++gi) {
+          if (DBG_TRACE_ON(g) && blockIdx.x == 0 && pipe == 0) trace(g, 2, dcount, 4);
           if (sub == 0) {
             ok = mbar_wait<32>(bar(ST_BAR_EMPTY + bofs + slot), ephase, abort_flag, g.status, 7);
             if (!ok) break;
           }
           uint32_t flags = rowflags | (uint32_t)(g.gch[gi] >> 1);
           if (last_unit && jj == rows_in - 1 && gi == g.G - 1) flags |= DF_LAST;
+          // the entry before the last one: the last entry of one of two alternating MMA warps
+          if (last_unit && ((g.G > 1 && jj == rows_in - 1 && gi == g.G - 2) || (g.G == 1 && jj == rows_in - 2)))
+            flags |= DF_PENULT;
           const uint32_t row_lo =
-              (((slots_addr + (uint32_t)slot * slot_bytes + (uint32_t)sub * row_bytes) & 0x3FFFFu) >> 4) | a_lo0;
+              (((slots_addr + (uint32_t)slot * slot_bytes + (uint32_t)sub * row_bytes + (uint32_t)g.shift * 16u) & 0x3FFFFu) >> 4) |
+              a_lo0;
           const uint32_t wgrp = (uint32_t)g.gc0[gi] * 3u * N16;  // group's first chunk, in 16 byte units
           const uint32_t b_lo = (((w_addr & 0x3FFFFu) >> 4) + wgrp) | b_lo0;
           const uint32_t tfbar = (gi == g.G - 1 && vA) ? bar(ST_BAR_TFULL + bofs + blkA) : 0u;
@@ -1942,6 +2079,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
             ok = mbar_wait<32>(bar(ST_BAR_TEMPTY + bofs + blkC), cphase, abort_flag, g.status, 3);
             if (!ok) break;
           }
+          if (DBG_TRACE_ON(g) && blockIdx.x == 0 && pipe == 0) trace(g, 2, dcount++, 5);
           if (sub == g.ER - 1) {
             mbar_arrive(bar(ST_BAR_FULL + bofs + slot));
             if (++slot == S) {
@@ -2069,6 +2207,29 @@ int make_tensor_map(CUtensorMap *tm, const void *ptr, int H, int W, int C, int b
   return r == CUDA_SUCCESS ? DNXCU_OK : DNXCU_E_CUDA;
 }
 
+// (H/2) x (W/2) x C binary16 tensor read through a 2x nearest upsample in x: rank 5 view (8, 2, W/2, C/8, H/2) whose
+// second dimension has stride 0, so a box of (8, 2, 66, chunks, 1) lands in shared memory as 132 pixels of 8
+// channels per chunk: every source pixel twice.  (The rows are doubled by reading row y >> 1.)
+int make_tensor_map_dup(CUtensorMap *tm, const void *ptr, int H2, int W2, int C, int box_chunks) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return DNXCU_E_CUDA;
+  const cuuint64_t dims[5] = {8, 2, (cuuint64_t)W2, (cuuint64_t)(C / 8), (cuuint64_t)H2};
+  const cuuint64_t strides[4] = {0, (cuuint64_t)C * 2, 16, (cuuint64_t)W2 * C * 2};
+  const cuuint32_t box[5] = {8, 2, (cuuint32_t)(WH / 2), (cuuint32_t)box_chunks, 1};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void *>(ptr), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if ((r != CUDA_ERROR_INVALID_CONTEXT && r != CUDA_ERROR_NOT_INITIALIZED) || cudaFree(nullptr) != cudaSuccess) break;
+  }
+  return r == CUDA_SUCCESS ? DNXCU_OK : DNXCU_E_CUDA;
+}
+// Whether the driver takes such maps: assumed until an encoding has failed once (then the producer warps expand
+// upsampled operands inside shared memory, as before).
+std::atomic<bool> g_dup_maps_ok{true};
+
 // One row tensor maps for the halo rows of a row band, per operand that is fetched by TMA: the same box as the
 // operand's own map (a half resolution row for an operand read through the 2x upsample).
 int encode_halo_maps(TcArgs &g, int W) {
@@ -2076,6 +2237,11 @@ int encode_halo_maps(TcArgs &g, int W) {
   for (int sg = 0; sg < 2; ++sg) {
     const Seg &s = sg ? g.b : g.a;
     if (!s.tma || s.nch == 0) continue;
+    if (s.dup) {
+      if (s.top && make_tensor_map_dup(&g.tm_halo[sg * 2], s.top, 1, W / 2, s.C, s.tbox)) return DNXCU_E_CUDA;
+      if (s.bot && make_tensor_map_dup(&g.tm_halo[sg * 2 + 1], s.bot, 1, W / 2, s.C, s.tbox)) return DNXCU_E_CUDA;
+      continue;
+    }
     const int Ws = s.up ? W / 2 : W, chunks = s.up ? 2 : s.tbox, px = s.up ? SRC_PX : WH;
     if (s.top && make_tensor_map(&g.tm_halo[sg * 2], s.top, 1, Ws, s.C, chunks, px)) return DNXCU_E_CUDA;
     if (s.bot && make_tensor_map(&g.tm_halo[sg * 2 + 1], s.bot, 1, Ws, s.C, chunks, px)) return DNXCU_E_CUDA;
@@ -2100,6 +2266,15 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   if (g.N > 128) return DNXCU_E_UNSUPPORTED;
   g.Ns = g.N;
   g.wstream = 0;
+  // A 2x upsampled operand of whole chunks comes through a pixel doubling tensor map when the other operand comes
+  // by TMA too: the copy engine writes the upsampled row, and nothing is left for the producer warps to do.
+  if (g.a.up && (g.a.C % 8) == 0 && !g.b.rg && (g.b.nch == 0 || g.b.tma) && g_dup_maps_ok.load(std::memory_order_relaxed) &&
+      !dbg_env("DNXCU_TC_NO_DUP")) {
+    g.a.dup = 1;
+    g.a.tma = 1;
+    g.cpa = 0;
+    g.shift = 1;
+  }
   const int nch = g.a.nch + g.b.nch;
   // K groups cost nothing here (every input row is used once): a slot holds one group of one row
   g.G = v.p1 > 0 ? v.p1 : 1;
@@ -2140,8 +2315,8 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   const bool a_up_ok = g.a.up && (g.a.C % 8) == 0;
   const bool a_kind_ok = a_up_ok || g.a.rg || (!g.a.up && g.a.tma);
   const bool b_kind_ok = g.b.nch == 0 || g.b.tma || g.b.rg;
-  const bool xp_possible = (a_up_ok || g.a.rg || g.b.rg) && a_kind_ok && b_kind_ok && !dbg_env("DNXCU_TC_NO_EXPAND") &&
-                           !dbg_env("DNXCU_TC_NO_TMA");
+  const bool xp_possible = !g.a.dup && (a_up_ok || g.a.rg || g.b.rg) && a_kind_ok && b_kind_ok &&
+                           !dbg_env("DNXCU_TC_NO_EXPAND") && !dbg_env("DNXCU_TC_NO_TMA");
   uint32_t xp_src_bytes = 0;
   if (xp_possible) {
     int amax = 0;
@@ -2164,9 +2339,15 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   int P = 0;
   size_t slot_bytes = 0, stage_total = 0;
   int total_slots = 0;
-  const int tries[8][3] = {{2, 1, 1}, {1, 1, 1}, {2, 1, 0}, {1, 1, 0}, {2, 0, 1}, {1, 0, 1}, {2, 0, 0}, {1, 0, 0}};
-  for (int ti = 0; ti < 8 && P == 0; ++ti) {
-    const int tp = tries[ti][0], txp = tries[ti][1], tst = tries[ti][2];
+  g.eteams = 1;
+  // one pipeline: a second epilogue team when its staging tiles fit (the second row of `tries` entries)
+  const int tries[16][4] = {{2, 1, 1, 1}, {1, 1, 1, 2}, {1, 1, 1, 1}, {2, 1, 0, 1}, {1, 1, 0, 2}, {2, 0, 1, 1}, {1, 0, 1, 2}, {1, 0, 1, 1},
+                            {2, 0, 0, 1}, {1, 0, 0, 2}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
+  const bool teams2_ok = ER == 1 && !dbg_env("DNXCU_TC_ONE_TEAM");
+  for (int ti = 0; ti < 16 && P == 0; ++ti) {
+    const int tp = tries[ti][0], txp = tries[ti][1], tst = tries[ti][2], tt = tries[ti][3];
+    if (tp == 0) break;
+    if (tt == 2 && (!teams2_ok || txp)) continue;  // (expand mode: the tiles would cost input slots, which count for more there)
     if (tp == 2 && !p2_possible) continue;
     {
       // two rows per entry keep four accumulator blocks in use at once: the ring must leave the epilogue room
@@ -2177,10 +2358,11 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
     if (txp != (xp_possible ? 1 : 0) && txp == 1) continue;
     if (tst && !stage_possible) continue;
     const size_t sb = plain_slot + (txp ? xp_src_bytes : 0);
-    const size_t st = tst ? (size_t)4 * tp * stage_per_warp : 0;
+    const size_t st = tst ? (size_t)4 * tp * tt * stage_per_warp : 0;
     const int min_slots = ER == 2 ? 2 : (tp == 2 ? 3 : 4);  // two issuing threads pay for a shorter ring
     if (base_bytes + st + (size_t)min_slots * tp * sb > SMEM_LIMIT) continue;
     P = tp;
+    g.eteams = tt;
     slot_bytes = sb;
     stage_total = st;
     total_slots = (int)((SMEM_LIMIT - base_bytes - st) / sb);
@@ -2207,6 +2389,10 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
     if (g.NB > ST_MAX_BLOCKS) g.NB = ST_MAX_BLOCKS;
     g.S = total_slots < MAX_SLOTS ? total_slots : MAX_SLOTS;
   }
+  // One pipeline: two MMA threads take alternate entries (each entry is one input row of one K group).  Not in
+  // fix-up mode: there the producer warps' work in shared memory bounds the kernel, and a second polling thread
+  // only takes shared memory cycles away from them (measured: 5-20 % slower).
+  g.ab = (P == 1 && ER == 1 && g.S >= 2 && !g.xp && !dbg_env("DNXCU_TC_ONE_ISSUER")) ? 1 : 0;
   uint32_t p2 = 32;
   while (p2 < (uint32_t)(P * g.NB * g.N)) p2 <<= 1;
   g.tmem_cols = p2;
@@ -2234,7 +2420,17 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   memset(&g.tm_b, 0, sizeof(g.tm_b));
   memset(g.tm_halo, 0, sizeof(g.tm_halo));
   if (encode) {
-    if (g.xp && g.a.up) {
+    if (g.a.dup) {
+      if (make_tensor_map_dup(&g.tm_a, d.in_a, H / 2, W / 2, d.c_a, g.a.tbox)) {
+        // this driver does not take a zero stride: plan again, with the expansion inside shared memory
+        g_dup_maps_ok.store(false, std::memory_order_relaxed);
+        g.a.dup = 0;
+        g.a.tma = 0;
+        g.cpa = 1;
+        g.shift = 0;
+        return make_plan_stack(v, d, pl, encode);
+      }
+    } else if (g.xp && g.a.up) {
       if (make_tensor_map(&g.tm_a, d.in_a, H / 2, W / 2, d.c_a, 2, SRC_PX)) return DNXCU_E_CUDA;
     } else if (g.a.tma && make_tensor_map(&g.tm_a, d.in_a, H, W, d.c_a, g.a.tbox)) {
       return DNXCU_E_CUDA;
@@ -2274,8 +2470,9 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
 
   pl.grid_y = 1;
   TcArgs &g = pl.args;
-  g.a = {(const __half *)d.in_a, (const __half *)d.halo[0], (const __half *)d.halo[1], d.c_a, nch_of(d.c_a), up ? 1 : 0, 0, 2, 0};
-  g.b = {(const __half *)d.in_b, (const __half *)d.halo[2], (const __half *)d.halo[3], d.c_b, nch_of(d.c_b), 0, 0, 2, 0};
+  g.a = {(const __half *)d.in_a, (const __half *)d.halo[0], (const __half *)d.halo[1], d.c_a, nch_of(d.c_a), up ? 1 : 0, 0, 2, 0, 0};
+  g.b = {(const __half *)d.in_b, (const __half *)d.halo[2], (const __half *)d.halo[3], d.c_b, nch_of(d.c_b), 0, 0, 2, 0, 0};
+  g.shift = 0;
   // TMA takes the operands whose pixels are whole 16 byte chunks at full resolution
   const bool allow_tma = !dbg_env("DNXCU_TC_NO_TMA");
   g.a.tma = allow_tma && !up && (d.c_a % 8 == 0);
@@ -2330,6 +2527,8 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   g.a.rg = g.b.rg = 0;  // the pass kernel loads ragged operands with its producer warps
   g.ER = 1;
   g.cparts = 1;
+  g.ab = 0;
+  g.eteams = 1;
   uint32_t cols = 2u * R * g.Ns;
   if (cols > 512) return DNXCU_E_UNSUPPORTED;
   uint32_t p2 = 32;
