@@ -1484,6 +1484,14 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           q[r][1] = lds16(da + (uint32_t)(r * ST_SUBDESC_BYTES + 16));
           q[r][2] = lds16(da + (uint32_t)(r * ST_SUBDESC_BYTES + 32));
         }
+        // the fresh accumulator block of each row has been read out and zeroed
+        {
+          bool blocks_ok = true;
+#pragma unroll
+          for (int r = 0; r < ERT; ++r)
+            if (q[r][2].z) blocks_ok = blocks_ok && mbar_wait(q[r][2].z, q[r][2].w, abort_flag, g.status, 3);
+          if (!blocks_ok) break;
+        }
         // my turn: the other thread has issued the entry before this one
         if (ab && !my_turn((uint32_t)pos)) break;
         tc_fence_after();
@@ -2073,12 +2081,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           const uint32_t da = sbase + ST_OFF_DESC + (uint32_t)(bofs + slot) * ST_DESC_BYTES + (uint32_t)(sub * ST_SUBDESC_BYTES);
           sts16(da, make_uint4(row_lo, b_lo, flags, tfbar));
           sts16(da + 16, make_uint4(R0.col, R0.boff, R0.idesc, R1.col));
-          sts16(da + 32, make_uint4(R1.boff, R1.idesc, 0u, 0u));
-          // the row's fresh TMEM block must have been read out and zeroed before the MMA thread may start the row
-          if (gi == 0 && vC) {
-            ok = mbar_wait<32>(bar(ST_BAR_TEMPTY + bofs + blkC), cphase, abort_flag, g.status, 3);
-            if (!ok) break;
-          }
+          // The row's fresh TMEM block must have been read out and zeroed before the MMAs of the row start.  The MMA
+          // thread waits for that itself, right before it issues (barrier and parity ride in the descriptor): this
+          // thread runs several entries ahead of the MMAs, and a wait here would claim the block that much earlier
+          // than it is needed, which a ring of eight blocks cannot afford.
+          const bool fresh = gi == 0 && vC;
+          sts16(da + 32, make_uint4(R1.boff, R1.idesc, fresh ? bar(ST_BAR_TEMPTY + bofs + blkC) : 0u, cphase));
           if (DBG_TRACE_ON(g) && blockIdx.x == 0 && pipe == 0) trace(g, 2, dcount++, 5);
           if (sub == g.ER - 1) {
             mbar_arrive(bar(ST_BAR_FULL + bofs + slot));
