@@ -213,9 +213,24 @@ def bands_4k(torch, dist, lib, nets, parallel, rank, world, local_rank, steps, w
     band_in = x[row0:row0 + rows].contiguous()
     raw = lambda ptr, n: torch.as_tensor(parallel._Raw(ptr, n * 2), device="cuda")
     raw(din, band_in.numel()).copy_(band_in.reshape(-1))
+    # every rank is ready before the first exchange: a band that starts seconds after its neighbours would let
+    # their first (bounded) wait run out
+    torch.cuda.synchronize()
+    dist.barrier()
     for _ in range(max(1, warmup)):
         runner.run()
-    torch.cuda.synchronize()
+        torch.cuda.synchronize()
+    warm_ok = 1
+    try:
+        runner.inst.wait()
+    except lib.DnxcuError:
+        warm_ok = 0
+    flag = torch.tensor([warm_ok], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if int(flag.item()) == 0:  # the same answer on every rank, so all of them leave together
+        runner.inst.close()
+        model.close()
+        return {"error": "a halo wait ran out during warm-up", "n_gpus": world} if rank == 0 else None
     dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -304,7 +319,9 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        # a rank that fell out of step ends the others' next collective after minutes, not after NCCL's default
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=300))
 
     def barrier():
         torch.cuda.synchronize()
@@ -461,8 +478,7 @@ def main():
     copy_fps = world * e2e_frames / copy_s
     del cdev_in, cdev_out, pin_in, pin_out
 
-    # ---- 4K frame in row bands over the same ranks ----
-    bands = None
+    # ---- free what the stream measurements held ----
     if dist is not None and not args.no_bands:
         for it in e2e_insts[1:]:
             it.close()
@@ -470,102 +486,129 @@ def main():
         insts = insts[:1]
         del dev_in[1:]
         torch.cuda.empty_cache()
-        try:
-            bands = bands_4k(torch, dist, lib, nets, parallel, rank, world, local_rank, args.band_steps, 3)
-        except Exception as e:  # the headline measurement above stands on its own
-            bands = {"error": f"{type(e).__name__}: {e}"[:300]}
 
+    out = None
+    if rank == 0:
+        # ---- per dispatch timing and roofline (rank 0) ----
+        pk = peaks()
+        infos, total_ms = insts[0].bench(warmup=3, iters=20)
+        table = []
+        for d in infos:
+            byts, flops = d.bytes_read + d.bytes_written, d.flops
+            nd = net.nodes[d.src_node]
+            if nd.kind == nets.CONV and d.flops > 0:
+                # algorithmic work from the model's own channel counts (no credit for zero padded channels)
+                c_real = net.channels[nd.in0]
+                c_run = d.c_a + d.c_b
+                flops = flops // c_run * c_real
+                byts -= 2 * d.h * d.w * (c_run - c_real) + 18 * (c_run - c_real) * d.c_out
+            t_s = d.ms * 1e-3
+            tf = flops / t_s / 1e12 if t_s > 0 else 0.0
+            gb = byts / t_s / 1e9 if t_s > 0 else 0.0
+            t_tc, t_hbm = flops / (pk["tc"] * 1e12), byts / (pk["hbm"] * 1e9)
+            bound = "tensor" if t_tc >= t_hbm else "hbm"
+            v = lib.L.dnxcu_variant(d.variant).contents
+            table.append(dict(name=net.nodes[d.src_node].name, dispatch=d.name.decode(), variant=v.config.decode(),
+                              hw=[d.h, d.w], c=[d.c_a, d.c_b, d.c_out], ms=round(d.ms, 5), tflops=round(tf, 2),
+                              gbs=round(gb, 1), bound=bound, frac=round(max(t_tc, t_hbm) / t_s, 4) if t_s > 0 else 0,
+                              share=round(d.ms / total_ms, 4), roof_ms=round(max(t_tc, t_hbm) * 1e3, 5)))
+        top = max(range(len(infos)), key=lambda i: infos[i].ms)
+        dt, tt = infos[top], table[top]
+        if tt["bound"] == "tensor":
+            roof = dict(bound="tensor", achieved=tt["tflops"], peak=pk["tc"], unit="TFLOP/s",
+                        frac=round(tt["tflops"] / pk["tc"], 4))
+        else:
+            roof = dict(bound="hbm", achieved=tt["gbs"], peak=pk["hbm"], unit="GB/s", frac=round(tt["gbs"] / pk["hbm"], 4))
+        shape_key = f"{dt.c_a}+{dt.c_b}->{dt.c_out}@{dt.h}x{dt.w}"
+        roof.update(traffic=measured_traffic(shape_key),
+                    kernel=f"conv3x3_tc {tt['name']} {dt.c_a}+{dt.c_b}->{dt.c_out} @{dt.h}x{dt.w}",
+                    peak_source=pk["src"], duration_ms=round(dt.ms, 5), share_of_frame=tt["share"])
+        sum_bound_ms = sum(r["roof_ms"] for r in table)
+
+        # ---- CPU baseline and parity on the same crop (rank 0, all host cores) ----
+        cpu = parity = None
+        if not args.no_cpu_baseline:
+            fps, dt_s, threads, crop_x, crop_ref = cpu_oracle_sample("f16", all_cores)
+            cpu = {"value": fps, "unit": "frames/s", "cores": threads, "kind": "port",
+                   "sample": f"whole net on a {CROP[0]}x{CROP[1]} crop (1/4 of the frame), binary16 accumulation, "
+                             f"{dt_s:.1f} s on {threads} threads, scaled by pixel count"}
+            ci = lib.Instance(model, CROP[0], CROP[1])
+            got = ci.infer(crop_x).astype(np.float32)
+            ci.close()
+            r = crop_ref.astype(np.float32)
+            dd = np.abs(got - r)
+            parity = {"against": "CPU oracle, binary16 accumulation (reference arithmetic), free running, whole net",
+                      "case": f"{CROP[0]}x{CROP[1]} crop of frame 1000", "max_abs": float(dd.max()),
+                      "mean_abs": float(dd.mean()), "rule": "|d| <= 2e-2 + 1e-2 |ref|",
+                      "violation_fraction": float((dd > 2e-2 + 1e-2 * np.abs(r)).mean())}
+
+        out = {
+            "metric": METRIC, "value": value, "unit": "frames/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "parallelism": f"frame-parallel x{world}" if world > 1 else "single GPU",
+                       "step": f"one pass over the {NF}-frame stream", "frames_per_step": NF,
+                       "l2": f"{NF} resident input frames per rank (2.4 GB > L2), every frame's activations 1.7 GB",
+                       "dispatches_per_frame": n_disp, "launches_per_frame": launches_per_frame, "streams": NS,
+                       "gflop_per_frame": nets.total_flops(net, H, W) / 1e9,
+                       "roofline_bound_ms_per_frame": round(sum_bound_ms, 4)},
+            "ms_per_frame": ms_per_frame,
+            "latency": dict(latency, note=f"event pair around each frame's graph, {NS} frames in flight"),
+            "single_stream": single,
+            "e2e": {"value": e2e, "unit": "frames/s", "h2d_bytes_per_step": in_bytes * NF, "d2h_bytes_per_step": out_bytes * NF,
+                    "h2d_bytes_per_frame": in_bytes, "d2h_bytes_per_frame": out_bytes, "frames": e2e_frames,
+                    "api": "dnxcu_instance_infer_async + dnxcu_instance_wait, 3 instances round robin, pinned host buffers",
+                    "copy_ceiling_fps": round(copy_fps, 1), "frac_of_copy_ceiling": round(e2e / copy_fps, 4),
+                    "h2d_gbs": round(e2e * in_bytes / 1e9, 2), "copy_ceiling_h2d_gbs": round(copy_fps * in_bytes / 1e9, 2),
+                    "numa_node": numa},
+            "gpu_launches": frames_timed * launches_per_frame,
+            "clocks": clocks,
+            "roofline": roof,
+            "cpu_baseline": cpu,
+            "parity": parity,
+            "tensor_tflops_whole_frame": round(nets.total_flops(net, H, W) / (ms_per_frame * 1e-3) / 1e12, 2),
+            "frac_of_roofline_sum": round(sum_bound_ms / ms_per_frame, 4),
+            "per_dispatch": table,
+        }
+
+    # ---- 4K frame in row bands over the same ranks ----
+    # Everything above is complete on rank 0 before this leg starts, and a watchdog prints it if the leg (or the
+    # final barrier) does not come back: one rank out of step must not cost the run its headline line.
+    import threading
+    done = threading.Lock()
+    state = {"printed": False}
+
+    def emit(bands_value):
+        with done:
+            if state["printed"]:
+                return
+            state["printed"] = True
+            if rank == 0:
+                if bands_value is not None:
+                    out["bands_4k"] = bands_value
+                print(json.dumps(out), file=result_out, flush=True)
+
+    bands = None
     if dist is not None:
+        limit = 240.0 if rank == 0 else 420.0  # (the other ranks wait for rank 0's per dispatch and CPU legs first)
+
+        def bail():
+            emit({"error": f"the row band leg gave no result within {limit:.0f} s", "n_gpus": world})
+            os._exit(0)
+
+        timer = threading.Timer(limit, bail)
+        timer.daemon = True
+        timer.start()
+        if not args.no_bands:
+            try:
+                bands = bands_4k(torch, dist, lib, nets, parallel, rank, world, local_rank, args.band_steps, 3)
+            except Exception as e:  # the headline measurement above stands on its own
+                bands = {"error": f"{type(e).__name__}: {e}"[:300]}
         torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
-    if rank != 0:
-        return
-
-    # ---- per dispatch timing and roofline (rank 0) ----
-    pk = peaks()
-    infos, total_ms = insts[0].bench(warmup=3, iters=20)
-    table = []
-    for d in infos:
-        byts, flops = d.bytes_read + d.bytes_written, d.flops
-        nd = net.nodes[d.src_node]
-        if nd.kind == nets.CONV and d.flops > 0:
-            # algorithmic work from the model's own channel counts (no credit for zero padded channels)
-            c_real = net.channels[nd.in0]
-            c_run = d.c_a + d.c_b
-            flops = flops // c_run * c_real
-            byts -= 2 * d.h * d.w * (c_run - c_real) + 18 * (c_run - c_real) * d.c_out
-        t_s = d.ms * 1e-3
-        tf = flops / t_s / 1e12 if t_s > 0 else 0.0
-        gb = byts / t_s / 1e9 if t_s > 0 else 0.0
-        t_tc, t_hbm = flops / (pk["tc"] * 1e12), byts / (pk["hbm"] * 1e9)
-        bound = "tensor" if t_tc >= t_hbm else "hbm"
-        v = lib.L.dnxcu_variant(d.variant).contents
-        table.append(dict(name=net.nodes[d.src_node].name, dispatch=d.name.decode(), variant=v.config.decode(),
-                          hw=[d.h, d.w], c=[d.c_a, d.c_b, d.c_out], ms=round(d.ms, 5), tflops=round(tf, 2),
-                          gbs=round(gb, 1), bound=bound, frac=round(max(t_tc, t_hbm) / t_s, 4) if t_s > 0 else 0,
-                          share=round(d.ms / total_ms, 4), roof_ms=round(max(t_tc, t_hbm) * 1e3, 5)))
-    top = max(range(len(infos)), key=lambda i: infos[i].ms)
-    dt, tt = infos[top], table[top]
-    if tt["bound"] == "tensor":
-        roof = dict(bound="tensor", achieved=tt["tflops"], peak=pk["tc"], unit="TFLOP/s",
-                    frac=round(tt["tflops"] / pk["tc"], 4))
-    else:
-        roof = dict(bound="hbm", achieved=tt["gbs"], peak=pk["hbm"], unit="GB/s", frac=round(tt["gbs"] / pk["hbm"], 4))
-    shape_key = f"{dt.c_a}+{dt.c_b}->{dt.c_out}@{dt.h}x{dt.w}"
-    roof.update(traffic=measured_traffic(shape_key),
-                kernel=f"conv3x3_tc {tt['name']} {dt.c_a}+{dt.c_b}->{dt.c_out} @{dt.h}x{dt.w}",
-                peak_source=pk["src"], duration_ms=round(dt.ms, 5), share_of_frame=tt["share"])
-    sum_bound_ms = sum(r["roof_ms"] for r in table)
-
-    # ---- CPU baseline and parity on the same crop (rank 0, all host cores) ----
-    cpu = parity = None
-    if not args.no_cpu_baseline:
-        fps, dt_s, threads, crop_x, crop_ref = cpu_oracle_sample("f16", all_cores)
-        cpu = {"value": fps, "unit": "frames/s", "cores": threads, "kind": "port",
-               "sample": f"whole net on a {CROP[0]}x{CROP[1]} crop (1/4 of the frame), binary16 accumulation, "
-                         f"{dt_s:.1f} s on {threads} threads, scaled by pixel count"}
-        ci = lib.Instance(model, CROP[0], CROP[1])
-        got = ci.infer(crop_x).astype(np.float32)
-        ci.close()
-        r = crop_ref.astype(np.float32)
-        dd = np.abs(got - r)
-        parity = {"against": "CPU oracle, binary16 accumulation (reference arithmetic), free running, whole net",
-                  "case": f"{CROP[0]}x{CROP[1]} crop of frame 1000", "max_abs": float(dd.max()),
-                  "mean_abs": float(dd.mean()), "rule": "|d| <= 2e-2 + 1e-2 |ref|",
-                  "violation_fraction": float((dd > 2e-2 + 1e-2 * np.abs(r)).mean())}
-
-    out = {
-        "metric": METRIC, "value": value, "unit": "frames/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "parallelism": f"frame-parallel x{world}" if world > 1 else "single GPU",
-                   "step": f"one pass over the {NF}-frame stream", "frames_per_step": NF,
-                   "l2": f"{NF} resident input frames per rank (2.4 GB > L2), every frame's activations 1.7 GB",
-                   "dispatches_per_frame": n_disp, "launches_per_frame": launches_per_frame, "streams": NS,
-                   "gflop_per_frame": nets.total_flops(net, H, W) / 1e9,
-                   "roofline_bound_ms_per_frame": round(sum_bound_ms, 4)},
-        "ms_per_frame": ms_per_frame,
-        "latency": dict(latency, note=f"event pair around each frame's graph, {NS} frames in flight"),
-        "single_stream": single,
-        "e2e": {"value": e2e, "unit": "frames/s", "h2d_bytes_per_step": in_bytes * NF, "d2h_bytes_per_step": out_bytes * NF,
-                "h2d_bytes_per_frame": in_bytes, "d2h_bytes_per_frame": out_bytes, "frames": e2e_frames,
-                "api": "dnxcu_instance_infer_async + dnxcu_instance_wait, 3 instances round robin, pinned host buffers",
-                "copy_ceiling_fps": round(copy_fps, 1), "frac_of_copy_ceiling": round(e2e / copy_fps, 4),
-                "h2d_gbs": round(e2e * in_bytes / 1e9, 2), "copy_ceiling_h2d_gbs": round(copy_fps * in_bytes / 1e9, 2),
-                "numa_node": numa},
-        "gpu_launches": frames_timed * launches_per_frame,
-        "clocks": clocks,
-        "roofline": roof,
-        "cpu_baseline": cpu,
-        "parity": parity,
-        "tensor_tflops_whole_frame": round(nets.total_flops(net, H, W) / (ms_per_frame * 1e-3) / 1e12, 2),
-        "frac_of_roofline_sum": round(sum_bound_ms / ms_per_frame, 4),
-        "per_dispatch": table,
-    }
-    if bands is not None:
-        out["bands_4k"] = bands
-    print(json.dumps(out), file=result_out, flush=True)
+        timer.cancel()
+    emit(bands)
 
 
 if __name__ == "__main__":

@@ -53,6 +53,10 @@ __global__ void __launch_bounds__(512) halo_xchg(const XchgArgs a) {
     __threadfence_system();
   }
   if (a.mode & XCHG_WAIT) {
+    // After a wait of this instance has run out its frames are void until the host has read the status and
+    // resynchronised the bands; waiting again for every later row would only add the limit once more per
+    // exchange (16 exchanges per frame).
+    if (a.status && *reinterpret_cast<volatile int *>(a.status) != 0) return;
     const unsigned long long t0 = clock64();
     for (int p = 0; p < a.npoints; ++p) {
       const XchgPoint &q = a.pt[p];
