@@ -527,7 +527,7 @@ def main():
 
         # ---- CPU baseline and parity on the same crop (rank 0, all host cores) ----
         cpu = parity = None
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:  # (a baseline of the one GPU run; the other ranks are waiting here)
             fps, dt_s, threads, crop_x, crop_ref = cpu_oracle_sample("f16", all_cores)
             cpu = {"value": fps, "unit": "frames/s", "cores": threads, "kind": "port",
                    "sample": f"whole net on a {CROP[0]}x{CROP[1]} crop (1/4 of the frame), binary16 accumulation, "
