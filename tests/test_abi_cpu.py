@@ -238,6 +238,34 @@ def test_prepare_weights_stacked_split_layout():
                     assert (t[part, sx, ch, 2 - r] == want).all()
 
 
+def test_prepare_weights_parts_of_one_launch():
+    """CSPLIT=3 at 80 output channels: three parts of 32 channels inside one launch, every part's blob 32 columns
+    wide (the last part holds 16 channels and 16 zero columns); the launch grid carries the parts in y."""
+    k, ca = 80, 16
+    w = nets.rng.he_normal_weights(11, k, ca)
+    vid = lib.find_variant("direct-conv-tc", "DY=stack#KG=1#W=resident#CSPLIT=3")
+    t = lib.prepare_weights(vid, w, ca).view(np.float16).reshape(3, 3, 2, 3, 32, 8)
+    for part in range(3):
+        n = min(32, k - part * 32)
+        for sx in range(3):
+            for r in range(3):
+                for ch in range(2):
+                    want = w[part * 32:part * 32 + n, ch * 8:(ch + 1) * 8, r, sx]
+                    assert (t[part, sx, ch, 2 - r, :n] == want).all()
+                    assert (t[part, sx, ch, 2 - r, n:] == 0).all()
+    d = lib.Dispatch()
+    d.variant, d.flags, d.c_a, d.c_out = vid, lib.F_RELU, ca, k
+    d.pc[0], d.pc[1] = 120, 68
+    d.in_a = d.out = d.weights = 0x1000
+    assert lib.L.dnxcu_validate(C.byref(d)) == 0
+    g = (C.c_uint32 * 3)()
+    assert lib.L.dnxcu_grid(C.byref(d), g) == 0
+    assert g[1] == 3 and g[2] == 1 and 1 <= g[0] <= 148 // 3
+    # nothing to split: the variant leaves the dispatch to the plain ones
+    d.c_out = 16
+    assert lib.L.dnxcu_validate(C.byref(d)) == lib.E_UNSUPPORTED
+
+
 def test_leaky_relu_flag_rules():
     ok = lib.L.dnxcu_validate
     d = _conv_dispatch(2)
