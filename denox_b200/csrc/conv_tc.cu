@@ -115,6 +115,7 @@ struct TcArgs {
   int xp;                // stacked form: operand a (2x upsampled) comes by TMA at half resolution and is expanded in shared memory
   uint32_t src_bytes;    // expand mode: bytes of one half resolution staging buffer (one per slot)
   int stage_pitch;       // stacked form: bytes per pixel row of an epilogue warp's staging tile, 0 = direct stores
+  int stage2;            // stacked form: two staging tiles per epilogue warp (a row pair is staged in one go)
   uint32_t stage_warp_bytes;  // staging bytes per epilogue warp
   uint32_t tmem_cols;
   int parts;       // launches of this dispatch that run side by side (output channel split): each plans for 1/parts of the SMs
@@ -277,6 +278,10 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
       : "memory");
 }
 // 4-D tiled TMA load, global -> shared, completion counted in bytes on an mbarrier.
+// Brings a tensor map into the descriptor cache ahead of its first use.
+__device__ __forceinline__ void tma_prefetch_map(const void *tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const void *tmap, int c0, int c1, int c2, int c3, int c4,
                                             uint32_t bar) {
   asm volatile(
@@ -1160,6 +1165,34 @@ __device__ __forceinline__ void stage_cols(const TcArgs &g, const OutPart &o, ui
                  : "memory");
 }
 
+// The same for one chunk of two rows: both TMEM loads are under way before the thread waits for either.
+template <int NC, int EPI>
+__device__ __forceinline__ void stage_cols2(const TcArgs &g, const OutPart &o, uint32_t taddr0, uint32_t taddr1, int c0,
+                                            uint32_t dst0, uint32_t dst1) {
+  uint32_t v0[NC], v1[NC];
+  if constexpr (NC == 32) {
+    tc_ld32(taddr0 + (uint32_t)c0, v0);
+    tc_ld32(taddr1 + (uint32_t)c0, v1);
+  } else {
+    tc_ld16(taddr0 + (uint32_t)c0, v0);
+    tc_ld16(taddr1 + (uint32_t)c0, v1);
+  }
+  tc_wait_ld();
+  uint32_t h[NC / 2];
+  round_row<NC, EPI>(g, o, v0, c0, h);
+#pragma unroll
+  for (int j8 = 0; j8 < NC; j8 += 8)
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 + (uint32_t)((c0 + j8) * 2)), "r"(h[j8 / 2]),
+                 "r"(h[j8 / 2 + 1]), "r"(h[j8 / 2 + 2]), "r"(h[j8 / 2 + 3])
+                 : "memory");
+  round_row<NC, EPI>(g, o, v1, c0, h);
+#pragma unroll
+  for (int j8 = 0; j8 < NC; j8 += 8)
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst1 + (uint32_t)((c0 + j8) * 2)), "r"(h[j8 / 2]),
+                 "r"(h[j8 / 2 + 1]), "r"(h[j8 / 2 + 2]), "r"(h[j8 / 2 + 3])
+                 : "memory");
+}
+
 __device__ __forceinline__ void sts16(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
@@ -1307,6 +1340,16 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
                  "r"(g.tmem_cols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (warp == 3 && lane == 0) {
+    // the first copy of every tensor map would otherwise wait for its descriptor (a launch of the small levels is
+    // a chain of such latencies)
+    if (g.a.tma) tma_prefetch_map(&g.tm_a);
+    if (g.b.tma && g.b.nch > 0) tma_prefetch_map(&g.tm_b);
+    if (g.a.tma && g.a.top) tma_prefetch_map(&g.tm_halo[0]);
+    if (g.a.tma && g.a.bot) tma_prefetch_map(&g.tm_halo[1]);
+    if (g.b.tma && g.b.top) tma_prefetch_map(&g.tm_halo[2]);
+    if (g.b.tma && g.b.bot) tma_prefetch_map(&g.tm_halo[3]);
   }
   tc_fence_before();
   __syncthreads();
@@ -1635,47 +1678,65 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           const uint32_t mine = (uint32_t)(lane * pitch);
           const int xw = t.x0 + q * 32;                      // first pixel of this warp
           const int npx = max(0, min(32, g.W - xw));        // pixels of this warp inside the image
-          const bool pool2 = (EPI & EPI_POOL) && nrows == 2;
+          // two tiles per warp (always with the fused pool, and where shared memory allows): a row pair is staged
+          // in one go, its blocks go back, then both rows are copied out
+          const bool both = g.stage2 && nrows == 2;
           if (!(DBG_SKIP(g) & 8)) {
-            for (int r = 0; r < nrows; ++r) {
-              const uint32_t tr_addr = r ? t1 : t0;
-              const uint32_t tile = (pool2 && r) ? tile1 : tile0;
+            if (both) {
               int c0 = 0;
 #pragma unroll 1
-              for (; c0 + 32 <= N; c0 += 32) stage_cols<32, EPI>(g, part, tr_addr, c0, tile + mine);
-              if (c0 < N) stage_cols<16, EPI>(g, part, tr_addr, c0, tile + mine);
-              if (tr && r == 0) trace(g, 1, item >> 1, 3);
-              if (r == nrows - 1) {
-                // last TMEM read of the item done: give the blocks back, zeroed (every MMA accumulates)
-                tc_zero_cols(t0, N);
-                if (nrows == 2) tc_zero_cols(t1, N);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                  mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b0));
-                  if (nrows == 2) mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b1));
-                }
-                if (tr) trace(g, 1, item >> 1, 4);
-              } else {
-                __syncwarp();
+              for (; c0 + 32 <= N; c0 += 32) stage_cols2<32, EPI>(g, part, t0, t1, c0, tile0 + mine, tile1 + mine);
+              if (c0 < N) stage_cols2<16, EPI>(g, part, t0, t1, c0, tile0 + mine, tile1 + mine);
+              if (tr) trace(g, 1, item >> 1, 3);
+              // last TMEM read of the item done: give the blocks back, zeroed (every MMA accumulates)
+              tc_zero_cols(t0, N);
+              tc_zero_cols(t1, N);
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) {
+                mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b0));
+                mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b1));
               }
-              if (!pool2) {
-                if ((EPI & EPI_FULL) && !(DBG_SKIP(g) & 4))
-                  copy_out(tile, pitch, nck, os8, npx, part.out + ((long long)(y + r) * g.W + xw) * g.os, lane);
-                __syncwarp();
-                if (tr && r == 0) trace(g, 1, item >> 1, 5);
-              }
-            }
-            if (pool2) {
+              if (tr) trace(g, 1, item >> 1, 4);
               if (!(DBG_SKIP(g) & 4)) {
                 if (EPI & EPI_FULL) {
                   copy_out(tile0, pitch, nck, os8, npx, part.out + ((long long)y * g.W + xw) * g.os, lane);
                   copy_out(tile1, pitch, nck, os8, npx, part.out + ((long long)(y + 1) * g.W + xw) * g.os, lane);
                 }
-                copy_out_pooled(tile0, tile1, pitch, nck, os8, npx,
-                                part.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (xw >> 1)) * g.os, lane);
+                if (EPI & EPI_POOL)
+                  copy_out_pooled(tile0, tile1, pitch, nck, os8, npx,
+                                  part.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (xw >> 1)) * g.os, lane);
               }
               __syncwarp();
+              if (tr) trace(g, 1, item >> 1, 5);
+            } else {
+              for (int r = 0; r < nrows; ++r) {
+                const uint32_t tr_addr = r ? t1 : t0;
+                int c0 = 0;
+#pragma unroll 1
+                for (; c0 + 32 <= N; c0 += 32) stage_cols<32, EPI>(g, part, tr_addr, c0, tile0 + mine);
+                if (c0 < N) stage_cols<16, EPI>(g, part, tr_addr, c0, tile0 + mine);
+                if (tr && r == 0) trace(g, 1, item >> 1, 3);
+                if (r == nrows - 1) {
+                  // last TMEM read of the item done: give the blocks back, zeroed (every MMA accumulates)
+                  tc_zero_cols(t0, N);
+                  if (nrows == 2) tc_zero_cols(t1, N);
+                  tc_fence_before();
+                  __syncwarp();
+                  if (lane == 0) {
+                    mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b0));
+                    if (nrows == 2) mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b1));
+                  }
+                  if (tr) trace(g, 1, item >> 1, 4);
+                } else {
+                  __syncwarp();
+                }
+                // (a single row of a plan with the fused pool is a last row without partner: it has no pooled output)
+                if ((EPI & EPI_FULL) && !(DBG_SKIP(g) & 4))
+                  copy_out(tile0, pitch, nck, os8, npx, part.out + ((long long)(y + r) * g.W + xw) * g.os, lane);
+                __syncwarp();
+                if (tr && r == 0) trace(g, 1, item >> 1, 5);
+              }
             }
           } else {
             tc_zero_cols(t0, N);
@@ -2338,7 +2399,10 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   }
   const bool stage_possible = g.K % 8 == 0 && !dbg_env("DNXCU_TC_NO_STAGE");
   const size_t stage_pitch = (size_t)(g.cparts > 1 ? g.N : g.K) * 2 + 16;
-  const size_t stage_per_warp = (g.pool ? 2 : 1) * 32 * stage_pitch;
+  // two tiles per warp where a row pair is staged in one go: with the fused pool (which needs both rows), and for
+  // thin layers, whose tiles are small and whose epilogue is what bounds them
+  const bool two_tiles = g.pool || (g.N <= 32 && !dbg_env("DNXCU_TC_ONE_TILE"));
+  const size_t stage_per_warp = (two_tiles ? 2 : 1) * 32 * stage_pitch;
   const size_t base_bytes = ST_HEADER_BYTES + wregion;
   const size_t plain_slot = (size_t)g.gmax * CHUNK_PITCH * ER;
   // v.p2 == 2 ("PIPES=1"): one pipeline with a longer slot ring even where two would fit
@@ -2377,6 +2441,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
     g.xp = txp;
     g.src_bytes = txp ? xp_src_bytes : 0;
     g.stage_pitch = tst ? (int)stage_pitch : 0;
+    g.stage2 = (tst && two_tiles) ? 1 : 0;
     g.stage_warp_bytes = tst ? (uint32_t)stage_per_warp : 0;
   }
   if (P == 0) return DNXCU_E_UNSUPPORTED;
@@ -2537,6 +2602,7 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   g.cparts = 1;
   g.ab = 0;
   g.eteams = 1;
+  g.stage2 = 0;
   uint32_t cols = 2u * R * g.Ns;
   if (cols > 512) return DNXCU_E_UNSUPPORTED;
   uint32_t p2 = 32;
