@@ -202,14 +202,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const unsigned long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
     if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
-    // (a probe may itself suspend the thread for a while, so a wait that was over the limit when it came true
-    // counts as run out too: the limit is then honoured whatever the probe does)
     const bool done = mbar_try_wait(bar, parity);
     if (done || (it & 63u) == 1u) {  // after the first probe that came back empty handed, then every 64th
       if (!done && *abort_flag) return false;
-      // the limit (clock64 ticks) sits in the header right behind the abort flag, written once at kernel start
-      const unsigned long long limit = *reinterpret_cast<const volatile unsigned long long *>(abort_flag + 1);
-      if ((unsigned long long)clock64() - t0 > limit) {
+      // The limit (clock64 ticks) sits in the header right behind the abort flag, written once at kernel start.
+      // Its top bit marks a limit below a millisecond (test use): a probe may itself suspend the thread for
+      // microseconds, so with such a limit a wait that was over it when it came true counts as run out too, and
+      // the limit is honoured whatever the probe does.  With ordinary limits a wait that came true has succeeded.
+      const unsigned long long raw = *reinterpret_cast<const volatile unsigned long long *>(abort_flag + 1);
+      if (done && !(raw >> 63)) return true;
+      if ((unsigned long long)clock64() - t0 > (raw & ~(1ull << 63))) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;
@@ -1499,7 +1501,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         if (*turn == want) return true;
         if ((it & 63u) == 0) {
           if (*abort_flag) return false;
-          const unsigned long long limit = *reinterpret_cast<const volatile unsigned long long *>(abort_flag + 1);
+          const unsigned long long limit =
+              *reinterpret_cast<const volatile unsigned long long *>(abort_flag + 1) & ~(1ull << 63);
           if ((unsigned long long)clock64() - t0 > limit) {
             *abort_flag = 1;
             if (g.status) atomicCAS(g.status, 0, 11);
@@ -2586,6 +2589,7 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   g.WST = v.p3 > 0 ? v.p3 : 2;
   if (g.WST > MAX_WST) g.WST = MAX_WST;
   g.wait_limit = wait_limit_cycles();
+  if (g.wait_limit < 2000000ull) g.wait_limit |= 1ull << 63;  // below about a millisecond: strict (see mbar_wait)
 #ifdef DNXCU_DEBUG_AIDS
   g.desc_swap = dbg_env("DNXCU_TC_DESC_SWAP") ? 1 : 0;
   const char *sk = getenv("DNXCU_TC_SKIP");
