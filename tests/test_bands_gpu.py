@@ -22,7 +22,7 @@ def _whole(net, x, h, w):
     return y
 
 
-@pytest.mark.parametrize("which,h,w,world", [("tiny", 64, 160, 2), ("oidn", 64, 144, 2), ("oidn", 128, 48, 4)])
+@pytest.mark.parametrize("which,h,w,world", [("tiny", 64, 160, 2), ("oidn", 64, 144, 2), ("oidn", 128, 48, 4), ("oidn", 384, 160, 8)])
 def test_bands_on_one_device_equal_whole_image(which, h, w, world):
     import torch
     from gpu_util import wrap
@@ -67,7 +67,7 @@ def test_bands_on_one_device_equal_whole_image(which, h, w, world):
     model.close()
 
 
-@pytest.mark.parametrize("which,h,w,world", [("tiny", 64, 160, 2), ("oidn", 64, 144, 2), ("oidn", 128, 48, 4)])
+@pytest.mark.parametrize("which,h,w,world", [("tiny", 64, 160, 2), ("oidn", 64, 144, 2), ("oidn", 128, 48, 4), ("oidn", 384, 160, 8)])
 def test_bands_with_peer_exchange_on_one_device(which, h, w, world):
     """The exchange kernel itself, with all bands on one device: every band pushes its boundary rows into its
     neighbours' slabs (the same stores that cross NVLink between GPUs), then every band waits for its flags,
