@@ -47,6 +47,9 @@ constexpr int STRIP = 128;        // pixels per MMA (M)
 constexpr int SLOT_PX = 130;      // pixels used per slot row (strip + 1 left + 1 right)
 constexpr int WH = 132;           // slot pixel pitch = TMA box width: two chunks = 4224 B, a multiple of 128
 constexpr int CHUNK_PITCH = WH * 16;
+constexpr int SW_PX = 136;                 // pixels per row of a swizzled block (the box of its tensor map)
+constexpr int SW_BLOCK = SW_PX * 64;       // 32 channels x 136 pixels: 8704 bytes = 17 x 512
+constexpr int SW_CHUNK = SW_BLOCK / 4;     // per 8 channel chunk of such a block
 constexpr int HEADER_BYTES = 1024;
 constexpr int MAX_SLOTS = 16;
 constexpr int MAX_GROUPS = 4;
@@ -79,6 +82,7 @@ struct Seg {
   int tbox;           // 8 channel chunks per TMA copy (box extent of the tensor map's chunk dimension)
   int rg;             // ragged operand (C not a multiple of 8, at most 16 channels): its rows are fetched as raw
                       // bytes by a bulk copy and re-laid into the chunk layout inside shared memory
+  int sw;             // pixel major slot layout with 64 byte swizzled rows of 32 channels ("blocks") for this operand
   int dup;            // 2x upsampled operand whose tensor map has a pixel doubling dimension of stride 0: the copy
                       // engine writes every half resolution pixel twice, i.e. the upsampled row itself
 };
@@ -121,6 +125,16 @@ struct TcArgs {
   int parts;       // launches of this dispatch that run side by side (output channel split): each plans for 1/parts of the SMs
   int ab;          // stacked form, one pipeline: two MMA warps issue alternate entries (see the kernel)
   int eteams;      // stacked form: epilogue teams per pipeline (2: one pipeline, the teams take alternate items)
+  // Stacked form, the A operand of the K steps of an entry (16 channels each), in K order: start address offset from
+  // the entry's slot row (>> 4, with the descriptor's leading byte offset bits), descriptor high word (stride byte
+  // offset, version, swizzle mode) and start address step per horizontal tap (>> 4).  Two slot layouts exist:
+  // [8 channel chunk][132 pixels][16 bytes] without swizzle, and, for operands of whole 32 channel blocks that
+  // come by TMA, [block][136 pixels][64 bytes] with the 64 byte swizzle (pixel major: the copy engine moves one
+  // box row per cycle, and these rows are four times as long).
+  uint32_t kst_lo[16], kst_hi[16], kst_dx[16];
+  uint32_t row_bytes;  // bytes of one input row (of one K group) in a slot
+  uint32_t seg_off[2]; // one K group: byte offset of each operand's area in the slot row
+  int swmode;          // some operand uses the swizzled layout
   int shift;       // stacked form: the slots hold pixels x0 - 2 .. x0 + 129 instead of x0 - 1 .. x0 + 130 (a row that
                    // comes through a pixel doubling map starts on an even pixel), so the MMAs read one pixel further
   int cparts;      // stacked form: output channel parts inside ONE launch (blockIdx.y): part p computes channels
@@ -1108,17 +1122,17 @@ struct Run {
 // line code.  Every instruction gets descriptor registers of its own, so the issuing thread keeps
 // several MMAs in flight; a loop that reuses the registers issues three times slower (measured).
 template <int NK, int NR>
-__device__ __forceinline__ void st_issue_row(uint32_t hi, uint32_t row_lo, uint32_t b_lo, uint32_t wdx16, uint32_t kstep_b,
-                                             const Run &r0, const Run &r1, uint32_t leader) {
-  constexpr uint32_t kstep_a = (2u * CHUNK_PITCH) >> 4;
+__device__ __forceinline__ void st_issue_row(const TcArgs &g, uint32_t hi, uint32_t row_lo, uint32_t b_lo, uint32_t wdx16,
+                                             uint32_t kstep_b, const Run &r0, const Run &r1, uint32_t leader) {
 #pragma unroll
   for (int dx = 0; dx < 3; ++dx) {
 #pragma unroll
     for (int kc = 0; kc < NK; ++kc) {
-      const uint32_t a = row_lo + (uint32_t)dx + (uint32_t)kc * kstep_a;
+      const uint32_t a = row_lo + g.kst_lo[kc] + (uint32_t)dx * g.kst_dx[kc];
+      const uint64_t ahi = (uint64_t)g.kst_hi[kc] << 32;
       const uint32_t b = b_lo + (uint32_t)dx * wdx16 + (uint32_t)kc * kstep_b;
-      tc_mma_e(r0.col, ((uint64_t)hi << 32) | a, ((uint64_t)hi << 32) | (b + r0.boff), r0.idesc, leader);
-      if (NR == 2) tc_mma_e(r1.col, ((uint64_t)hi << 32) | a, ((uint64_t)hi << 32) | (b + r1.boff), r1.idesc, leader);
+      tc_mma_e(r0.col, ahi | a, ((uint64_t)hi << 32) | (b + r0.boff), r0.idesc, leader);
+      if (NR == 2) tc_mma_e(r1.col, ahi | a, ((uint64_t)hi << 32) | (b + r1.boff), r1.idesc, leader);
     }
   }
 }
@@ -1127,17 +1141,17 @@ struct IntC {
   static constexpr int value = V;
 };
 template <int NR>
-__device__ __forceinline__ bool st_issue_nk(int nk, uint32_t hi, uint32_t row_lo, uint32_t b_lo, uint32_t wdx16,
-                                            uint32_t kstep_b, const Run &r0, const Run &r1, uint32_t leader) {
+__device__ __forceinline__ bool st_issue_nk(const TcArgs &g, int nk, uint32_t hi, uint32_t row_lo, uint32_t b_lo,
+                                            uint32_t wdx16, uint32_t kstep_b, const Run &r0, const Run &r1, uint32_t leader) {
   switch (nk) {
-    case 1: st_issue_row<1, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
-    case 2: st_issue_row<2, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
-    case 3: st_issue_row<3, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
-    case 4: st_issue_row<4, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
-    case 5: st_issue_row<5, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
-    case 6: st_issue_row<6, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
-    case 7: st_issue_row<7, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
-    case 8: st_issue_row<8, NR>(hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 1: st_issue_row<1, NR>(g, hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 2: st_issue_row<2, NR>(g, hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 3: st_issue_row<3, NR>(g, hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 4: st_issue_row<4, NR>(g, hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 5: st_issue_row<5, NR>(g, hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 6: st_issue_row<6, NR>(g, hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 7: st_issue_row<7, NR>(g, hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
+    case 8: st_issue_row<8, NR>(g, hi, row_lo, b_lo, wdx16, kstep_b, r0, r1, leader); return true;
     default: return false;
   }
 }
@@ -1291,9 +1305,10 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   const int N = g.N, NB = g.NB, P = g.P;
   const uint32_t wdx_bytes = (uint32_t)nch * 3u * N * 16u;  // one horizontal tap: all chunks x 3N rows
   const uint32_t w_addr = sbase + ST_HEADER_BYTES;
-  const uint32_t row_bytes = (uint32_t)g.gmax * CHUNK_PITCH;  // one input row (of one K group) in a slot
+  const uint32_t row_bytes = g.row_bytes;  // one input row (of one K group) in a slot
   const uint32_t slot_bytes = row_bytes * (uint32_t)g.ER;
-  const uint32_t slots_addr0 = w_addr + ((wdx_bytes * 3u + 127u) & ~127u);
+  // (slots on a 1024 byte boundary of the shared memory window: swizzled rows repeat their pattern every 512 bytes)
+  const uint32_t slots_addr0 = (w_addr + wdx_bytes * 3u + 1023u) & ~1023u;
   const int S = g.S;  // slots per pipeline
   const int unit_stride = (int)gridDim.x * P;
   const int nprod_warps = P == 2 ? 2 : 4;  // producer warps per pipeline
@@ -1485,12 +1500,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     const int nw = ab ? 2 : 1;
     const uint32_t leader = 1u;
     const int bofs = pipe * ST_PIPE_STRIDE;
-    const uint32_t a_hi = (128u >> 4) | (1u << 14), b_hi = a_hi;
-    const uint32_t kstep_a = (2u * CHUNK_PITCH) >> 4, kstep_b = 2u * 3u * N;
+    const uint32_t a_hi = (128u >> 4) | (1u << 14), b_hi = a_hi;  // (the B operand's high word; A's comes from the K step table)
+    const uint32_t kstep_b = 2u * 3u * N;
     bool ok = lane == 0 && mbar_wait(bar(ST_BAR_WRES), 0, abort_flag, g.status, 1);
     const bool tr = DBG_TRACE_ON(g) && blockIdx.x == 0 && lane == 0 && warp == 0;
-    auto mma1 = [&](uint32_t d, uint32_t alo, uint32_t blo, uint32_t idesc) {
-      tc_mma_e(d, ((uint64_t)a_hi << 32) | alo, ((uint64_t)b_hi << 32) | blo, idesc, leader);
+    auto mma1 = [&](uint32_t d, uint32_t ahi, uint32_t alo, uint32_t blo, uint32_t idesc) {
+      tc_mma_e(d, ((uint64_t)ahi << 32) | alo, ((uint64_t)b_hi << 32) | blo, idesc, leader);
     };
     // Waits until `want` entries have been issued (this thread's turn); gives up like mbar_wait does.
     volatile uint32_t *turn = reinterpret_cast<volatile uint32_t *>(smem + ST_OFF_TURN);
@@ -1551,22 +1566,22 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
             const uint32_t row_lo = q0.x, b_lo = q0.y;
             const Run R0 = {q1.x, q1.y, q1.z, 1u}, R1 = {q1.w, q2.x, q2.y, 1u};
             if constexpr (NK > 0) {
-              if (flags & DF_NR2) st_issue_row<NK, 2>(a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1, leader);
-              else st_issue_row<NK, 1>(a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0, leader);
+              if (flags & DF_NR2) st_issue_row<NK, 2>(g, b_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1, leader);
+              else st_issue_row<NK, 1>(g, b_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0, leader);
             } else {
               const int nk16 = (int)(flags & 15u);
               bool done = false;
               if (!DBG_LOOP_ISSUE(g))
-                done = (flags & DF_NR2) ? st_issue_nk<2>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1, leader)
-                                        : st_issue_nk<1>(nk16, a_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0, leader);
+                done = (flags & DF_NR2) ? st_issue_nk<2>(g, nk16, b_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R1, leader)
+                                        : st_issue_nk<1>(g, nk16, b_hi, row_lo, b_lo, wdx_bytes >> 4, kstep_b, R0, R0, leader);
               if (!done) {
                 // more K steps than the straight line forms cover
                 for (int dx = 0; dx < 3; ++dx)
                   for (int kc = 0; kc < nk16; ++kc) {
-                    const uint32_t a = row_lo + (uint32_t)dx + (uint32_t)kc * kstep_a;
+                    const uint32_t a = row_lo + g.kst_lo[kc & 15] + (uint32_t)dx * g.kst_dx[kc & 15];
                     const uint32_t b = b_lo + (uint32_t)dx * (wdx_bytes >> 4) + (uint32_t)kc * kstep_b;
-                    mma1(R0.col, a, b + R0.boff, R0.idesc);
-                    if (flags & DF_NR2) mma1(R1.col, a, b + R1.boff, R1.idesc);
+                    mma1(R0.col, g.kst_hi[kc & 15], a, b + R0.boff, R0.idesc);
+                    if (flags & DF_NR2) mma1(R1.col, g.kst_hi[kc & 15], a, b + R1.boff, R1.idesc);
                   }
               }
             }
@@ -1801,7 +1816,15 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
               if (tr) trace(g, 2, pcount, 1);
               const uint32_t fb = bar(ST_BAR_FULL + bofs + slot);
               const int c_lo = g.gc0[gi], c_hi = c_lo + g.gch[gi];
-              mbar_expect_tx(fb, (uint32_t)g.gch[gi] * CHUNK_PITCH * (uint32_t)g.ER);
+              // bytes of the group's row: 2112 per chunk in the 16 byte layout, 2176 per chunk (8704 per 32 channel
+              // block) in the swizzled one
+              uint32_t row_tx = (uint32_t)g.gch[gi] * CHUNK_PITCH;
+              if (g.swmode) {
+                const int sa = max(0, min(c_hi, nca) - c_lo), sbn = g.gch[gi] - sa;
+                row_tx = (uint32_t)sa * (g.a.sw ? (uint32_t)SW_CHUNK : (uint32_t)CHUNK_PITCH) +
+                         (uint32_t)sbn * (g.b.sw ? (uint32_t)SW_CHUNK : (uint32_t)CHUNK_PITCH);
+              }
+              mbar_expect_tx(fb, row_tx * (uint32_t)g.ER);
               if (!(DBG_SKIP(g) & 1)) {
                 // the entry's rows one after the other in the slot (rows past the image are zero filled by the copy)
                 for (int r = 0; r < g.ER; ++r) {
@@ -1810,33 +1833,33 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
                   // first pixel of the slot row: x0 - 1, or x0 - 2 when an operand comes through a pixel doubling
                   // map (whose rows start on an even pixel: half resolution pixel x0 / 2 - 1, row iy >> 1)
                   const int xs = t.x0 - 1 - g.shift;
-                  if (!band) {
-                    for (int c = c_lo; c < min(c_hi, nca); c += g.a.tbox) {
-                      if (g.a.dup)
-                        tma_load_5d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, 0, (t.x0 >> 1) - 1, c, iy >> 1, fb);
-                      else
-                        tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_a, 0, xs, c, iy, fb);
+#pragma unroll 1
+                  for (int sg = 0; sg < 2; ++sg) {
+                    const Seg &sgm = sg ? g.b : g.a;
+                    const int first = sg ? nca : 0;                       // the operand's first chunk
+                    const int lo = max(c_lo, first), hi = min(c_hi, first + sgm.nch);
+                    if (hi <= lo) continue;
+                    int y;
+                    const void *tm = band ? tmap_of(g, sg, iy, sgm.dup ? iy >> 1 : iy, &y) : (sg ? (const void *)&g.tm_b : (const void *)&g.tm_a);
+                    if (!band) y = sgm.dup ? iy >> 1 : iy;
+                    const uint32_t per = sgm.sw ? (uint32_t)SW_CHUNK : (uint32_t)CHUNK_PITCH;
+                    // where the operand's chunks of this group lie in the slot row
+                    uint32_t area;
+                    if (!g.swmode) area = (uint32_t)(lo - c_lo) * CHUNK_PITCH;
+                    else if (g.G == 1) area = g.seg_off[sg];
+                    else area = (uint32_t)(lo - c_lo) * SW_CHUNK;
+                    const int step = sgm.sw ? 4 * sgm.tbox : sgm.tbox;  // chunks per copy
+                    for (int c = lo; c < hi; c += step) {
+                      const uint32_t dst = slot_addr + area + (uint32_t)(c - lo) * per;
+                      const int unit = sgm.sw ? (c - first) >> 2 : c - first;  // block or chunk coordinate
+                      if (sgm.dup) tma_load_5d(dst, tm, 0, 0, (t.x0 >> 1) - 1, unit, y, fb);
+                      else tma_load_4d(dst, tm, 0, xs, unit, y, fb);
                     }
-                    for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
-                      tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), &g.tm_b, 0, xs, c - nca, iy, fb);
-                  } else {
-                    int ya, yb;
-                    const void *tma = tmap_of(g, 0, iy, g.a.dup ? iy >> 1 : iy, &ya), *tmb = tmap_of(g, 1, iy, iy, &yb);
-                    for (int c = c_lo; c < min(c_hi, nca); c += g.a.tbox) {
-                      if (g.a.dup)
-                        tma_load_5d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), tma, 0, 0, (t.x0 >> 1) - 1, c, ya, fb);
-                      else
-                        tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), tma, 0, xs, c, ya, fb);
-                    }
-                    for (int c = max(c_lo, nca); c < c_hi; c += g.b.tbox)
-                      tma_load_4d(slot_addr + (uint32_t)((c - c_lo) * CHUNK_PITCH), tmb, 0, xs, c - nca, yb, fb);
                   }
                 }
               } else {
                 // timing aid: nothing will land, so complete the transaction count by hand
-                asm volatile("mbarrier.complete_tx.shared::cta.b64 [%0], %1;" ::"r"(fb),
-                             "r"((uint32_t)g.gch[gi] * CHUNK_PITCH * (uint32_t)g.ER)
-                             : "memory");
+                asm volatile("mbarrier.complete_tx.shared::cta.b64 [%0], %1;" ::"r"(fb), "r"(row_tx * (uint32_t)g.ER) : "memory");
               }
               if (tr) trace(g, 2, pcount, 2);
               ++pcount;
@@ -2051,7 +2074,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     const int bofs = pipe * ST_PIPE_STRIDE;
     const uint32_t tmem_base = tmem_base0 + (uint32_t)(pipe * NB * N);
     const uint32_t slots_addr = slots_addr0 + (uint32_t)(pipe * S) * slot_bytes;
-    const uint32_t a_lo0 = ((uint32_t)CHUNK_PITCH >> 4) << 16;
     const uint32_t b_lo0 = (3u * N) << 16;  // leading offset = chunk pitch = 3N rows x 16 bytes, >> 4
     const uint32_t idesc0 = (1u << 4) | ((uint32_t)(STRIP >> 4) << 24);
     const bool two = 2 * N <= 256, three = 3 * N <= 256;
@@ -2136,9 +2158,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           // the entry before the last one: the last entry of one of two alternating MMA warps
           if (last_unit && ((g.G > 1 && jj == rows_in - 1 && gi == g.G - 2) || (g.G == 1 && jj == rows_in - 2)))
             flags |= DF_PENULT;
-          const uint32_t row_lo =
-              (((slots_addr + (uint32_t)slot * slot_bytes + (uint32_t)sub * row_bytes + (uint32_t)g.shift * 16u) & 0x3FFFFu) >> 4) |
-              a_lo0;
+          // (the slot row's address; layout, leading byte offset and the extra pixel of shifted rows are in the K step table)
+          const uint32_t row_lo = ((slots_addr + (uint32_t)slot * slot_bytes + (uint32_t)sub * row_bytes) & 0x3FFFFu) >> 4;
           const uint32_t wgrp = (uint32_t)g.gc0[gi] * 3u * N16;  // group's first chunk, in 16 byte units
           const uint32_t b_lo = (((w_addr & 0x3FFFFu) >> 4) + wgrp) | b_lo0;
           const uint32_t tfbar = (gi == g.G - 1 && vA) ? bar(ST_BAR_TFULL + bofs + blkA) : 0u;
@@ -2214,6 +2235,7 @@ struct Plan {
   size_t smem;
   int grid;
   int grid_y;  // output channel parts inside the launch (stacked form), else 1
+  int no_sw;   // stacked form: the swizzled slot layout did not fit (its K groups are whole 32 channel blocks): plan without
   int R;
 };
 
@@ -2298,6 +2320,33 @@ int make_tensor_map_dup(CUtensorMap *tm, const void *ptr, int H2, int W2, int C,
   }
   return r == CUDA_SUCCESS ? DNXCU_OK : DNXCU_E_CUDA;
 }
+// Pixel major views for the swizzled slot layout: rows of 32 channels (64 bytes), box (32, 136, blocks, 1), 64 byte
+// swizzle; the copy engine then moves a quarter of the box rows it moves for 16 byte rows.
+int make_tensor_map_sw(CUtensorMap *tm, const void *ptr, int H, int W, int C, int box_blocks, bool dup) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return DNXCU_E_CUDA;
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    if (!dup) {
+      const cuuint64_t dims[4] = {32, (cuuint64_t)W, (cuuint64_t)(C / 32), (cuuint64_t)H};
+      const cuuint64_t strides[3] = {(cuuint64_t)C * 2, 64, (cuuint64_t)W * C * 2};
+      const cuuint32_t box[4] = {32, (cuuint32_t)SW_PX, (cuuint32_t)box_blocks, 1};
+      r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {  // (H, W: extent of the half resolution tensor)
+      const cuuint64_t dims[5] = {32, 2, (cuuint64_t)W, (cuuint64_t)(C / 32), (cuuint64_t)H};
+      const cuuint64_t strides[4] = {0, (cuuint64_t)C * 2, 64, (cuuint64_t)W * C * 2};
+      const cuuint32_t box[5] = {32, 2, (cuuint32_t)(SW_PX / 2), (cuuint32_t)box_blocks, 1};
+      r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void *>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if ((r != CUDA_ERROR_INVALID_CONTEXT && r != CUDA_ERROR_NOT_INITIALIZED) || cudaFree(nullptr) != cudaSuccess) break;
+  }
+  return r == CUDA_SUCCESS ? DNXCU_OK : DNXCU_E_CUDA;
+}
 // Whether the driver takes such maps: assumed until an encoding has failed once (then the producer warps expand
 // upsampled operands inside shared memory, as before).
 std::atomic<bool> g_dup_maps_ok{true};
@@ -2309,6 +2358,12 @@ int encode_halo_maps(TcArgs &g, int W) {
   for (int sg = 0; sg < 2; ++sg) {
     const Seg &s = sg ? g.b : g.a;
     if (!s.tma || s.nch == 0) continue;
+    if (s.sw) {
+      const int Ws = s.dup ? W / 2 : W;
+      if (s.top && make_tensor_map_sw(&g.tm_halo[sg * 2], s.top, 1, Ws, s.C, s.tbox, s.dup != 0)) return DNXCU_E_CUDA;
+      if (s.bot && make_tensor_map_sw(&g.tm_halo[sg * 2 + 1], s.bot, 1, Ws, s.C, s.tbox, s.dup != 0)) return DNXCU_E_CUDA;
+      continue;
+    }
     if (s.dup) {
       if (s.top && make_tensor_map_dup(&g.tm_halo[sg * 2], s.top, 1, W / 2, s.C, s.tbox)) return DNXCU_E_CUDA;
       if (s.bot && make_tensor_map_dup(&g.tm_halo[sg * 2 + 1], s.bot, 1, W / 2, s.C, s.tbox)) return DNXCU_E_CUDA;
@@ -2372,9 +2427,82 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   const int ER = v.p4 == 2 ? 2 : 1;
   if (ER == 2 && (g.cpa || g.a.up || g.G != 1 || (H & 1) || nch / 2 > 6)) return DNXCU_E_UNSUPPORTED;
   g.ER = ER;
-  // one TMA copy per operand and row when a slot holds all channels, else two chunks per copy
-  g.a.tbox = (g.G == 1) ? g.a.nch : 2;
-  g.b.tbox = (g.G == 1 && g.b.nch) ? g.b.nch : 2;
+  // Slot layout per operand.  Everything by TMA, one input row per entry, an operand of whole 32 channel blocks:
+  // pixel major rows with the 64 byte swizzle.  With K groups every operand must be of that kind, and the groups
+  // are made of whole blocks.
+  g.a.sw = g.b.sw = 0;
+  if (!g.cpa && ER == 1 && !pl.no_sw && !dbg_env("DNXCU_TC_NO_SW")) {
+    const bool a_sw = g.a.C % 32 == 0, b_sw = g.b.nch > 0 && g.b.C % 32 == 0;
+    if (g.G == 1) {
+      g.a.sw = a_sw;
+      g.b.sw = b_sw;
+    } else if (a_sw && (g.b.nch == 0 || b_sw)) {
+      int per = (nch + g.G - 1) / g.G;
+      per = (per + 3) / 4 * 4;
+      int c = 0, gi = 0;
+      for (; gi < MAX_GROUPS && c < nch; ++gi) {
+        g.gc0[gi] = c;
+        g.gch[gi] = (nch - c < per) ? nch - c : per;
+        c += g.gch[gi];
+      }
+      g.G = gi;
+      for (; gi < MAX_GROUPS; ++gi) g.gc0[gi] = g.gch[gi] = 0;
+      g.gmax = per < nch ? per : nch;
+      g.a.sw = 1;
+      g.b.sw = g.b.nch > 0;
+    }
+  }
+  g.swmode = (g.a.sw || g.b.sw) ? 1 : 0;
+  // chunks (16 byte layout) or blocks (swizzled layout) per TMA copy: the operand's whole row when a slot holds all
+  // channels, else two chunks / one block
+  g.a.tbox = g.a.sw ? (g.G == 1 ? g.a.nch / 4 : 1) : ((g.G == 1) ? g.a.nch : 2);
+  g.b.tbox = g.b.sw ? (g.G == 1 ? g.b.nch / 4 : 1) : ((g.G == 1 && g.b.nch) ? g.b.nch : 2);
+  // the slot row and the K step table of an entry
+  {
+    const uint32_t hi16 = (128u >> 4) | (1u << 14);                 // 16 byte layout: stride 128 bytes, version 1
+    const uint32_t hisw = (512u >> 4) | (1u << 14) | (4u << 29);    // swizzled: stride 512 bytes, version 1, 64 byte swizzle
+    const uint32_t lbo16 = ((uint32_t)CHUNK_PITCH >> 4) << 16, lbosw = 1u << 16;
+    const uint32_t sh16 = g.shift ? 1u : 0u, shsw = g.shift ? 4u : 0u;  // rows that start one pixel early
+    for (int kc = 0; kc < 16; ++kc) {
+      g.kst_lo[kc] = ((uint32_t)kc * ((2u * CHUNK_PITCH) >> 4) + sh16) | lbo16;
+      g.kst_hi[kc] = hi16;
+      g.kst_dx[kc] = 1;
+    }
+    g.seg_off[0] = g.seg_off[1] = 0;
+    g.row_bytes = (uint32_t)g.gmax * CHUNK_PITCH;
+    if (g.swmode && g.G > 1) {
+      g.row_bytes = (uint32_t)g.gmax * SW_CHUNK;
+      for (int kc = 0; kc < 16; ++kc) {
+        g.kst_lo[kc] = ((((uint32_t)(kc >> 1) * SW_BLOCK + (uint32_t)(kc & 1) * 32u) >> 4) + shsw) | lbosw;
+        g.kst_hi[kc] = hisw;
+        g.kst_dx[kc] = 4;
+      }
+    } else if (g.swmode) {
+      // swizzled areas first (they want 512 byte boundaries), then the 16 byte chunks
+      uint32_t off = 0;
+      if (g.a.sw) { g.seg_off[0] = off; off += (uint32_t)(g.a.nch / 4) * SW_BLOCK; }
+      if (g.b.sw) { g.seg_off[1] = off; off += (uint32_t)(g.b.nch / 4) * SW_BLOCK; }
+      if (!g.a.sw) { g.seg_off[0] = off; off += (uint32_t)g.a.nch * CHUNK_PITCH; }
+      if (g.b.nch > 0 && !g.b.sw) { g.seg_off[1] = off; off += (uint32_t)g.b.nch * CHUNK_PITCH; }
+      g.row_bytes = (off + 511u) & ~511u;
+      int kc = 0;
+      for (int sg = 0; sg < 2; ++sg) {
+        const Seg &s = sg ? g.b : g.a;
+        for (int j = 0; j < s.nch / 2 && kc < 16; ++j, ++kc) {
+          if (s.sw) {
+            g.kst_lo[kc] = (((g.seg_off[sg] + (uint32_t)(j >> 1) * SW_BLOCK + (uint32_t)(j & 1) * 32u) >> 4) + shsw) | lbosw;
+            g.kst_hi[kc] = hisw;
+            g.kst_dx[kc] = 4;
+          } else {
+            g.kst_lo[kc] = (((g.seg_off[sg] + (uint32_t)j * 2u * CHUNK_PITCH) >> 4) + sh16) | lbo16;
+            g.kst_hi[kc] = hi16;
+            g.kst_dx[kc] = 1;
+          }
+        }
+      }
+      if (nch / 2 > 16) return DNXCU_E_UNSUPPORTED;
+    }
+  }
   const size_t wbytes = (size_t)9 * nch * g.N * 16;
   if (wbytes >= (1u << 20)) return DNXCU_E_UNSUPPORTED;
   const size_t wregion = (wbytes + 127) & ~(size_t)127;
@@ -2406,8 +2534,8 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   // thin layers, whose tiles are small and whose epilogue is what bounds them
   const bool two_tiles = g.pool || (g.N <= 32 && !dbg_env("DNXCU_TC_ONE_TILE"));
   const size_t stage_per_warp = (two_tiles ? 2 : 1) * 32 * stage_pitch;
-  const size_t base_bytes = ST_HEADER_BYTES + wregion;
-  const size_t plain_slot = (size_t)g.gmax * CHUNK_PITCH * ER;
+  const size_t base_bytes = ST_HEADER_BYTES + wregion + 1024;  // (the slots start on a 1024 byte boundary)
+  const size_t plain_slot = (size_t)g.row_bytes * ER;
   // v.p2 == 2 ("PIPES=1"): one pipeline with a longer slot ring even where two would fit
   const bool p2_possible = 4 * g.N <= 256 && !dbg_env("DNXCU_TC_PIPES") && v.p2 != 2;
   // candidate configurations, best first: (pipelines, expand, staging)
@@ -2447,6 +2575,10 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
     g.stage2 = (tst && two_tiles) ? 1 : 0;
     g.stage_warp_bytes = tst ? (uint32_t)stage_per_warp : 0;
   }
+  if (P == 0 && g.swmode && !pl.no_sw) {
+    pl.no_sw = 1;  // (groups of whole blocks can make the slots larger than the 16 byte layout would)
+    return make_plan_stack(v, d, pl, encode);
+  }
   if (P == 0) return DNXCU_E_UNSUPPORTED;
   if (g.xp) {
     g.cpa = 1;
@@ -2473,7 +2605,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   while (p2 < (uint32_t)(P * g.NB * g.N)) p2 <<= 1;
   g.tmem_cols = p2;
   g.D = g.S - 1 < MAX_DEPTH ? g.S - 1 : MAX_DEPTH;
-  pl.smem = ST_HEADER_BYTES + wregion + (size_t)P * g.S * slot_bytes + stage_total;
+  pl.smem = ST_HEADER_BYTES + wregion + 1024 + (size_t)P * g.S * slot_bytes + stage_total;
   const int sms = g.parts > 1 ? (sm_count() / g.parts > 0 ? sm_count() / g.parts : 1) : sm_count();
   const int lanes = sms * P;
   double best = 1e30;
@@ -2496,7 +2628,9 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   memset(&g.tm_b, 0, sizeof(g.tm_b));
   memset(g.tm_halo, 0, sizeof(g.tm_halo));
   if (encode) {
-    if (g.a.dup) {
+    if (g.a.sw) {
+      if (make_tensor_map_sw(&g.tm_a, d.in_a, g.a.dup ? H / 2 : H, g.a.dup ? W / 2 : W, d.c_a, g.a.tbox, g.a.dup != 0)) return DNXCU_E_CUDA;
+    } else if (g.a.dup) {
       if (make_tensor_map_dup(&g.tm_a, d.in_a, H / 2, W / 2, d.c_a, g.a.tbox)) {
         // this driver does not take a zero stride: plan again, with the expansion inside shared memory
         g_dup_maps_ok.store(false, std::memory_order_relaxed);
@@ -2511,7 +2645,11 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
     } else if (g.a.tma && make_tensor_map(&g.tm_a, d.in_a, H, W, d.c_a, g.a.tbox)) {
       return DNXCU_E_CUDA;
     }
-    if (g.b.tma && make_tensor_map(&g.tm_b, d.in_b, H, W, d.c_b, g.b.tbox)) return DNXCU_E_CUDA;
+    if (g.b.sw) {
+      if (make_tensor_map_sw(&g.tm_b, d.in_b, H, W, d.c_b, g.b.tbox, false)) return DNXCU_E_CUDA;
+    } else if (g.b.tma && make_tensor_map(&g.tm_b, d.in_b, H, W, d.c_b, g.b.tbox)) {
+      return DNXCU_E_CUDA;
+    }
     if (encode_halo_maps(g, W)) return DNXCU_E_CUDA;
   }
   return DNXCU_OK;
@@ -2545,9 +2683,10 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
     return DNXCU_E_MISALIGNED;
 
   pl.grid_y = 1;
+  pl.no_sw = 0;
   TcArgs &g = pl.args;
-  g.a = {(const __half *)d.in_a, (const __half *)d.halo[0], (const __half *)d.halo[1], d.c_a, nch_of(d.c_a), up ? 1 : 0, 0, 2, 0, 0};
-  g.b = {(const __half *)d.in_b, (const __half *)d.halo[2], (const __half *)d.halo[3], d.c_b, nch_of(d.c_b), 0, 0, 2, 0, 0};
+  g.a = {(const __half *)d.in_a, (const __half *)d.halo[0], (const __half *)d.halo[1], d.c_a, nch_of(d.c_a), up ? 1 : 0, 0, 2, 0, 0, 0};
+  g.b = {(const __half *)d.in_b, (const __half *)d.halo[2], (const __half *)d.halo[3], d.c_b, nch_of(d.c_b), 0, 0, 2, 0, 0, 0};
   g.shift = 0;
   // TMA takes the operands whose pixels are whole 16 byte chunks at full resolution
   const bool allow_tma = !dbg_env("DNXCU_TC_NO_TMA");
