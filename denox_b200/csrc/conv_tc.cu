@@ -132,6 +132,16 @@ struct TcArgs {
   // come by TMA, [block][136 pixels][64 bytes] with the 64 byte swizzle (pixel major: the copy engine moves one
   // box row per cycle, and these rows are four times as long).
   uint32_t kst_lo[16], kst_hi[16], kst_dx[16];
+  // The TMA copies of an entry, per K group, worked out by the host: where the box lands in the slot row, which
+  // operand, and its chunk or block coordinate.  (The feeding thread is a single thread: what it has to compute per
+  // entry is time the slots wait.)
+  struct Copy {
+    uint32_t dst;
+    short unit;
+    unsigned char sg, pad;
+  } cp[MAX_GROUPS][8];
+  int ncp[MAX_GROUPS];
+  uint32_t grp_tx[MAX_GROUPS];  // bytes the copies of one row of the group bring
   uint32_t row_bytes;  // bytes of one input row (of one K group) in a slot
   uint32_t seg_off[2]; // one K group: byte offset of each operand's area in the slot row
   int swmode;          // some operand uses the swizzled layout
@@ -1804,7 +1814,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
       if (tid == 0) {
         int slot = 0, pcount = 0;
         uint32_t phase = 1;  // parity to wait for on the empty barrier: first round passes
-        const int nca = g.a.nch;
         const bool tr = DBG_TRACE_ON(g) && blockIdx.x == 0 && pipe == 0;
         for (int u = (int)blockIdx.x + pipe * (int)gridDim.x; ok && u < g.nunits; u += unit_stride) {
           const StUnit t = st_unit_of(g, u);
@@ -1815,15 +1824,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
               if (!ok) break;
               if (tr) trace(g, 2, pcount, 1);
               const uint32_t fb = bar(ST_BAR_FULL + bofs + slot);
-              const int c_lo = g.gc0[gi], c_hi = c_lo + g.gch[gi];
-              // bytes of the group's row: 2112 per chunk in the 16 byte layout, 2176 per chunk (8704 per 32 channel
-              // block) in the swizzled one
-              uint32_t row_tx = (uint32_t)g.gch[gi] * CHUNK_PITCH;
-              if (g.swmode) {
-                const int sa = max(0, min(c_hi, nca) - c_lo), sbn = g.gch[gi] - sa;
-                row_tx = (uint32_t)sa * (g.a.sw ? (uint32_t)SW_CHUNK : (uint32_t)CHUNK_PITCH) +
-                         (uint32_t)sbn * (g.b.sw ? (uint32_t)SW_CHUNK : (uint32_t)CHUNK_PITCH);
-              }
+              const uint32_t row_tx = g.grp_tx[gi];
               mbar_expect_tx(fb, row_tx * (uint32_t)g.ER);
               if (!(DBG_SKIP(g) & 1)) {
                 // the entry's rows one after the other in the slot (rows past the image are zero filled by the copy)
@@ -1832,29 +1833,18 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
                   const uint32_t slot_addr = slots_addr + (uint32_t)slot * slot_bytes + (uint32_t)r * row_bytes;
                   // first pixel of the slot row: x0 - 1, or x0 - 2 when an operand comes through a pixel doubling
                   // map (whose rows start on an even pixel: half resolution pixel x0 / 2 - 1, row iy >> 1)
-                  const int xs = t.x0 - 1 - g.shift;
+                  const int xs = t.x0 - 1 - g.shift, xh = (t.x0 >> 1) - 1;
+                  const int ncp = g.ncp[gi];
 #pragma unroll 1
-                  for (int sg = 0; sg < 2; ++sg) {
-                    const Seg &sgm = sg ? g.b : g.a;
-                    const int first = sg ? nca : 0;                       // the operand's first chunk
-                    const int lo = max(c_lo, first), hi = min(c_hi, first + sgm.nch);
-                    if (hi <= lo) continue;
-                    int y;
-                    const void *tm = band ? tmap_of(g, sg, iy, sgm.dup ? iy >> 1 : iy, &y) : (sg ? (const void *)&g.tm_b : (const void *)&g.tm_a);
-                    if (!band) y = sgm.dup ? iy >> 1 : iy;
-                    const uint32_t per = sgm.sw ? (uint32_t)SW_CHUNK : (uint32_t)CHUNK_PITCH;
-                    // where the operand's chunks of this group lie in the slot row
-                    uint32_t area;
-                    if (!g.swmode) area = (uint32_t)(lo - c_lo) * CHUNK_PITCH;
-                    else if (g.G == 1) area = g.seg_off[sg];
-                    else area = (uint32_t)(lo - c_lo) * SW_CHUNK;
-                    const int step = sgm.sw ? 4 * sgm.tbox : sgm.tbox;  // chunks per copy
-                    for (int c = lo; c < hi; c += step) {
-                      const uint32_t dst = slot_addr + area + (uint32_t)(c - lo) * per;
-                      const int unit = sgm.sw ? (c - first) >> 2 : c - first;  // block or chunk coordinate
-                      if (sgm.dup) tma_load_5d(dst, tm, 0, 0, (t.x0 >> 1) - 1, unit, y, fb);
-                      else tma_load_4d(dst, tm, 0, xs, unit, y, fb);
-                    }
+                  for (int j = 0; j < ncp; ++j) {
+                    const uint32_t dst = slot_addr + g.cp[gi][j].dst;
+                    const int unit = g.cp[gi][j].unit, sg = g.cp[gi][j].sg;
+                    const bool dup = sg == 0 && g.a.dup;
+                    int y = dup ? iy >> 1 : iy;
+                    const void *tm = sg ? (const void *)&g.tm_b : (const void *)&g.tm_a;
+                    if (band) tm = tmap_of(g, sg, iy, y, &y);
+                    if (dup) tma_load_5d(dst, tm, 0, 0, xh, unit, y, fb);
+                    else tma_load_4d(dst, tm, 0, xs, unit, y, fb);
                   }
                 }
               } else {
@@ -2501,6 +2491,34 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
         }
       }
       if (nch / 2 > 16) return DNXCU_E_UNSUPPORTED;
+    }
+  }
+  // the copies of an entry, per K group (used when everything comes by TMA)
+  for (int gi = 0; gi < MAX_GROUPS; ++gi) {
+    g.ncp[gi] = 0;
+    g.grp_tx[gi] = 0;
+    if (gi >= g.G) continue;
+    const int c_lo = g.gc0[gi], c_hi = c_lo + g.gch[gi];
+    for (int sg = 0; sg < 2; ++sg) {
+      const Seg &s = sg ? g.b : g.a;
+      const int first = sg ? g.a.nch : 0;
+      const int lo = c_lo > first ? c_lo : first, hi = c_hi < first + s.nch ? c_hi : first + s.nch;
+      if (hi <= lo) continue;
+      const uint32_t per = s.sw ? (uint32_t)SW_CHUNK : (uint32_t)CHUNK_PITCH;
+      uint32_t area;
+      if (!g.swmode) area = (uint32_t)(lo - c_lo) * CHUNK_PITCH;
+      else if (g.G == 1) area = g.seg_off[sg];
+      else area = (uint32_t)(lo - c_lo) * SW_CHUNK;
+      const int step = s.sw ? 4 * s.tbox : s.tbox;
+      for (int c = lo; c < hi; c += step) {
+        if (g.ncp[gi] >= 8) return DNXCU_E_UNSUPPORTED;
+        TcArgs::Copy &cp = g.cp[gi][g.ncp[gi]++];
+        cp.dst = area + (uint32_t)(c - lo) * per;
+        cp.unit = (short)(s.sw ? (c - first) >> 2 : c - first);
+        cp.sg = (unsigned char)sg;
+        cp.pad = 0;
+      }
+      g.grp_tx[gi] += (uint32_t)(hi - lo) * per;
     }
   }
   const size_t wbytes = (size_t)9 * nch * g.N * 16;
