@@ -92,6 +92,7 @@ struct TcArgs {
   // (8, 132, 2, 1) lands in shared memory as [chunk][pixel][8 halves] — the MMA's K major core matrix order
   alignas(64) CUtensorMap tm_a;
   alignas(64) CUtensorMap tm_b;
+  alignas(64) CUtensorMap tm_out;  // (channels, x, y) view of the full resolution output, box (K, 32, 1)
   // the halo rows of a row band (one row tensors of their own): a above, a below, b above, b below
   alignas(64) CUtensorMap tm_halo[4];
   Seg a, b;
@@ -120,6 +121,8 @@ struct TcArgs {
   uint32_t src_bytes;    // expand mode: bytes of one half resolution staging buffer (one per slot)
   int stage_pitch;       // stacked form: bytes per pixel row of an epilogue warp's staging tile, 0 = direct stores
   int stage2;            // stacked form: two staging tiles per epilogue warp (a row pair is staged in one go)
+  int out_tma;           // stacked form: staged rows leave by one tensor copy per warp and row (shared -> global) from an
+                         // unpadded, swizzled tile: 1 = 128 byte pixel rows (64 channels), 2 = 64 byte rows (32 channels)
   uint32_t stage_warp_bytes;  // staging bytes per epilogue warp
   uint32_t tmem_cols;
   int parts;       // launches of this dispatch that run side by side (output channel split): each plans for 1/parts of the SMs
@@ -1177,7 +1180,7 @@ __device__ __forceinline__ bool st_issue_nk(const TcArgs &g, int nk, uint32_t hi
 
 // TMEM -> registers -> (+bias) -> binary16 pairs -> (ReLU) -> this lane's pixel row of the staging tile
 template <int NC, int EPI>
-__device__ __forceinline__ void stage_cols(const TcArgs &g, const OutPart &o, uint32_t taddr, int c0, uint32_t dst) {
+__device__ __forceinline__ void stage_cols(const TcArgs &g, const OutPart &o, uint32_t taddr, int c0, uint32_t dst, uint32_t xr) {
   uint32_t v[NC];
   if constexpr (NC == 32) tc_ld32(taddr + (uint32_t)c0, v);
   else tc_ld16(taddr + (uint32_t)c0, v);
@@ -1186,7 +1189,7 @@ __device__ __forceinline__ void stage_cols(const TcArgs &g, const OutPart &o, ui
   round_row<NC, EPI>(g, o, v, c0, h);
 #pragma unroll
   for (int j8 = 0; j8 < NC; j8 += 8)
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (uint32_t)((c0 + j8) * 2)), "r"(h[j8 / 2]),
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + ((uint32_t)((c0 + j8) * 2) ^ xr)), "r"(h[j8 / 2]),
                  "r"(h[j8 / 2 + 1]), "r"(h[j8 / 2 + 2]), "r"(h[j8 / 2 + 3])
                  : "memory");
 }
@@ -1194,7 +1197,7 @@ __device__ __forceinline__ void stage_cols(const TcArgs &g, const OutPart &o, ui
 // The same for one chunk of two rows: both TMEM loads are under way before the thread waits for either.
 template <int NC, int EPI>
 __device__ __forceinline__ void stage_cols2(const TcArgs &g, const OutPart &o, uint32_t taddr0, uint32_t taddr1, int c0,
-                                            uint32_t dst0, uint32_t dst1) {
+                                            uint32_t dst0, uint32_t dst1, uint32_t xr) {
   uint32_t v0[NC], v1[NC];
   if constexpr (NC == 32) {
     tc_ld32(taddr0 + (uint32_t)c0, v0);
@@ -1208,13 +1211,13 @@ __device__ __forceinline__ void stage_cols2(const TcArgs &g, const OutPart &o, u
   round_row<NC, EPI>(g, o, v0, c0, h);
 #pragma unroll
   for (int j8 = 0; j8 < NC; j8 += 8)
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 + (uint32_t)((c0 + j8) * 2)), "r"(h[j8 / 2]),
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 + ((uint32_t)((c0 + j8) * 2) ^ xr)), "r"(h[j8 / 2]),
                  "r"(h[j8 / 2 + 1]), "r"(h[j8 / 2 + 2]), "r"(h[j8 / 2 + 3])
                  : "memory");
   round_row<NC, EPI>(g, o, v1, c0, h);
 #pragma unroll
   for (int j8 = 0; j8 < NC; j8 += 8)
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst1 + (uint32_t)((c0 + j8) * 2)), "r"(h[j8 / 2]),
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst1 + ((uint32_t)((c0 + j8) * 2) ^ xr)), "r"(h[j8 / 2]),
                  "r"(h[j8 / 2 + 1]), "r"(h[j8 / 2 + 2]), "r"(h[j8 / 2 + 3])
                  : "memory");
 }
@@ -1254,21 +1257,38 @@ __device__ __forceinline__ void copy_out(uint32_t tile, int pitch, int nck, int 
   }
 }
 
+// A warp's staged row (32 pixels x K channels, swizzled like the tensor map says) to global memory through the
+// copy engine; pixels right of the image are dropped by the copy.  (The channel coordinate is 0: 16 byte rule.)
+__device__ __forceinline__ void tma_store_3d(const void *tmap, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tmap), "r"(src),
+               "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 __device__ __forceinline__ uint4 hmax8_u(uint4 a, uint4 b) {
   return make_uint4(hmax2_u32(a.x, b.x), hmax2_u32(a.y, b.y), hmax2_u32(a.z, b.z), hmax2_u32(a.w, b.w));
 }
 
 // 2x2 max of two staged rows (tile0, tile1), `npx` input pixels -> npx / 2 pooled pixels at `dst`.
+// (sw: 0 = padded tile, 1 / 2 = tile swizzled for the tensor copy, 128 / 64 byte pixel rows)
 __device__ __forceinline__ void copy_out_pooled(uint32_t tile0, uint32_t tile1, int pitch, int nck, int os8, int npx,
-                                                __half *dst, int lane) {
+                                                __half *dst, int lane, int sw) {
   const int total = (npx >> 1) * nck;
   int px = lane / nck, ch = lane - px * nck;
   const int dpx = 32 / nck, dch = 32 - dpx * nck;
   uint4 *o = reinterpret_cast<uint4 *>(dst);
   for (int i = lane; i < total; i += 32) {
-    const uint32_t off = (uint32_t)(2 * px * pitch + ch * 16);
-    const uint4 a = hmax8_u(lds16(tile0 + off), lds16(tile0 + off + (uint32_t)pitch));
-    const uint4 b = hmax8_u(lds16(tile1 + off), lds16(tile1 + off + (uint32_t)pitch));
+    const int p0 = 2 * px, p1 = p0 + 1;
+    const uint32_t x0 = sw == 1 ? (uint32_t)(p0 & 7) << 4 : sw == 2 ? (uint32_t)((p0 >> 1) & 3) << 4 : 0u;
+    const uint32_t x1 = sw == 1 ? (uint32_t)(p1 & 7) << 4 : sw == 2 ? (uint32_t)((p1 >> 1) & 3) << 4 : 0u;
+    const uint32_t off0 = (uint32_t)(p0 * pitch) + ((uint32_t)(ch * 16) ^ x0);
+    const uint32_t off1 = (uint32_t)(p1 * pitch) + ((uint32_t)(ch * 16) ^ x1);
+    const uint4 a = hmax8_u(lds16(tile0 + off0), lds16(tile0 + off1));
+    const uint4 b = hmax8_u(lds16(tile1 + off0), lds16(tile1 + off1));
     o[px * os8 + ch] = hmax8_u(a, b);
     px += dpx;
     ch += dch;
@@ -1662,7 +1682,11 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
     const int pitch = g.stage_pitch;  // 0: no staging tile, direct stores
     const int nck = part.K >> 3;
     const int os8 = g.os >> 3;  // output pixel stride in 16 byte units (= nck unless the output channels are split)
-    const uint32_t stage_base = slots_addr0 + (uint32_t)(P * S) * (slot_bytes + g.src_bytes) + (uint32_t)(warp - 2) * g.stage_warp_bytes;
+    const int otma = g.out_tma;
+    // (tiles that leave by tensor copy start on a 1024 byte boundary: the swizzle pattern is a function of the address)
+    const uint32_t stage_region = slots_addr0 + (uint32_t)(P * S) * (slot_bytes + g.src_bytes);
+    const uint32_t stage_base = (otma ? (stage_region + 1023u) & ~1023u : stage_region) + (uint32_t)(warp - 2) * g.stage_warp_bytes;
+    const uint32_t xr = otma == 1 ? (uint32_t)(lane & 7) << 4 : otma == 2 ? (uint32_t)((lane >> 1) & 3) << 4 : 0u;
     bool ok = true;
     int item = 0;
     int blk = 0;
@@ -1711,10 +1735,15 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           const bool both = g.stage2 && nrows == 2;
           if (!(DBG_SKIP(g) & 8)) {
             if (both) {
+              if (otma) {  // (the copies of this warp's last item have read the tiles)
+                if (lane == 0) bulk_wait_read();
+                __syncwarp();
+              }
               int c0 = 0;
 #pragma unroll 1
-              for (; c0 + 32 <= N; c0 += 32) stage_cols2<32, EPI>(g, part, t0, t1, c0, tile0 + mine, tile1 + mine);
-              if (c0 < N) stage_cols2<16, EPI>(g, part, t0, t1, c0, tile0 + mine, tile1 + mine);
+              for (; c0 + 32 <= N; c0 += 32) stage_cols2<32, EPI>(g, part, t0, t1, c0, tile0 + mine, tile1 + mine, xr);
+              if (c0 < N) stage_cols2<16, EPI>(g, part, t0, t1, c0, tile0 + mine, tile1 + mine, xr);
+              if (otma) fence_async_smem();  // (my rows of the tiles, for the copy engine; the warp meets below)
               if (tr) trace(g, 1, item >> 1, 3);
               // last TMEM read of the item done: give the blocks back, zeroed (every MMA accumulates)
               tc_zero_cols(t0, N);
@@ -1727,23 +1756,34 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
               }
               if (tr) trace(g, 1, item >> 1, 4);
               if (!(DBG_SKIP(g) & 4)) {
-                if (EPI & EPI_FULL) {
+                if ((EPI & EPI_FULL) && otma) {
+                  if (lane == 0 && npx > 0) {
+                    tma_store_3d(&g.tm_out, tile0, 0, xw, y);
+                    tma_store_3d(&g.tm_out, tile1, 0, xw, y + 1);
+                    bulk_commit();
+                  }
+                } else if (EPI & EPI_FULL) {
                   copy_out(tile0, pitch, nck, os8, npx, part.out + ((long long)y * g.W + xw) * g.os, lane);
                   copy_out(tile1, pitch, nck, os8, npx, part.out + ((long long)(y + 1) * g.W + xw) * g.os, lane);
                 }
                 if (EPI & EPI_POOL)
                   copy_out_pooled(tile0, tile1, pitch, nck, os8, npx,
-                                  part.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (xw >> 1)) * g.os, lane);
+                                  part.out_pool + ((long long)(y >> 1) * (g.W >> 1) + (xw >> 1)) * g.os, lane, otma);
               }
               __syncwarp();
               if (tr) trace(g, 1, item >> 1, 5);
             } else {
               for (int r = 0; r < nrows; ++r) {
                 const uint32_t tr_addr = r ? t1 : t0;
+                if (otma) {
+                  if (lane == 0) bulk_wait_read();
+                  __syncwarp();
+                }
                 int c0 = 0;
 #pragma unroll 1
-                for (; c0 + 32 <= N; c0 += 32) stage_cols<32, EPI>(g, part, tr_addr, c0, tile0 + mine);
-                if (c0 < N) stage_cols<16, EPI>(g, part, tr_addr, c0, tile0 + mine);
+                for (; c0 + 32 <= N; c0 += 32) stage_cols<32, EPI>(g, part, tr_addr, c0, tile0 + mine, xr);
+                if (c0 < N) stage_cols<16, EPI>(g, part, tr_addr, c0, tile0 + mine, xr);
+                if (otma) fence_async_smem();
                 if (tr && r == 0) trace(g, 1, item >> 1, 3);
                 if (r == nrows - 1) {
                   // last TMEM read of the item done: give the blocks back, zeroed (every MMA accumulates)
@@ -1760,8 +1800,16 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
                   __syncwarp();
                 }
                 // (a single row of a plan with the fused pool is a last row without partner: it has no pooled output)
-                if ((EPI & EPI_FULL) && !(DBG_SKIP(g) & 4))
-                  copy_out(tile0, pitch, nck, os8, npx, part.out + ((long long)(y + r) * g.W + xw) * g.os, lane);
+                if ((EPI & EPI_FULL) && !(DBG_SKIP(g) & 4)) {
+                  if (otma) {
+                    if (lane == 0 && npx > 0) {
+                      tma_store_3d(&g.tm_out, tile0, 0, xw, y + r);
+                      bulk_commit();
+                    }
+                  } else {
+                    copy_out(tile0, pitch, nck, os8, npx, part.out + ((long long)(y + r) * g.W + xw) * g.os, lane);
+                  }
+                }
                 __syncwarp();
                 if (tr && r == 0) trace(g, 1, item >> 1, 5);
               }
@@ -1800,6 +1848,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
         }
       }
     }
+    if (g.out_tma && lane == 0) bulk_wait_all();  // (the staging tiles must outlive the copies that read them)
   } else if (warp >= 10 && warp < 14) {
     // ---------------- input slots ----------------
     // P == 2: warps 10, 11 feed pipeline 0 and warps 12, 13 pipeline 1; P == 1: all four feed pipeline 0.
@@ -2337,6 +2386,24 @@ int make_tensor_map_sw(CUtensorMap *tm, const void *ptr, int H, int W, int C, in
   }
   return r == CUDA_SUCCESS ? DNXCU_OK : DNXCU_E_CUDA;
 }
+// The full resolution output as (K channels, x, y): box (K, 32, 1) = one epilogue warp's pixels of a row; the
+// swizzle mode is the one whose span is a pixel's K * 2 bytes (K = 64: 128 bytes, K = 32: 64 bytes).
+int make_tensor_map_out(CUtensorMap *tm, const void *ptr, int H, int W, int K) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return DNXCU_E_CUDA;
+  const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)W, (cuuint64_t)H};
+  const cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)W * K * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)K, 32, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, K == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if ((r != CUDA_ERROR_INVALID_CONTEXT && r != CUDA_ERROR_NOT_INITIALIZED) || cudaFree(nullptr) != cudaSuccess) break;
+  }
+  return r == CUDA_SUCCESS ? DNXCU_OK : DNXCU_E_CUDA;
+}
 // Whether the driver takes such maps: assumed until an encoding has failed once (then the producer warps expand
 // upsampled operands inside shared memory, as before).
 std::atomic<bool> g_dup_maps_ok{true};
@@ -2547,12 +2614,19 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
     (void)amax;
   }
   const bool stage_possible = g.K % 8 == 0 && !dbg_env("DNXCU_TC_NO_STAGE");
-  const size_t stage_pitch = (size_t)(g.cparts > 1 ? g.N : g.K) * 2 + 16;
+  // Full resolution rows of 32 or 64 channels leave through the copy engine: one tensor copy per warp and row out
+  // of an unpadded tile whose 16 byte pieces are swizzled the way the tensor map says (which keeps the staging
+  // writes free of bank conflicts, as the padding does for the other shapes).
+  const int out_tma = (stage_possible && g.full_out && g.cparts == 1 && g.parts == 1 && g.os == g.K && (g.K == 32 || g.K == 64) &&
+                       !dbg_env("DNXCU_TC_NO_OTMA"))
+                          ? (g.K == 64 ? 1 : 2)
+                          : 0;
+  const size_t stage_pitch = out_tma ? (size_t)g.K * 2 : (size_t)(g.cparts > 1 ? g.N : g.K) * 2 + 16;
   // two tiles per warp where a row pair is staged in one go: with the fused pool (which needs both rows), and for
   // thin layers, whose tiles are small and whose epilogue is what bounds them
   const bool two_tiles = g.pool || (g.N <= 32 && !dbg_env("DNXCU_TC_ONE_TILE"));
   const size_t stage_per_warp = (two_tiles ? 2 : 1) * 32 * stage_pitch;
-  const size_t base_bytes = ST_HEADER_BYTES + wregion + 1024;  // (the slots start on a 1024 byte boundary)
+  const size_t base_bytes = ST_HEADER_BYTES + wregion + 1024 + (out_tma ? 1024 : 0);  // (the slots start on a 1024 byte boundary, swizzled staging tiles too)
   const size_t plain_slot = (size_t)g.row_bytes * ER;
   // v.p2 == 2 ("PIPES=1"): one pipeline with a longer slot ring even where two would fit
   const bool p2_possible = 4 * g.N <= 256 && !dbg_env("DNXCU_TC_PIPES") && v.p2 != 2;
@@ -2591,6 +2665,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
     g.src_bytes = txp ? xp_src_bytes : 0;
     g.stage_pitch = tst ? (int)stage_pitch : 0;
     g.stage2 = (tst && two_tiles) ? 1 : 0;
+    g.out_tma = tst ? out_tma : 0;
     g.stage_warp_bytes = tst ? (uint32_t)stage_per_warp : 0;
   }
   if (P == 0 && g.swmode && !pl.no_sw) {
@@ -2623,7 +2698,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   while (p2 < (uint32_t)(P * g.NB * g.N)) p2 <<= 1;
   g.tmem_cols = p2;
   g.D = g.S - 1 < MAX_DEPTH ? g.S - 1 : MAX_DEPTH;
-  pl.smem = ST_HEADER_BYTES + wregion + 1024 + (size_t)P * g.S * slot_bytes + stage_total;
+  pl.smem = ST_HEADER_BYTES + wregion + 1024 + (g.out_tma ? 1024 : 0) + (size_t)P * g.S * slot_bytes + stage_total;
   const int sms = g.parts > 1 ? (sm_count() / g.parts > 0 ? sm_count() / g.parts : 1) : sm_count();
   const int lanes = sms * P;
   double best = 1e30;
@@ -2645,7 +2720,9 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   memset(&g.tm_a, 0, sizeof(g.tm_a));
   memset(&g.tm_b, 0, sizeof(g.tm_b));
   memset(g.tm_halo, 0, sizeof(g.tm_halo));
+  memset(&g.tm_out, 0, sizeof(g.tm_out));
   if (encode) {
+    if (g.out_tma && make_tensor_map_out(&g.tm_out, d.out, H, W, g.K)) return DNXCU_E_CUDA;
     if (g.a.sw) {
       if (make_tensor_map_sw(&g.tm_a, d.in_a, g.a.dup ? H / 2 : H, g.a.dup ? W / 2 : W, d.c_a, g.a.tbox, g.a.dup != 0)) return DNXCU_E_CUDA;
     } else if (g.a.dup) {
@@ -2764,6 +2841,7 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   g.ab = 0;
   g.eteams = 1;
   g.stage2 = 0;
+  g.out_tma = 0;
   uint32_t cols = 2u * R * g.Ns;
   if (cols > 512) return DNXCU_E_UNSUPPORTED;
   uint32_t p2 = 32;
