@@ -107,6 +107,12 @@ struct TcArgs {
   int leaky;                 // the activation is max(x, alpha * x) in binary16
   uint32_t alpha_h2;         // alpha as a binary16 pair
   int RB, S, nstrips, nunits;
+  // Stacked form, "cut" units (cut_L > 0): the rows of all strips, strip after strip, are cut into cut_R ranges of
+  // cut_L rows, one per pipeline of a CTA.  A range that crosses from one strip into the next makes two units;
+  // those ranges (cut_nb of them, indices cut_x[], ascending) go to the first lanes, so unit u < lanes is the
+  // first part of lane u's range and unit lanes + i the second part of lane i's.
+  int cut_L, cut_R, cut_nb;
+  short cut_x[32];
   int wstream, WST;
   int G;                 // K groups: 1 = rolling row window; > 1 = every pass loads its rows once per group
   int gc0[MAX_GROUPS];   // first 8 channel chunk of each group
@@ -1117,6 +1123,30 @@ struct StUnit {
 };
 __device__ __forceinline__ StUnit st_unit_of(const TcArgs &g, int u) {
   StUnit t;
+  if (g.cut_L > 0) {
+    const int second = u >= g.cut_R ? 1 : 0;
+    const int lane = second ? u - g.cut_R : u;
+    int r;
+    if (lane < g.cut_nb) {
+      r = g.cut_x[lane];
+    } else {
+      r = lane - g.cut_nb;  // the (lane - cut_nb)-th range that stays inside one strip
+      for (int i = 0; i < g.cut_nb; ++i)
+        if (g.cut_x[i] <= r) ++r;
+    }
+    const int start = r * g.cut_L, end = min(start + g.cut_L, g.nstrips * g.H);
+    const int strip = start / g.H, boundary = (strip + 1) * g.H;
+    if (!second) {
+      t.x0 = strip * STRIP;
+      t.y0 = start - strip * g.H;
+      t.rows_out = min(end, boundary) - start;
+    } else {
+      t.x0 = (strip + 1) * STRIP;
+      t.y0 = 0;
+      t.rows_out = end - boundary;
+    }
+    return t;
+  }
   const int strip = u % g.nstrips, rb = u / g.nstrips;
   t.x0 = strip * STRIP;
   t.y0 = rb * g.RB;
@@ -2715,6 +2745,40 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   g.RB = bestRB;
   g.nunits = g.nstrips * ((H + g.RB - 1) / g.RB);
   pl.grid = g.nunits < sms ? g.nunits : sms;  // spread first: a second unit per SM only when every SM has one
+  g.cut_L = g.cut_R = g.cut_nb = 0;
+  // More units than pipelines: blocks of RB rows leave the last wave partly empty and pay two halo rows per unit
+  // (1088 rows x 15 strips on 148 SMs: 3 units of 38 rows + 6 halo rows where 110.3 rows are the fair share).
+  // Instead cut the rows of all strips, laid end to end, into one range per pipeline: two halo rows per range,
+  // four for the few ranges that cross into the next strip.  (Row pairs stay together where the pool or a two
+  // row entry needs them.)
+  if (g.nunits > lanes && !dbg_env("DNXCU_TC_NO_CUT")) {
+    const int step = (g.pool || ER == 2 || (H & 1)) ? 2 : 1;
+    const long long T = (long long)g.nstrips * H;
+    int L = (int)((T + lanes - 1) / lanes);
+    L = (L + step - 1) / step * step;
+    for (int attempt = 0; attempt < 8 && !g.cut_L; ++attempt, L += step) {
+      const int R = (int)((T + L - 1) / L);
+      if (R % P != 0 || R > lanes || L > H || (step == 2 && (H & 1))) continue;
+      int nb = 0;
+      bool fits = true;
+      for (int r = 0; r < R && fits; ++r) {
+        const long long start = (long long)r * L, end = start + L < T ? start + L : T;
+        if (start / H != (end - 1) / H) {
+          if (nb < 32) g.cut_x[nb] = (short)r;
+          else fits = false;
+          ++nb;
+        }
+      }
+      if (!fits || R > 32767) continue;
+      const double cost = (double)L + (nb ? 5.0 : 2.5);
+      if (cost >= best) break;
+      g.cut_L = L;
+      g.cut_R = R;
+      g.cut_nb = nb;
+      g.nunits = R + nb;
+      pl.grid = R / P;
+    }
+  }
   pl.grid_y = g.cparts;
   pl.R = 0;
   memset(&g.tm_a, 0, sizeof(g.tm_a));
@@ -2842,6 +2906,7 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   g.eteams = 1;
   g.stage2 = 0;
   g.out_tma = 0;
+  g.cut_L = g.cut_R = g.cut_nb = 0;
   uint32_t cols = 2u * R * g.Ns;
   if (cols > 512) return DNXCU_E_UNSUPPORTED;
   uint32_t p2 = 32;
