@@ -111,7 +111,9 @@ struct TcArgs {
   // cut_L rows, one per pipeline of a CTA.  A range that crosses from one strip into the next makes two units;
   // those ranges (cut_nb of them, indices cut_x[], ascending) go to the first lanes, so unit u < lanes is the
   // first part of lane u's range and unit lanes + i the second part of lane i's.
-  int cut_L, cut_R, cut_nb;
+  // The ranges are cut in a row count that has cut_pad extra rows between two strips, so a range that crosses
+  // (two more halo rows and a restart of the pipeline) gets that many rows less.
+  int cut_L, cut_R, cut_nb, cut_pad;
   short cut_x[32];
   int wstream, WST;
   int G;                 // K groups: 1 = rolling row window; > 1 = every pass loads its rows once per group
@@ -1134,16 +1136,20 @@ __device__ __forceinline__ StUnit st_unit_of(const TcArgs &g, int u) {
       for (int i = 0; i < g.cut_nb; ++i)
         if (g.cut_x[i] <= r) ++r;
     }
-    const int start = r * g.cut_L, end = min(start + g.cut_L, g.nstrips * g.H);
-    const int strip = start / g.H, boundary = (strip + 1) * g.H;
+    const int Hp = g.H + g.cut_pad;
+    const int v0 = r * g.cut_L, v1 = min(v0 + g.cut_L, g.nstrips * Hp - g.cut_pad);
+    int s0 = v0 / Hp, y0 = v0 - s0 * Hp;       // first row of the range (one that starts in the padding starts the next strip)
+    if (y0 >= g.H) { ++s0; y0 = 0; }
+    int s1 = (v1 - 1) / Hp, y1 = (v1 - 1) - s1 * Hp;  // last row
+    if (y1 >= g.H) y1 = g.H - 1;
     if (!second) {
-      t.x0 = strip * STRIP;
-      t.y0 = start - strip * g.H;
-      t.rows_out = min(end, boundary) - start;
+      t.x0 = s0 * STRIP;
+      t.y0 = y0;
+      t.rows_out = (s1 == s0 ? y1 + 1 : g.H) - y0;
     } else {
-      t.x0 = (strip + 1) * STRIP;
+      t.x0 = s1 * STRIP;
       t.y0 = 0;
-      t.rows_out = end - boundary;
+      t.rows_out = y1 + 1;
     }
     return t;
   }
@@ -2745,7 +2751,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   g.RB = bestRB;
   g.nunits = g.nstrips * ((H + g.RB - 1) / g.RB);
   pl.grid = g.nunits < sms ? g.nunits : sms;  // spread first: a second unit per SM only when every SM has one
-  g.cut_L = g.cut_R = g.cut_nb = 0;
+  g.cut_L = g.cut_R = g.cut_nb = g.cut_pad = 0;
   // More units than pipelines: blocks of RB rows leave the last wave partly empty and pay two halo rows per unit
   // (1088 rows x 15 strips on 148 SMs: 3 units of 38 rows + 6 halo rows where 110.3 rows are the fair share).
   // Instead cut the rows of all strips, laid end to end, into one range per pipeline: two halo rows per range,
@@ -2753,28 +2759,34 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   // row entry needs them.)
   if (g.nunits > lanes && !dbg_env("DNXCU_TC_NO_CUT")) {
     const int step = (g.pool || ER == 2 || (H & 1)) ? 2 : 1;
-    const long long T = (long long)g.nstrips * H;
+    const int pad = step == 2 ? 4 : 3;
+    const int Hp = H + pad;
+    const long long T = (long long)g.nstrips * Hp - pad;
     int L = (int)((T + lanes - 1) / lanes);
     L = (L + step - 1) / step * step;
     for (int attempt = 0; attempt < 8 && !g.cut_L; ++attempt, L += step) {
       const int R = (int)((T + L - 1) / L);
-      if (R % P != 0 || R > lanes || L > H || (step == 2 && (H & 1))) continue;
+      if (R % P != 0 || R > lanes || L > H || L <= pad || (step == 2 && (H & 1))) continue;
       int nb = 0;
       bool fits = true;
       for (int r = 0; r < R && fits; ++r) {
-        const long long start = (long long)r * L, end = start + L < T ? start + L : T;
-        if (start / H != (end - 1) / H) {
+        const long long v0 = (long long)r * L, v1 = v0 + L < T ? v0 + L : T;
+        long long s0 = v0 / Hp;
+        if (v0 - s0 * Hp >= H) ++s0;
+        const long long s1 = (v1 - 1) / Hp;
+        if (s1 != s0) {
           if (nb < 32) g.cut_x[nb] = (short)r;
           else fits = false;
           ++nb;
         }
       }
       if (!fits || R > 32767) continue;
-      const double cost = (double)L + (nb ? 5.0 : 2.5);
+      const double cost = (double)L + 2.5;
       if (cost >= best) break;
       g.cut_L = L;
       g.cut_R = R;
       g.cut_nb = nb;
+      g.cut_pad = pad;
       g.nunits = R + nb;
       pl.grid = R / P;
     }
@@ -2906,7 +2918,7 @@ int make_plan(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool encode, 
   g.eteams = 1;
   g.stage2 = 0;
   g.out_tma = 0;
-  g.cut_L = g.cut_R = g.cut_nb = 0;
+  g.cut_L = g.cut_R = g.cut_nb = g.cut_pad = 0;
   uint32_t cols = 2u * R * g.Ns;
   if (cols > 512) return DNXCU_E_UNSUPPORTED;
   uint32_t p2 = 32;
