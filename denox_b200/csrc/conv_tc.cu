@@ -1013,9 +1013,14 @@ __device__ __forceinline__ void store_row(int K, __half *o, const uint32_t (&h)[
   }
 }
 
-template <int NC, int RSTEP, int EPI>
+struct NoRelease {
+  __device__ __forceinline__ void operator()() const {}
+};
+// `rel` runs as soon as the accumulators are in registers (a layer of at most 32 channels hands its TMEM blocks back
+// there, before the conversion and the stores: the ring of blocks is what couples MMA and epilogue in thin layers).
+template <int NC, int RSTEP, int EPI, class Rel = NoRelease>
 __device__ __forceinline__ void epi_fast(const TcArgs &g, const OutPart &o, uint32_t t0, uint32_t t1, int c0, int x,
-                                         int y, bool xin, int lane) {
+                                         int y, bool xin, int lane, Rel rel = Rel()) {
   uint32_t v0[NC], v1[RSTEP == 2 ? NC : 2];
   if constexpr (NC == 32) {
     tc_ld32(t0 + (uint32_t)c0, v0);
@@ -1025,6 +1030,7 @@ __device__ __forceinline__ void epi_fast(const TcArgs &g, const OutPart &o, uint
     if constexpr (RSTEP == 2) tc_ld16(t1 + (uint32_t)c0, v1);
   }
   tc_wait_ld();
+  rel();
   if (DBG_SKIP(g) & 16) return;
   if (DBG_SKIP(g) & 4) xin = false;
   uint32_t h0[NC / 2], h1[RSTEP == 2 ? NC / 2 : 1];
@@ -1231,9 +1237,9 @@ __device__ __forceinline__ void stage_cols(const TcArgs &g, const OutPart &o, ui
 }
 
 // The same for one chunk of two rows: both TMEM loads are under way before the thread waits for either.
-template <int NC, int EPI>
+template <int NC, int EPI, class Rel = NoRelease>
 __device__ __forceinline__ void stage_cols2(const TcArgs &g, const OutPart &o, uint32_t taddr0, uint32_t taddr1, int c0,
-                                            uint32_t dst0, uint32_t dst1, uint32_t xr) {
+                                            uint32_t dst0, uint32_t dst1, uint32_t xr, Rel rel = Rel()) {
   uint32_t v0[NC], v1[NC];
   if constexpr (NC == 32) {
     tc_ld32(taddr0 + (uint32_t)c0, v0);
@@ -1243,6 +1249,7 @@ __device__ __forceinline__ void stage_cols2(const TcArgs &g, const OutPart &o, u
     tc_ld16(taddr1 + (uint32_t)c0, v1);
   }
   tc_wait_ld();
+  rel();
   uint32_t h[NC / 2];
   round_row<NC, EPI>(g, o, v0, c0, h);
 #pragma unroll
@@ -1775,21 +1782,32 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
                 if (lane == 0) bulk_wait_read();
                 __syncwarp();
               }
-              int c0 = 0;
-#pragma unroll 1
-              for (; c0 + 32 <= N; c0 += 32) stage_cols2<32, EPI>(g, part, t0, t1, c0, tile0 + mine, tile1 + mine, xr);
-              if (c0 < N) stage_cols2<16, EPI>(g, part, t0, t1, c0, tile0 + mine, tile1 + mine, xr);
-              if (otma) fence_async_smem();  // (my rows of the tiles, for the copy engine; the warp meets below)
-              if (tr) trace(g, 1, item >> 1, 3);
               // last TMEM read of the item done: give the blocks back, zeroed (every MMA accumulates)
-              tc_zero_cols(t0, N);
-              tc_zero_cols(t1, N);
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) {
-                mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b0));
-                mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b1));
+              auto release = [&]() {
+                tc_zero_cols(t0, N);
+                tc_zero_cols(t1, N);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                  mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b0));
+                  mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b1));
+                }
+              };
+              if (N == 32) {
+                // one chunk: the blocks go back as soon as it is in registers, before the conversion
+                stage_cols2<32, EPI>(g, part, t0, t1, 0, tile0 + mine, tile1 + mine, xr, release);
+              } else if (N == 16) {
+                stage_cols2<16, EPI>(g, part, t0, t1, 0, tile0 + mine, tile1 + mine, xr, release);
+              } else {
+                int c0 = 0;
+#pragma unroll 1
+                for (; c0 + 32 <= N; c0 += 32) stage_cols2<32, EPI>(g, part, t0, t1, c0, tile0 + mine, tile1 + mine, xr);
+                if (c0 < N) stage_cols2<16, EPI>(g, part, t0, t1, c0, tile0 + mine, tile1 + mine, xr);
+                release();
               }
+              if (otma) fence_async_smem();  // (my rows of the tiles, for the copy engine; the warp meets below)
+              __syncwarp();
+              if (tr) trace(g, 1, item >> 1, 3);
               if (tr) trace(g, 1, item >> 1, 4);
               if (!(DBG_SKIP(g) & 4)) {
                 if ((EPI & EPI_FULL) && otma) {
@@ -1864,6 +1882,23 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
           continue;
         }
         int c0 = (DBG_SKIP(g) & 8) ? N : 0;
+        if (nrows == 2 && N <= 32 && c0 == 0) {
+          // one chunk: the blocks go back as soon as it is in registers, before the conversion and the stores
+          auto release = [&]() {
+            tc_zero_cols(t0, N);
+            tc_zero_cols(t1, N);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b0));
+              mbar_arrive(bar(ST_BAR_TEMPTY + bofs + b1));
+            }
+          };
+          if (N == 32) epi_fast<32, 2, EPI>(g, part, t0, t1, 0, x, y, xin, lane, release);
+          else epi_fast<16, 2, EPI>(g, part, t0, t1, 0, x, y, xin, lane, release);
+          if (tr) trace(g, 1, item >> 1, 2);
+          continue;
+        }
         if (nrows == 2) {
 #pragma unroll 1
           for (; c0 + 32 <= N; c0 += 32) epi_fast<32, 2, EPI>(g, part, t0, t1, c0, x, y, xin, lane);
