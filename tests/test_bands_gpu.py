@@ -22,7 +22,10 @@ def _whole(net, x, h, w):
     return y
 
 
-@pytest.mark.parametrize("which,h,w,world", [("tiny", 64, 160, 2), ("oidn", 64, 144, 2), ("oidn", 128, 48, 4), ("oidn", 384, 160, 8)])
+# (the last case is large enough for the conv kernel to cut its work units as contiguous row ranges, with other
+# boundaries in a band than in the whole image)
+@pytest.mark.parametrize("which,h,w,world", [("tiny", 64, 160, 2), ("oidn", 64, 144, 2), ("oidn", 128, 48, 4), ("oidn", 384, 160, 8),
+                                             ("oidn", 1280, 1920, 2)])
 def test_bands_on_one_device_equal_whole_image(which, h, w, world):
     import torch
     from gpu_util import wrap
