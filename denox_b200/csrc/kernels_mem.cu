@@ -136,6 +136,41 @@ __global__ void pad_channels(const unsigned short *__restrict__ in, uint4 *__res
   }
 }
 
+// The same by warps: the input of 32 consecutive pixels is 64 * C contiguous bytes that start on a 16 byte boundary
+// when the tensor does, so a warp fetches them with 16 byte loads into its piece of shared memory (instead of up to
+// nine 2 byte loads per pixel), picks the pieces apart there and writes the 32 * Cp8 output pieces with consecutive
+// lanes on consecutive 16 bytes.  The last, partial group of pixels is fetched by 2 byte loads.
+__global__ void pad_channels_warp(const unsigned short *__restrict__ in, uint4 *__restrict__ out, long long P, int C,
+                                  int Cp8) {
+  extern __shared__ uint4 pad_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  uint4 *s4 = pad_smem + (size_t)warp * 4 * C;  // 64 * C bytes per warp
+  const unsigned short *s = reinterpret_cast<const unsigned short *>(s4);
+  const uint4 *in16 = reinterpret_cast<const uint4 *>(in);
+  const long long groups = (P + 31) / 32;
+  for (long long w = (long long)blockIdx.x * wpb + warp; w < groups; w += (long long)gridDim.x * wpb) {
+    const long long p0 = w * 32;
+    const int np = (int)(P - p0 < 32 ? P - p0 : 32);
+    if (np == 32) {
+      for (int i = lane; i < 4 * C; i += 32) s4[i] = __ldg(in16 + w * 4 * C + i);
+    } else {
+      unsigned short *sw = reinterpret_cast<unsigned short *>(s4);
+      for (int i = lane; i < np * C; i += 32) sw[i] = __ldg(in + p0 * C + i);
+    }
+    __syncwarp();
+    for (int q = lane; q < np * Cp8; q += 32) {
+      const int px = q / Cp8, c8 = q - px * Cp8;
+      const unsigned short *src = s + px * C + c8 * 8;
+      unsigned int wv[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (c8 * 8 + e < C) wv[e >> 1] |= (unsigned int)src[e] << ((e & 1) * 16);
+      out[p0 * Cp8 + q] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+    }
+    __syncwarp();
+  }
+}
+
 // Spatial pad by edge replication and spatial slice: one thread per output pixel and piece (16 bytes
 // or one channel) of it.  T = uint4 (C % 8 == 0) or unsigned short.
 //   pad:   out[ho][wo] = in[clamp(ho - top, 0, IH - 1)][clamp(wo - left, 0, IW - 1)]   (memory_pad.comp:71-72)
@@ -242,8 +277,18 @@ int mem_launch(const Variant &v, const dnxcu_dispatch &d, cudaStream_t s) {
     if (((uintptr_t)d.out & 15) || ((uintptr_t)d.in_a & 1)) return DNXCU_E_MISALIGNED;
     uint32_t gp[3];
     mem_grid(v, d, gp);
-    pad_channels<<<gp[0], kThreads, 0, s>>>((const unsigned short *)d.in_a, (uint4 *)d.out, (long long)H * W, d.c_a,
-                                            d.c_out / 8);
+    const size_t warp_smem = (size_t)(kThreads / 32) * 64 * d.c_a;
+    if (((uintptr_t)d.in_a & 15) == 0 && warp_smem <= 48 * 1024) {
+      // (a grid of a few blocks per SM: every warp walks groups of 32 pixels)
+      const long long groups = ((long long)H * W + 31) / 32;
+      long long blocks = (groups + kThreads / 32 - 1) / (kThreads / 32);
+      if (blocks > gp[0]) blocks = gp[0];
+      pad_channels_warp<<<(unsigned)blocks, kThreads, warp_smem, s>>>((const unsigned short *)d.in_a, (uint4 *)d.out,
+                                                                      (long long)H * W, d.c_a, d.c_out / 8);
+    } else {
+      pad_channels<<<gp[0], kThreads, 0, s>>>((const unsigned short *)d.in_a, (uint4 *)d.out, (long long)H * W, d.c_a,
+                                              d.c_out / 8);
+    }
     DNXCU_CUDA(cudaGetLastError());
     return DNXCU_OK;
   }
