@@ -1091,8 +1091,8 @@ constexpr int ST_BAR_COUNT = ST_BAR_RAW + MAX_SLOTS;
 static_assert(ST_BAR_COUNT * 8 + 16 <= HEADER_BYTES, "header too small");
 constexpr int ST_OFF_TMEM_PTR = ST_BAR_COUNT * 8;
 constexpr int ST_OFF_ABORT = ST_OFF_TMEM_PTR + 4;   // int abort flag, then the 64-bit wait limit
-constexpr int ST_OFF_TURN = ST_OFF_ABORT + 12;      // entries issued so far (two alternating MMA threads)
-static_assert(ST_OFF_TURN + 4 <= HEADER_BYTES, "header too small");
+constexpr int ST_OFF_TURN = ST_OFF_ABORT + 12;      // entries issued so far (two alternating MMA threads), one word per pipeline
+static_assert(ST_OFF_TURN + 8 <= HEADER_BYTES, "header too small");
 // entry descriptors, one per slot (index: pipeline's barrier offset + slot), written by the descriptor threads
 constexpr int ST_SUBDESC_BYTES = 48;                  // one input row
 constexpr int ST_DESC_BYTES = 2 * ST_SUBDESC_BYTES;   // an entry holds one or two input rows (TcArgs::ER)
@@ -1401,6 +1401,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
       *abort_flag = 0;
       *reinterpret_cast<volatile unsigned long long *>(abort_flag + 1) = g.wait_limit;
       *reinterpret_cast<volatile uint32_t *>(smem + ST_OFF_TURN) = 0u;
+      *reinterpret_cast<volatile uint32_t *>(smem + ST_OFF_TURN + 4) = 0u;
     }
     // who completes a slot: the TMA bytes alone; or TMA bytes + the producer warps' cp.async part; or, in expand
     // mode, the producer warps alone after they have expanded the TMA data that landed on the raw barrier;
@@ -1563,13 +1564,16 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
   // issued so far) that the thread whose turn it is next polls, bounded like every other wait; the order of the
   // MMAs, and with it the order of the additions into an accumulator, stays that of the entries.
   const bool ab = g.ab != 0;
-  if (warp < P || (ab && warp == 15)) {
+  // (the partner thread sits in warp 15 with one pipeline; with two pipelines, which alternate only when every
+  // operand comes by TMA, in the then idle producer warps 11 and 13)
+  const bool ab_partner = ab && (P == 1 ? warp == 15 : (warp == 11 || warp == 13));
+  if (warp < P || ab_partner) {
     // ---------------- MMA issue: one thread, one descriptor per entry ----------------
     // Everything that depends on where an entry sits in its unit (TMEM blocks, runs, barriers) was worked
     // out by the pipeline's descriptor thread and lies in shared memory when the slot's barrier completes;
     // this thread only waits, loads six vectors and issues.  It is the thread the kernel's speed hangs on.
-    const int pipe = warp == 15 ? 0 : warp;
-    const int me = warp == 15 ? 1 : 0;  // which of the two alternating threads
+    const int pipe = ab_partner ? (warp == 13 ? 1 : 0) : warp;
+    const int me = ab_partner ? 1 : 0;  // which of the two alternating threads
     const int nw = ab ? 2 : 1;
     const uint32_t leader = 1u;
     const int bofs = pipe * ST_PIPE_STRIDE;
@@ -1581,7 +1585,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv3x3_tc_stack(const __grid_c
       tc_mma_e(d, ((uint64_t)ahi << 32) | alo, ((uint64_t)b_hi << 32) | blo, idesc, leader);
     };
     // Waits until `want` entries have been issued (this thread's turn); gives up like mbar_wait does.
-    volatile uint32_t *turn = reinterpret_cast<volatile uint32_t *>(smem + ST_OFF_TURN);
+    volatile uint32_t *turn = reinterpret_cast<volatile uint32_t *>(smem + ST_OFF_TURN + 4 * pipe);
     auto my_turn = [&](uint32_t want) -> bool {
       if (*turn == want) return true;
       const unsigned long long t0 = clock64();
@@ -2764,7 +2768,7 @@ int make_plan_stack(const Variant &v, const dnxcu_dispatch &d, Plan &pl, bool en
   // One pipeline: two MMA threads take alternate entries (each entry is one input row of one K group).  Not in
   // fix-up mode: there the producer warps' work in shared memory bounds the kernel, and a second polling thread
   // only takes shared memory cycles away from them (measured: 5-20 % slower).
-  g.ab = (P == 1 && ER == 1 && g.S >= 2 && !g.xp && !dbg_env("DNXCU_TC_ONE_ISSUER")) ? 1 : 0;
+  g.ab = (ER == 1 && g.S >= 2 && !g.xp && (P == 1 || !g.cpa) && !dbg_env("DNXCU_TC_ONE_ISSUER")) ? 1 : 0;
   uint32_t p2 = 32;
   while (p2 < (uint32_t)(P * g.NB * g.N)) p2 <<= 1;
   g.tmem_cols = p2;
