@@ -1074,7 +1074,9 @@ __device__ __forceinline__ void epi_fast(const TcArgs &g, const OutPart &o, uint
 //   - runs of blocks are split where the ring wraps and where N' would exceed 256
 //   - an input slot is released as soon as its own row's MMAs are committed
 // Warp roles (512 threads): warps 0..P-1 issue the MMAs of pipeline 0..P-1 (one thread
-// each; warp 0 owns the TMEM allocation); warp 1 also moves the weights and, with one
+// each, or two that take alternate entries: the partner of a single pipeline's thread
+// is in warp 15, the partners of two pipelines are in the producer warps 11 and 13 when
+// every operand comes by TMA; warp 0 owns the TMEM allocation); warp 1 also moves the weights and, with one
 // pipeline in expand mode, issues the TMA copies; warps 2..2+4P-1 are the epilogue teams
 // (four warps per pipeline, one TMEM lane quarter each); warps 10-13 fill the input
 // slots; warps 14, 15 hold the descriptor threads (one thread per pipeline), which work
